@@ -1,0 +1,144 @@
+/*
+ * powerinfer_b200.h -- C ABI of the B200 (sm_100a) implementation of PowerInfer's decode hot path.
+ *
+ * The library replaces what the reference's CUDA back end (ggml-cuda.cu behind ggml-cuda.h) does
+ * for the decode token loop: the activation predictor, the two neuron-sparse operators
+ * ggml_mul_mat_idx / ggml_axpy, the Q4_0 / Q8_0 block formats they read, and the dense decode nodes
+ * between them (norms, mat-vecs, RoPE, KV store, attention, lm head).  Each entry point names the
+ * reference interface it stands in for (file:line in the reference tree).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name starts with host_;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing synchronises
+ *     unless the comment says so;
+ *   - matrices are row-major [rows, cols] with cols contiguous (ggml: ne[0] = cols), activations are
+ *     [T tokens, n] with n contiguous;
+ *   - functions return PI_OK or an error code and leave a message in pi_last_error(); they never call
+ *     exit() (the reference does: ggml-cuda.cu:193-230);
+ *   - nothing here allocates device memory: scratch comes in as (workspace, workspace_bytes), sized by
+ *     pi_workspace_bytes().  Scratch must be 256-byte aligned.
+ */
+#ifndef POWERINFER_B200_H
+#define POWERINFER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PI_OK               0
+#define PI_ERR_INVALID      1   /* bad argument (shape, alignment, null pointer) */
+#define PI_ERR_CUDA         2   /* a CUDA runtime call failed; message holds cudaGetErrorString */
+#define PI_ERR_WORKSPACE    3   /* workspace too small or misaligned */
+#define PI_ERR_UNSUPPORTED  4
+#define PI_ERR_TIMEOUT      5   /* a bounded device-side wait ran out (multi-GPU exchange) */
+
+/* weight storage types (ggml.h GGML_TYPE_F16 / GGML_TYPE_Q4_0) */
+#define PI_TYPE_F16   1         /* IEEE half, row of n halves */
+#define PI_TYPE_Q4_0  2         /* ggml block_q4_0 {fp16 d; uint8 qs[16]} (ggml-quants.h:11-15), 18 bytes per 32 weights.
+                                 * Device copies are held in the PLANAR form made by pi_q4_0_repack. */
+
+const char * pi_last_error(void);
+int          pi_version(void);
+
+/* bytes of one weight row: F16 2n, Q4_0 18n/32 (same for the ggml and the planar layout) */
+size_t pi_row_bytes(int wtype, int64_t ncols);
+
+/* upper bound of the scratch any single op below needs for these extents */
+size_t pi_workspace_bytes(int64_t ncols, int64_t nrows, int T);
+
+/* ---- block formats (ggml-quants.c) ------------------------------------------------------------ */
+
+/* quantize_row_q4_0_reference (ggml-quants.c:428-463): x F32 [nrows, ncols] -> ggml Q4_0 blocks. ncols % 32 == 0 */
+int pi_quantize_q4_0(const float * x, void * q4_ggml, int64_t nrows, int64_t ncols, void * stream);
+
+/* Re-layout done once at upload (the reference uploads through ggml_cuda_transform_tensor, ggml-cuda.cu:8946-9000,
+ * and the host never looks at device bytes): ggml blocks -> per row [ncols/32 x 16 B nibbles][ncols/32 x fp16 d],
+ * so nibbles load as aligned 128-bit words.  Needs ncols % 256 == 0.  src and dst must not overlap. */
+int pi_q4_0_repack(const void * q4_ggml, void * q4_planar, int64_t nrows, int64_t ncols, void * stream);
+
+/* dequantize_row_q4_0 (ggml-quants.c:1074-1092) from the planar layout -> F32 [nrows, ncols] */
+int pi_dequantize_q4_0(const void * q4_planar, float * y, int64_t nrows, int64_t ncols, void * stream);
+
+/* The activation quantiser of the CPU path, quantize_row_q8_0 (ggml-quants.c:702-760): per 32 values
+ * d = amax/127 (stored as fp16), q = rne(x * 127/amax).  Output is ggml block_q8_0 (34-byte blocks). */
+int pi_quantize_q8_0(const float * x, void * q8_ggml, int64_t nrows, int64_t ncols, void * stream);
+
+/* ---- the two sparse operators (ggml.h:1094-1112) ------------------------------------------------ */
+
+/* ggml_mul_mat_idx / ggml_mul_mat_idx_upscale -> GGML_OP_MUL_MAT_SPARSE
+ * (CPU ggml.c:14030-14282; CUDA ggml-cuda.cu:4684-4824, 5489-5535, dispatch 8787-8803).
+ *   W      [n_w_rows, ncols] F16 or planar Q4_0 : rows of up / gate held on this device
+ *   x      F32 [T, ncols]
+ *   idx    F32 [T, idx_stride]  predictor logits, indexed by GLOBAL neuron id
+ *   bucket NULL, or int32 [n_w_rows] sorted global ids of the local rows (gpu_bucket, llama.cpp:2943-2967)
+ *   dst    F32 [T, n_dst_rows]  dst[t, g] = idx[t, g] >= threshold ? W[r,:] . x[t,:] : 0 with g = bucket ? bucket[r] : r;
+ *          rows no local row maps to are written 0.
+ * Activations are rounded as the CPU path does before the dot product: to FP16 for F16 weights, to Q8_0 for Q4_0. */
+int pi_mul_mat_idx(int wtype, const void * W, int64_t n_w_rows, int64_t ncols,
+                   const float * x, int T, const float * idx, int64_t idx_stride,
+                   const int32_t * bucket, float threshold,
+                   float * dst, int64_t n_dst_rows,
+                   void * workspace, size_t workspace_bytes, void * stream);
+
+/* ggml_axpy -> GGML_OP_AXPY (CPU ggml.c:14314-14618, ggml-quants.c:2426-2509; CUDA ggml-cuda.cu:4478-4682,
+ * dispatch 8805-8814).
+ *   Wt     [n_w_rows, ncols] : rows of ffn_down_t held on this device (one row per neuron)
+ *   h      F32 [T, h_stride]   FFN hidden activations, indexed by global neuron id
+ *   dst    F32 [T, ncols]      dst[t,:] = sum over local rows r with idx[t,g] >= threshold of coef(h[t,g]) * Wt[r,:]
+ * coef() is the CPU path's: h rounded to FP16 (F16 weights), or Q8_0 over blocks of 32 consecutive neurons (Q4_0
+ * weights; then h_stride % 32 == 0 and a bucket must hold whole 32-neuron blocks).  The sum runs in a fixed order
+ * (no atomics): two calls give identical bits. */
+int pi_axpy(int wtype, const void * Wt, int64_t n_w_rows, int64_t ncols,
+            const float * h, int T, int64_t h_stride, const float * idx, int64_t idx_stride,
+            const int32_t * bucket, float threshold,
+            float * dst,
+            void * workspace, size_t workspace_bytes, void * stream);
+
+/* ---- dense decode nodes ------------------------------------------------------------------------------ */
+
+/* ggml_mul_mat with a weight matrix and T <= 32 activation columns (ggml.c:9598-9807; CUDA ggml-cuda.cu:4310-4414):
+ * dst[t, r] = W[r,:] . x[t,:] (+ bias[r]).  Same activation rounding as above. */
+int pi_mul_mat(int wtype, const void * W, int64_t nrows, int64_t ncols, const float * x, int T,
+               const float * bias, float * dst, void * workspace, size_t workspace_bytes, void * stream);
+
+/* The predictor sub-graph of llm_build_ffn_sparse (llama.cpp:4688-4695): idx = fc2 . relu(fc1 . p), both F16.
+ *   fc1 [rank, d], fc2 [F, rank], p F32 [T, d] -> idx F32 [T, F] */
+int pi_predictor(const void * fc1, const void * fc2, int64_t d, int64_t rank, int64_t F,
+                 const float * p, int T, float * idx, void * workspace, size_t workspace_bytes, void * stream);
+
+/* Predictor mask -> sorted list of the neurons active for at least one token (warp ballot / popc compaction).
+ * There is no such list in the reference (every row is tested in place: ggml-cuda.cu:4694-4697); it is what lets the
+ * sparse kernels spend no warp on an inactive row.  list int32 [F], count int32 [1]. */
+int pi_active_list(const float * idx, int64_t F, int T, int64_t idx_stride, float threshold,
+                   int32_t * list, int32_t * count, void * workspace, size_t workspace_bytes, void * stream);
+
+/* ggml_rms_norm / ggml_norm followed by the weight (and bias) of llm_build_norm (llama.cpp:4420-4450;
+ * ggml.c:9169-9284).  rms != 0 selects RMSNorm.  w, b may be NULL. */
+int pi_norm(const float * x, int T, int64_t n, int rms, float eps, const float * w, const float * b,
+            float * y, void * stream);
+
+/* ggml_rope_custom modes 0 (pairs (2i, 2i+1)) and 2 (neox: pairs (i, i+n/2)) for one token per row
+ * (ggml.c:11163-11325).  x F32 [T, n_heads*head_dim] in place; pos int32 [T].  The angle table
+ * cs F32 [n_pos, head_dim/2, 2] = (cos, sin) is built on the host by pi_rope_table_host with the reference's
+ * float recurrence theta *= theta_scale, so device and CPU path use the same angles. */
+int pi_rope(float * x, int T, int n_heads, int head_dim, const int32_t * pos, const float * cs, int neox, void * stream);
+void pi_rope_table_host(float * host_cs, int n_pos, int head_dim, float freq_base);
+
+/* One decode step of attention for T tokens that each own one sequence position (llm_build_kv_store +
+ * llm_build_kqv, llama.cpp:4383-4418, 4764-4850): store K,V of the new token as FP16, then softmax(QK^T/sqrt(hd)) V
+ * over positions 0..pos[t] of its sequence.  Numerics follow the CPU path: Q and the probabilities are rounded to FP16,
+ * exp goes through FP16 (ggml.c:10757-10759).
+ *   q F32 [T, n_head*hd] (RoPE'd), k,v F32 [T, n_head_kv*hd]
+ *   k_cache, v_cache FP16 [n_seq, n_ctx, n_head_kv*hd]; seq int32 [T] (NULL: sequence 0), pos int32 [T]
+ *   out F32 [T, n_head*hd] */
+int pi_attention_decode(const float * q, const float * k, const float * v, void * k_cache, void * v_cache,
+                        const int32_t * seq, const int32_t * pos, int T, int n_head, int n_head_kv, int head_dim,
+                        int n_ctx, float * out, void * stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

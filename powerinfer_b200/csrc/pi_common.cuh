@@ -1,0 +1,211 @@
+// Shared device helpers and the internal launcher interface of the sm_100a kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/powerinfer_b200.h"
+
+namespace pi {
+
+// ---------------------------------------------------------------------------------------------- errors
+void set_error(const char * fmt, ...);
+int  cuda_fail(cudaError_t e, const char * what);
+
+#define PI_CUDA(call)                                                         \
+    do {                                                                      \
+        cudaError_t e_ = (call);                                              \
+        if (e_ != cudaSuccess) return ::pi::cuda_fail(e_, #call);             \
+    } while (0)
+
+#define PI_REQUIRE(cond, ...)                                                 \
+    do {                                                                      \
+        if (!(cond)) { ::pi::set_error(__VA_ARGS__); return PI_ERR_INVALID; } \
+    } while (0)
+
+#define PI_LAUNCH_CHECK(name)                                                 \
+    do {                                                                      \
+        cudaError_t e_ = cudaGetLastError();                                  \
+        if (e_ != cudaSuccess) return ::pi::cuda_fail(e_, name);              \
+    } while (0)
+
+static inline int64_t imin64(int64_t a, int64_t b) { return a < b ? a : b; }
+int sm_count();                                   // multiprocessors of the current device (cached per device)
+
+// ---------------------------------------------------------------------------------------- activations
+// An activation vector in the form a mat-vec consumes it (the reference's vec_dot_type, ggml.c:430-440):
+//   F16 weights  -> h16 [T, n] halves (FP32 rounded to nearest even)
+//   Q4_0 weights -> Q8_0 split into planes so that every plane loads as aligned 128-bit words:
+//                   lo/hi [T, n/32] uint4 = int8 values 0..15 / 16..31 of each block,
+//                   d [T, n/32] float (the FP16-rounded scale), s [T, n/32] int (sum of the block's 32 int8)
+struct Act {
+    const __half * h16 = nullptr;
+    const uint4 *  lo  = nullptr;
+    const uint4 *  hi  = nullptr;
+    const float *  d   = nullptr;
+    const int *    s   = nullptr;
+};
+
+struct ActBuf {            // writable view of the same planes
+    __half * h16 = nullptr;
+    uint4 *  lo  = nullptr;
+    uint4 *  hi  = nullptr;
+    float *  d   = nullptr;
+    int *    s   = nullptr;
+    Act view() const { Act a; a.h16 = h16; a.lo = lo; a.hi = hi; a.d = d; a.s = s; return a; }
+};
+
+// bytes of an ActBuf for T tokens of n values in the form `wtype` weights consume, rounded up to 256
+size_t act_bytes(int wtype, int64_t n, int T);
+// carve an ActBuf out of scratch memory; advances *p
+ActBuf act_carve(int wtype, int64_t n, int T, char ** p);
+
+// simple bump allocator over caller-provided scratch
+struct Scratch {
+    char * base; char * cur; char * end;
+    Scratch(void * p, size_t n) : base((char *)p), cur((char *)p), end((char *)p + n) {}
+    void * take(size_t bytes) {
+        bytes = (bytes + 255) & ~size_t(255);
+        if (cur + bytes > end) return nullptr;
+        void * r = cur; cur += bytes; return r;
+    }
+};
+
+// ------------------------------------------------------------------------------------------- launchers
+// All launchers enqueue on `st` and return PI_OK / error.  Shapes are validated by the callers in pi_capi.cu.
+
+int launch_quantize_q4_0(const float * x, void * q4, int64_t nrows, int64_t ncols, cudaStream_t st);
+int launch_q4_0_repack(const void * src, void * dst, int64_t nrows, int64_t ncols, cudaStream_t st);
+int launch_dequantize_q4_0(const void * q4p, float * y, int64_t nrows, int64_t ncols, cudaStream_t st);
+int launch_quantize_q8_0_ggml(const float * x, void * q8, int64_t nrows, int64_t ncols, cudaStream_t st);
+
+// x F32 [T, n] (row stride x_stride) -> activation planes for `wtype` weights
+int launch_convert_act(int wtype, const float * x, int64_t x_stride, int64_t n, int T, ActBuf out, cudaStream_t st);
+
+struct GemvArgs {
+    int wtype = PI_TYPE_F16;
+    const void * W = nullptr;          // [nrows, ncols]
+    int64_t nrows = 0, ncols = 0;
+    Act x;                             // T tokens
+    int T = 1;
+    // row selection: dense when list == nullptr
+    const int32_t * list = nullptr;    // compacted LOCAL row numbers (sorted)
+    const int32_t * count = nullptr;   // number of entries of list (device)
+    const int32_t * bucket = nullptr;  // local row -> global neuron id (nullptr: identity)
+    const float * idx = nullptr;       // predictor logits [T, idx_stride] by global id: per-token predicate
+    int64_t idx_stride = 0;
+    float threshold = 0.f;
+    // epilogue
+    const float * bias = nullptr;      // by destination row
+    int relu = 0;
+    float * dst = nullptr;             // F32 [T, dst_stride]; destination row = global id (sparse) or row (dense)
+    int64_t dst_stride = 0;
+    __half * dst16 = nullptr;          // optional FP16 copy of the result [T, dst_stride] (feeds an F16 mat-vec)
+    // second matrix sharing the row selection (gate with up): dst = relu(W2 row . x) * (W row . x)
+    const void * W2 = nullptr;
+};
+int launch_gemv(const GemvArgs & a, cudaStream_t st);
+
+// predictor logits -> compacted list of LOCAL rows active for >= 1 token; also writes zeros (or relu(bias)) into
+// h_init [T, h_stride] for rows that are inactive for a token when h_init != nullptr
+struct CompactArgs {
+    const float * idx = nullptr; int64_t idx_stride = 0; int T = 1; float threshold = 0.f;
+    int64_t n_local = 0; const int32_t * bucket = nullptr;
+    int32_t * list = nullptr; int32_t * count = nullptr;
+    float * zero_dst = nullptr; int64_t zero_stride = 0;   // dense [T, zero_stride] vector: entries of rows inactive for a token are
+    const float * fill_bias = nullptr; int fill_relu = 0;  // set to 0, or to (relu of) fill_bias[g] (what the graph's bias add leaves there)
+    uint32_t * masks = nullptr;        // scratch: one word per 32 local rows
+    unsigned int * ticket = nullptr;   // scratch: one word, must be 0 on entry, is 0 again on exit
+};
+int launch_compact(const CompactArgs & a, cudaStream_t st);
+
+struct AxpyArgs {
+    int wtype = PI_TYPE_F16;
+    const void * Wt = nullptr; int64_t nrows = 0, ncols = 0;
+    const float * h = nullptr; int64_t h_stride = 0; int T = 1;       // by global id
+    const int32_t * list = nullptr; const int32_t * count = nullptr; const int32_t * bucket = nullptr;
+    const float * idx = nullptr; int64_t idx_stride = 0; float threshold = 0.f;
+    // Q4_0: coefficient planes made by launch_neuron_q8 (int8 by global id, float scale per 32-neuron block)
+    const int8_t * cq = nullptr; const float * cd = nullptr; int64_t c_stride = 0;
+    float * partial = nullptr; int n_groups = 0;                      // [n_groups, T, ncols]
+};
+int axpy_groups(int wtype, int64_t ncols, int T);                     // row groups the launcher will use
+int launch_axpy(const AxpyArgs & a, cudaStream_t st);
+// h F32 [T, stride] -> Q8_0 over 32-neuron blocks: cq int8 [T, stride], cd float [T, stride/32]
+int launch_neuron_q8(const float * h, int64_t stride, int64_t n, int T, int8_t * cq, float * cd, cudaStream_t st);
+
+// sum partial [n_groups, T, n] in group order (+ residual + bias) -> dst [T, n]
+int launch_reduce_partials(const float * partial, int n_groups, int T, int64_t n, const float * residual,
+                           const float * bias, float * dst, cudaStream_t st);
+
+struct NormArgs {
+    const float * x = nullptr; int T = 1; int64_t n = 0; int rms = 1; float eps = 0.f;
+    const float * w = nullptr; const float * b = nullptr;
+    // optional prologue: the vector to normalise is sum_j partial[j, t, :] (+ in_bias) (+ residual[t, :]) instead of x,
+    // and is written to x_out (the new residual stream)
+    const float * partial = nullptr; int n_groups = 0; const float * residual = nullptr; const float * in_bias = nullptr;
+    float * x_out = nullptr;
+    float * y = nullptr;               // optional F32 output
+    int act_type = 0; ActBuf act;      // optional activation planes of the normalised vector (0: none, else PI_TYPE_*)
+    int act2_type = 0; ActBuf act2; int act2_src = 1;   // second set of planes, of the input (src 0) or the output (src 1)
+};
+int launch_norm(const NormArgs & a, cudaStream_t st);
+
+int launch_rope(float * x, int T, int n_heads, int head_dim, const int32_t * pos, const float * cs, int neox, cudaStream_t st);
+
+struct AttnArgs {
+    const float * q = nullptr; const float * k = nullptr; const float * v = nullptr;
+    __half * k_cache = nullptr; __half * v_cache = nullptr;
+    const int32_t * seq = nullptr; const int32_t * pos = nullptr;
+    int T = 1, n_head = 0, n_head_kv = 0, head_dim = 0, n_ctx = 0;
+    const float * cs = nullptr; int neox = 0;          // fused RoPE of q and k from the angle table (nullptr: already rotated)
+    float * out = nullptr;                             // optional F32 [T, n_head*head_dim]
+    int out_act_type = 0; ActBuf out_act;              // optional activation planes of the output
+};
+int launch_attention(const AttnArgs & a, cudaStream_t st);
+
+// ------------------------------------------------------------------------------------ device primitives
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint4 ldg_stream(const void * p) {     // read-once weights: bypass L1 allocation
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream8(const void * p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float2 h2f(uint32_t u) {               // two packed halves -> floats
+    __half2 h = *reinterpret_cast<__half2 *>(&u);
+    return __half22float2(h);
+}
+__device__ __forceinline__ float round_f16(float x) { return __half2float(__float2half_rn(x)); }
+
+#endif  // __CUDACC__
+
+}  // namespace pi

@@ -1,0 +1,378 @@
+// Dense decode nodes between the sparse operators: normalisation (with the residual / partial-sum reduction that
+// precedes it fused in), RoPE, KV store and one-token attention.  All are latency-bound at batch 1; they exist to
+// keep the residual stream on the device and to hand the next mat-vec its input already in FP16 / Q8_0 form.
+#include "pi_common.cuh"
+
+namespace pi {
+
+static constexpr int QK = 32;
+
+// ------------------------------------------------------------------------------------------------
+// llm_build_norm (llama.cpp:4420-4450) = ggml_rms_norm | ggml_norm, * weight, + bias, with the CPU path's numerics
+// (ggml.c:9169-9284): squares / deviations are formed in float, summed in double, scale = 1/sqrtf(mean + eps).
+// Optional prologue: v = sum_j partial[j] (+ in_bias) (+ residual), written back as the new residual stream.
+// Optional epilogue: the normalised vector as FP16 or Q8_0 planes for the mat-vec that consumes it.
+// One CTA per token; a thread owns up to NORM_CHUNKS groups of 8 consecutive values.
+static constexpr int NORM_CHUNKS = 2;
+
+struct NormP {
+    const float * x; int64_t n; int rms; float eps; const float * w; const float * b;
+    const float * partial; int n_groups; int T; const float * residual; const float * in_bias; float * x_out;
+    float * y; int act_type; ActBuf act; int act2_type; ActBuf act2; int act2_src;
+};
+
+__device__ __forceinline__ double block_sum_d(double v, double * s_red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum_d(v);
+    __syncthreads();                       // s_red may still be read from a previous call
+    if (lane == 0) s_red[wid] = v;
+    __syncthreads();
+    double t = 0.0;
+    for (int i = 0; i < nw; i++) t += s_red[i];
+    return t;
+}
+
+// Emit 8 consecutive values (chunk index c8 = first column / 8) of token t as activation planes.
+// Must be called by every lane of a warp (it shuffles); `valid` gates the stores.  With n % 32 == 0 the 4 lanes that
+// share a Q8 block are valid or invalid together.
+__device__ __forceinline__ void emit_act8(int type, const ActBuf & a, int t, int64_t n, int c8, const float (&v)[8], bool valid) {
+    if (type == PI_TYPE_F16) {
+        if (!valid) return;
+        __half2 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) h[j] = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+        *reinterpret_cast<uint4 *>(a.h16 + (size_t)t * n + (size_t)c8 * 8) = *reinterpret_cast<uint4 *>(h);
+    } else if (type == PI_TYPE_Q4_0) {
+        // 4 consecutive threads (lanes 4k..4k+3) hold one block of 32 values
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float d  = amax / 127.0f;
+        const float id = amax != 0.0f ? 127.0f / amax : 0.0f;
+        int q[8], s = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) { q[j] = __float2int_rn(v[j] * id); s += q[j]; }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        const int nb = (int)(n / QK);
+        const size_t blk = (size_t)t * nb + (c8 >> 2);
+        const int part = c8 & 3;                                  // which 8 of the 32
+        uint2 packed;
+        packed.x = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+        packed.y = (uint32_t)(q[4] & 0xFF) | ((uint32_t)(q[5] & 0xFF) << 8) | ((uint32_t)(q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+        if (!valid) return;
+        uint2 * plane = reinterpret_cast<uint2 *>(part < 2 ? a.lo + blk : a.hi + blk);
+        plane[part & 1] = packed;
+        if (part == 0) { a.d[blk] = __half2float(__float2half_rn(d)); a.s[blk] = s; }
+    }
+}
+
+__global__ void __launch_bounds__(1024) k_norm(const NormP p) {
+    __shared__ double s_red[32];
+    const int t = blockIdx.x;
+    const int64_t n = p.n;
+    const size_t tn = (size_t)p.T * n;
+    float v[NORM_CHUNKS][8];
+    bool ok[NORM_CHUNKS];
+#pragma unroll
+    for (int k = 0; k < NORM_CHUNKS; k++) {
+        const int64_t c = ((int64_t)k * blockDim.x + threadIdx.x) * 8;
+        ok[k] = c < n;
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[k][j] = 0.f;
+        const size_t o = (size_t)t * n + c;
+        if (ok[k]) {
+        if (p.partial) {
+            for (int g = 0; g < p.n_groups; g++) {
+                const float4 a = *reinterpret_cast<const float4 *>(p.partial + (size_t)g * tn + o);
+                const float4 b = *reinterpret_cast<const float4 *>(p.partial + (size_t)g * tn + o + 4);
+                v[k][0] += a.x; v[k][1] += a.y; v[k][2] += a.z; v[k][3] += a.w;
+                v[k][4] += b.x; v[k][5] += b.y; v[k][6] += b.z; v[k][7] += b.w;
+            }
+        } else {
+            const float4 a = *reinterpret_cast<const float4 *>(p.x + o);
+            const float4 b = *reinterpret_cast<const float4 *>(p.x + o + 4);
+            v[k][0] = a.x; v[k][1] = a.y; v[k][2] = a.z; v[k][3] = a.w;
+            v[k][4] = b.x; v[k][5] = b.y; v[k][6] = b.z; v[k][7] = b.w;
+        }
+        if (p.in_bias) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[k][j] += p.in_bias[c + j];
+        }
+        if (p.residual) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[k][j] += p.residual[o + j];
+        }
+        if (p.x_out) {
+            *reinterpret_cast<float4 *>(p.x_out + o)     = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+            *reinterpret_cast<float4 *>(p.x_out + o + 4) = make_float4(v[k][4], v[k][5], v[k][6], v[k][7]);
+        }
+        }
+        if (p.act2_type && p.act2_src == 0) emit_act8(p.act2_type, p.act2, t, n, (int)(c / 8), v[k], ok[k]);
+    }
+
+    float scale, mean = 0.f;
+    if (p.rms) {
+        double s = 0.0;
+#pragma unroll
+        for (int k = 0; k < NORM_CHUNKS; k++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) s += (double)(v[k][j] * v[k][j]);
+        s = block_sum_d(s, s_red);
+        const float ms = (float)(s / (double)n);
+        scale = 1.0f / sqrtf(ms + p.eps);
+    } else {
+        double s = 0.0;
+#pragma unroll
+        for (int k = 0; k < NORM_CHUNKS; k++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) s += (double)v[k][j];           // slots beyond n hold 0
+        s = block_sum_d(s, s_red);
+        mean = (float)(s / (double)n);
+        double s2 = 0.0;
+#pragma unroll
+        for (int k = 0; k < NORM_CHUNKS; k++) {
+            if (!ok[k]) continue;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { v[k][j] = v[k][j] - mean; s2 += (double)(v[k][j] * v[k][j]); }
+        }
+        s2 = block_sum_d(s2, s_red);
+        const float var = (float)(s2 / (double)n);
+        scale = 1.0f / sqrtf(var + p.eps);
+    }
+#pragma unroll
+    for (int k = 0; k < NORM_CHUNKS; k++) {
+        const int64_t c = ((int64_t)k * blockDim.x + threadIdx.x) * 8;
+        float y[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float r = __fmul_rn(v[k][j], scale);                       // separate roundings, as separate graph nodes give
+            if (ok[k] && p.w) r = __fmul_rn(r, p.w[c + j]);
+            if (ok[k] && p.b) r = __fadd_rn(r, p.b[c + j]);
+            y[j] = r;
+        }
+        if (ok[k] && p.y) {
+            float * o = p.y + (size_t)t * n + c;
+            *reinterpret_cast<float4 *>(o)     = make_float4(y[0], y[1], y[2], y[3]);
+            *reinterpret_cast<float4 *>(o + 4) = make_float4(y[4], y[5], y[6], y[7]);
+        }
+        if (p.act_type) emit_act8(p.act_type, p.act, t, n, (int)(c / 8), y, ok[k]);
+        if (p.act2_type && p.act2_src == 1) emit_act8(p.act2_type, p.act2, t, n, (int)(c / 8), y, ok[k]);
+    }
+}
+
+int launch_norm(const NormArgs & a, cudaStream_t st) {
+    if (a.T <= 0) return PI_OK;
+    PI_REQUIRE(a.n % 8 == 0 && a.n <= (int64_t)NORM_CHUNKS * 1024 * 8, "norm: n=%lld must be a multiple of 8 and <= %d",
+               (long long)a.n, NORM_CHUNKS * 1024 * 8);
+    NormP p;
+    p.x = a.x; p.n = a.n; p.rms = a.rms; p.eps = a.eps; p.w = a.w; p.b = a.b;
+    p.partial = a.partial; p.n_groups = a.n_groups; p.T = a.T; p.residual = a.residual; p.in_bias = a.in_bias; p.x_out = a.x_out;
+    p.y = a.y; p.act_type = a.act_type; p.act = a.act; p.act2_type = a.act2_type; p.act2 = a.act2; p.act2_src = a.act2_src;
+    int threads = (int)((a.n / 8 + NORM_CHUNKS - 1) / NORM_CHUNKS);
+    threads = min(1024, max(32, (threads + 31) / 32 * 32));
+    k_norm<<<a.T, threads, 0, st>>>(p);
+    PI_LAUNCH_CHECK("k_norm");
+    return PI_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// ggml_rope_custom, modes 0 and 2 (ggml.c:11163-11325), angles from a host-built table so that device and CPU path
+// rotate by the same float cos / sin.  Products and sums are rounded separately, as the CPU build does.
+__device__ __forceinline__ void rope_pair(float x0, float x1, float c, float s, float & o0, float & o1) {
+    o0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+    o1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+}
+
+__global__ void k_rope(float * __restrict__ x, int n_heads, int head_dim, const int32_t * __restrict__ pos,
+                       const float * __restrict__ cs, int neox) {
+    const int t = blockIdx.y;
+    const int half = head_dim / 2;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;           // pair index over heads
+    if (i >= n_heads * half) return;
+    const int h = i / half, k = i - h * half;
+    const float2 a = reinterpret_cast<const float2 *>(cs)[(size_t)pos[t] * half + k];
+    float * v = x + ((size_t)t * n_heads + h) * head_dim;
+    const int i0 = neox ? k : 2 * k, i1 = neox ? k + half : 2 * k + 1;
+    float o0, o1;
+    rope_pair(v[i0], v[i1], a.x, a.y, o0, o1);
+    v[i0] = o0; v[i1] = o1;
+}
+
+int launch_rope(float * x, int T, int n_heads, int head_dim, const int32_t * pos, const float * cs, int neox, cudaStream_t st) {
+    if (T <= 0) return PI_OK;
+    const int pairs = n_heads * head_dim / 2;
+    const dim3 grid((pairs + 255) / 256, T);
+    k_rope<<<grid, 256, 0, st>>>(x, n_heads, head_dim, pos, cs, neox);
+    PI_LAUNCH_CHECK("k_rope");
+    return PI_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// llm_build_kv_store + llm_build_kqv for one new token per sequence (llama.cpp:4383-4418, 4764-4850).
+// One CTA per (query head, token).  Optional fused RoPE of q and k (cs != nullptr).  The first query head of each KV
+// group stores the new K (after RoPE) and V as FP16; every head reads the new token's K/V from the F32 inputs
+// (rounded to FP16, exactly what was stored) so no CTA depends on another one's store.
+// CPU-path numerics: q and the probabilities are rounded to FP16 before the dot products; exp() goes through FP16
+// in and out (the reference uses a table of FP16(expf(FP16))); the normaliser is summed in double.
+static constexpr int ATTN_THREADS = 256;
+
+struct AttnP {
+    const float * q; const float * k; const float * v; __half * k_cache; __half * v_cache;
+    const int32_t * seq; const int32_t * pos; int n_head, n_head_kv, hd, n_ctx;
+    const float * cs; int neox; int sc_floats;
+    float * out; ActBuf out_act; int out_act_type;
+};
+
+__global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ double s_red[32];
+    __shared__ float s_max[ATTN_THREADS / 32];
+    const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int hd = p.hd, half = hd / 2;
+    const int group = p.n_head / p.n_head_kv, hk = h / group;
+    const int dkv = p.n_head_kv * hd;
+    const int pos = p.pos[t];
+    const int sq = p.seq ? p.seq[t] : 0;
+    if (pos < 0 || pos >= p.n_ctx) return;                       // never index the cache out of range
+
+    float *  sc  = reinterpret_cast<float *>(smem_raw);          // scores, then exp values, then the output slices
+    __half * q16 = reinterpret_cast<__half *>(sc + p.sc_floats); // [hd]   (sc_floats = max(n_ctx, slices*hd))
+    __half * k16 = q16 + hd;                                     // [hd] the new token's K
+    __half * v16 = k16 + hd;                                     // [hd] the new token's V
+    __half * p16 = v16 + hd;                                     // [n_ctx] probabilities in FP16
+
+    const float * qh = p.q + ((size_t)t * p.n_head + h) * hd;
+    const float * kh = p.k + ((size_t)t * p.n_head_kv + hk) * hd;
+    const float * vh = p.v + ((size_t)t * p.n_head_kv + hk) * hd;
+    for (int e = tid; e < hd; e += ATTN_THREADS) v16[e] = __float2half_rn(vh[e]);
+    if (p.cs) {
+        for (int k = tid; k < half; k += ATTN_THREADS) {
+            const float2 a = reinterpret_cast<const float2 *>(p.cs)[(size_t)pos * half + k];
+            const int i0 = p.neox ? k : 2 * k, i1 = p.neox ? k + half : 2 * k + 1;
+            float o0, o1;
+            rope_pair(qh[i0], qh[i1], a.x, a.y, o0, o1);
+            q16[i0] = __float2half_rn(o0); q16[i1] = __float2half_rn(o1);
+            rope_pair(kh[i0], kh[i1], a.x, a.y, o0, o1);
+            k16[i0] = __float2half_rn(o0); k16[i1] = __float2half_rn(o1);
+        }
+    } else {
+        for (int e = tid; e < hd; e += ATTN_THREADS) { q16[e] = __float2half_rn(qh[e]); k16[e] = __float2half_rn(kh[e]); }
+    }
+    __syncthreads();
+    __half * kc = p.k_cache + (size_t)sq * p.n_ctx * dkv + (size_t)hk * hd;
+    __half * vc = p.v_cache + (size_t)sq * p.n_ctx * dkv + (size_t)hk * hd;
+    if (h % group == 0) {
+        for (int e = tid; e < hd; e += ATTN_THREADS) {
+            kc[(size_t)pos * dkv + e] = k16[e];
+            vc[(size_t)pos * dkv + e] = v16[e];
+        }
+    }
+
+    // ---- scores: one warp per position, lanes split head_dim
+    const float scale = 1.0f / sqrtf((float)hd);
+    float mx = -INFINITY;
+    for (int j = wid; j <= pos; j += ATTN_THREADS / 32) {
+        const __half * kr = j == pos ? k16 : kc + (size_t)j * dkv;
+        float a = 0.f;
+        for (int e = lane * 2; e < hd; e += 64) {
+            const float2 kk = __half22float2(*reinterpret_cast<const __half2 *>(kr + e));
+            const float2 qq = __half22float2(*reinterpret_cast<const __half2 *>(q16 + e));
+            a = fmaf(kk.x, qq.x, a); a = fmaf(kk.y, qq.y, a);
+        }
+        a = warp_sum(a) * scale;
+        if (lane == 0) sc[j] = a;
+        mx = fmaxf(mx, a);
+    }
+    if (lane == 0) s_max[wid] = mx;
+    __syncthreads();
+    mx = s_max[0];
+#pragma unroll
+    for (int i = 1; i < ATTN_THREADS / 32; i++) mx = fmaxf(mx, s_max[i]);
+
+    // ---- softmax (ggml.c:10708-10777)
+    double part = 0.0;
+    for (int j = tid; j <= pos; j += ATTN_THREADS) {
+        const float arg = __half2float(__float2half_rn(sc[j] - mx));
+        const float e = __half2float(__float2half_rn(expf(arg)));
+        sc[j] = e;
+        part += (double)e;
+    }
+    {
+        part = warp_sum_d(part);
+        if (lane == 0) s_red[wid] = part;
+        __syncthreads();
+        double tot = 0.0;
+        for (int i = 0; i < ATTN_THREADS / 32; i++) tot += s_red[i];
+        const float inv = (float)(1.0 / tot);
+        for (int j = tid; j <= pos; j += ATTN_THREADS) p16[j] = __float2half_rn(sc[j] * inv);
+    }
+    __syncthreads();
+
+    // ---- out[e] = sum_j p_j V[j, e]: threads split (e pairs) x (position slices), slices reduced through smem
+    const int pairs = half;                                        // hd/2 half2 columns
+    const int slices = ATTN_THREADS / pairs > 0 ? ATTN_THREADS / pairs : 1;
+    float * red = sc;                                              // scores are dead: reuse as [slices][hd]
+    float ax = 0.f, ay = 0.f;
+    const int e2 = tid % pairs, sl = tid / pairs;
+    if (sl < slices) {
+        for (int j = sl; j <= pos; j += slices) {
+            const __half * vr = j == pos ? v16 : vc + (size_t)j * dkv;
+            const float2 vv = __half22float2(*reinterpret_cast<const __half2 *>(vr + 2 * e2));
+            const float pj = __half2float(p16[j]);
+            ax = fmaf(pj, vv.x, ax); ay = fmaf(pj, vv.y, ay);
+        }
+    }
+    __syncthreads();                                               // everyone is done reading sc as probabilities
+    if (sl < slices) { red[sl * hd + 2 * e2] = ax; red[sl * hd + 2 * e2 + 1] = ay; }
+    __syncthreads();
+    for (int e = tid; e < hd; e += ATTN_THREADS) {
+        float o = 0.f;
+        for (int s = 0; s < slices; s++) o += red[s * hd + e];
+        if (p.out) p.out[((size_t)t * p.n_head + h) * hd + e] = o;
+        red[e] = o;                                                // slice 0 row now holds the final value
+    }
+    if (p.out_act_type) {
+        __syncthreads();
+        // hd % 32 == 0: this head owns whole Q8 blocks of the concatenated [n_head*hd] vector
+        const int64_t n = (int64_t)p.n_head * hd;
+        if (wid == 0) {                                             // hd/8 <= 32 chunks: one per lane of warp 0
+            const bool valid = lane < hd / 8;
+            float y[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) y[j] = valid ? red[lane * 8 + j] : 0.f;
+            emit_act8(p.out_act_type, p.out_act, t, n, h * (hd / 8) + lane, y, valid);
+        }
+    }
+}
+
+int launch_attention(const AttnArgs & a, cudaStream_t st) {
+    if (a.T <= 0) return PI_OK;
+    PI_REQUIRE(a.head_dim % 32 == 0 && a.head_dim <= 256, "attention: head_dim=%d must be a multiple of 32, <= 256", a.head_dim);
+    PI_REQUIRE(a.n_head % a.n_head_kv == 0, "attention: n_head %% n_head_kv != 0");
+    AttnP p;
+    p.q = a.q; p.k = a.k; p.v = a.v; p.k_cache = a.k_cache; p.v_cache = a.v_cache; p.seq = a.seq; p.pos = a.pos;
+    p.n_head = a.n_head; p.n_head_kv = a.n_head_kv; p.hd = a.head_dim; p.n_ctx = a.n_ctx;
+    p.cs = a.cs; p.neox = a.neox; p.out = a.out; p.out_act = a.out_act; p.out_act_type = a.out_act_type;
+    // sc must hold max(n_ctx, slices*hd) floats
+    const int slices = ATTN_THREADS / (a.head_dim / 2) > 0 ? ATTN_THREADS / (a.head_dim / 2) : 1;
+    const size_t sc_floats = (size_t)max(a.n_ctx, slices * a.head_dim);
+    const size_t smem = sc_floats * 4 + (size_t)3 * a.head_dim * 2 + (size_t)a.n_ctx * 2 + 16;
+    p.sc_floats = (int)sc_floats;
+    static bool attr_set[16] = {false};
+    int dev = 0;
+    PI_CUDA(cudaGetDevice(&dev));
+    if (smem > 48 * 1024 && !(dev < 16 && attr_set[dev])) {
+        PI_CUDA(cudaFuncSetAttribute(k_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        if (dev < 16) attr_set[dev] = true;
+    }
+    PI_REQUIRE(smem <= 200 * 1024, "attention: n_ctx=%d needs %zu bytes of shared memory", a.n_ctx, smem);
+    const dim3 grid(a.n_head, a.T);
+    k_attention<<<grid, ATTN_THREADS, smem, st>>>(p);
+    PI_LAUNCH_CHECK("k_attention");
+    return PI_OK;
+}
+
+}  // namespace pi

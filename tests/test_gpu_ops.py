@@ -1,0 +1,202 @@
+"""Parity of the CUDA operators (through the C ABI) with the CPU checker and the reference's golden outputs.
+
+Tolerances: quantisers and index lists bit-exact; mat-vec style results within 2e-4 absolute of the
+reference (its outputs here are O(0.1-1); the stated bars are 2e-2 for FP16 and 5e-2 for Q4_0 logits),
+the only difference being the order of FP32 additions.
+"""
+import numpy as np
+import pytest
+
+import make_golden as mg
+from powerinfer_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+ATOL = 2e-4
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from powerinfer_b200 import ggml_ops
+    return ggml_ops
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_q4_0_quantiser_bit_exact(ops, oracle, golden_ops):
+    xs = np.random.default_rng(7).standard_normal((3, 512), dtype=np.float32)
+    q = ops.quantize_q4_0(dev(xs * np.float32(0.02))).cpu().numpy()
+    assert np.array_equal(q, golden_ops["q4_0"])
+    q8 = ops.quantize_q8_0(dev(xs)).cpu().numpy()
+    assert np.array_equal(q8, golden_ops["q8_0"])
+    # edge cases: all-zero block, ties in magnitude, huge and tiny values
+    e = np.zeros((4, 256), np.float32)
+    e[1, :32] = 1.0
+    e[1, 5] = -1.0
+    e[2] = np.random.default_rng(1).standard_normal(256).astype(np.float32) * 1e-30
+    e[3] = np.random.default_rng(2).standard_normal(256).astype(np.float32) * 6e4
+    assert np.array_equal(ops.quantize_q4_0(dev(e)).cpu().numpy(), oracle.quantize_q4_0(e))
+    assert np.array_equal(ops.quantize_q8_0(dev(e)).cpu().numpy(), oracle.quantize_q8_0(e))
+
+
+def test_q4_0_repack_round_trip(ops, oracle):
+    w = (np.random.default_rng(3).standard_normal((64, 512)) * 0.02).astype(np.float32)
+    q = synth.quantize_q4_0(w)
+    W = ops.upload_weight(q, synth.Q4_0, 64, 512)
+    deq = ops.dequantize(W).cpu().numpy()
+    assert np.array_equal(deq.reshape(-1), oracle.dequantize_q4_0(q.reshape(-1), w.size))
+
+
+@pytest.mark.parametrize("name", sorted(mg.op_cases()))
+def test_sparse_ops_vs_reference_golden(ops, golden_ops, name):
+    c = mg.op_cases()[name]
+    x, W, Wt, idx = mg.op_inputs(c)
+    Wd = ops.upload_weight(W, c["wtype"], c["F"], c["d"])
+    Wtd = ops.upload_weight(Wt, c["wtype"], c["F"], c["d"])
+    up = ops.ggml_mul_mat_idx(Wd, dev(x), dev(idx))
+    ref_up = golden_ops[name + ".up"]
+    assert np.abs(up.cpu().numpy() - ref_up).max() <= ATOL
+    assert np.all(up.cpu().numpy()[idx < 0] == 0.0)                      # inactive rows are exactly zero
+    h = np.maximum(ref_up, 0)
+    down = ops.ggml_axpy(Wtd, dev(h), dev(idx)).cpu().numpy()
+    assert np.abs(down - golden_ops[name + ".down"]).max() <= ATOL
+    down2 = ops.ggml_axpy(Wtd, dev(h), dev(idx)).cpu().numpy()
+    assert np.array_equal(down, down2)                                  # fixed summation order
+    dense = ops.ggml_mul_mat(Wd, dev(x)).cpu().numpy()
+    assert np.abs(dense - golden_ops[name + ".dense"]).max() <= ATOL
+
+
+@pytest.mark.parametrize("wtype", [synth.F16, synth.Q4_0])
+@pytest.mark.parametrize("T", [1, 3, 8, 16])
+def test_sparse_ops_vs_oracle_batches_and_buckets(ops, oracle, wtype, T):
+    """Union list across the batch with a per-token predicate, and the gpu_bucket (row subset) form."""
+    rng = np.random.default_rng(100 * wtype + T)
+    d, F = 512, 2048
+    x = rng.standard_normal((T, d), dtype=np.float32)
+    Wf = rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.02)
+    Wtf = rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.02)
+    W = synth.quantize_q4_0(Wf) if wtype == synth.Q4_0 else Wf.astype(np.float16)
+    Wt = synth.quantize_q4_0(Wtf) if wtype == synth.Q4_0 else Wtf.astype(np.float16)
+    idx = (rng.random((T, F)) - 0.85).astype(np.float32)
+    ref_up = oracle.mul_mat_idx(wtype, W, F, d, x, idx)
+    h = np.maximum(ref_up, 0)
+    ref_down = oracle.axpy(wtype, Wt, F, d, h, idx, np.zeros(F, np.int32))
+    Wd, Wtd = ops.upload_weight(W, wtype, F, d), ops.upload_weight(Wt, wtype, F, d)
+    up = ops.ggml_mul_mat_idx(Wd, dev(x), dev(idx)).cpu().numpy()
+    assert np.abs(up - ref_up).max() <= ATOL
+    down = ops.ggml_axpy(Wtd, dev(h), dev(idx)).cpu().numpy()
+    assert np.abs(down - ref_down).max() <= ATOL
+    # bucket: this device holds whole 32-neuron blocks 0, 2, 4, ...; the CPU op sees the complement as gpu_idx == 1
+    blocks = np.arange(0, F // 32, 2)
+    bucket = (blocks[:, None] * 32 + np.arange(32)[None, :]).reshape(-1).astype(np.int32)
+    rb = W.shape[1] if wtype == synth.Q4_0 else None
+    Wb = W[bucket]
+    Wtb = Wt[bucket]
+    Wbd, Wtbd = ops.upload_weight(Wb, wtype, len(bucket), d), ops.upload_weight(Wtb, wtype, len(bucket), d)
+    gpu_idx = np.ones(F, np.int32)
+    gpu_idx[bucket] = 0
+    ref_up_b = oracle.mul_mat_idx(wtype, W, F, d, x, idx, gpu_idx)
+    up_b = ops.ggml_mul_mat_idx(Wbd, dev(x), dev(idx), dev(bucket), result_ne0=F).cpu().numpy()
+    assert np.abs(up_b - ref_up_b).max() <= ATOL
+    ref_down_b = oracle.axpy(wtype, Wt, F, d, h, idx, gpu_idx)
+    down_b = ops.ggml_axpy(Wtbd, dev(h), dev(idx), dev(bucket)).cpu().numpy()
+    assert np.abs(down_b - ref_down_b).max() <= ATOL
+
+
+def test_predictor_and_active_list(ops, oracle):
+    spec = synth.ModelSpec(n_layer=1, d=512, n_ff=4096, rank=128, firing=0.1, seed=5)
+    t = synth.build_model(spec)
+    rng = np.random.default_rng(0)
+    for T in (1, 4):
+        p = rng.standard_normal((T, spec.d), dtype=np.float32)
+        hid = np.maximum(oracle.mul_mat(synth.F16, t["blk.0.fc1.weight"], spec.rank, spec.d, p), 0)
+        ref = oracle.mul_mat(synth.F16, t["blk.0.fc2.weight"], spec.n_ff, spec.rank, hid)
+        fc1 = ops.upload_weight(t["blk.0.fc1.weight"], synth.F16, spec.rank, spec.d)
+        fc2 = ops.upload_weight(t["blk.0.fc2.weight"], synth.F16, spec.n_ff, spec.rank)
+        idx = ops.predictor(fc1, fc2, dev(p))
+        got = idx.cpu().numpy()
+        assert np.abs(got - ref).max() <= 1e-4
+        # index sets: bit-exact except neurons whose logit lies within 1e-3 of the threshold
+        sure = np.abs(ref) > 1e-3
+        assert np.array_equal((got >= 0)[sure], (ref >= 0)[sure])
+        lst, cnt = ops.active_list(idx)
+        n = int(cnt.item())
+        want = np.nonzero((got >= 0).any(axis=0))[0]
+        assert n == len(want) and np.array_equal(lst[:n].cpu().numpy(), want)
+
+
+def test_active_list_edges(ops):
+    for F in (32, 1000, 1280, 49152):
+        for kind in ("empty", "full", "one", "ragged"):
+            idx = -np.ones((1, F), np.float32)
+            if kind == "full":
+                idx[:] = 1
+            elif kind == "one":
+                idx[0, F - 1] = 0.0
+            elif kind == "ragged":
+                idx[0, ::7] = 0.5
+            lst, cnt = ops.active_list(dev(idx))
+            want = np.nonzero(idx[0] >= 0)[0]
+            assert int(cnt.item()) == len(want)
+            assert np.array_equal(lst[:len(want)].cpu().numpy(), want)
+
+
+def test_norms_rope_bit_exact(ops, golden_ops):
+    xs = np.random.default_rng(7).standard_normal((3, 512), dtype=np.float32)
+    assert np.array_equal(ops.ggml_rms_norm(dev(xs), 1e-5).cpu().numpy(), golden_ops["rms_norm"])
+    got = ops.ggml_norm(dev(xs), 1e-5).cpu().numpy()
+    assert np.abs(got - golden_ops["norm"]).max() <= 1e-6
+    tab = ops.rope_table(320, 128, 10000.0)
+    tab64 = ops.rope_table(320, 64, 10000.0)
+    for pos in (0, 1, 37, 300):
+        p = torch.tensor([pos], dtype=torch.int32, device="cuda")
+        y = ops.ggml_rope_custom(dev(xs[0].reshape(1, 4, 128)), p, 128, 0, tab).cpu().numpy().reshape(4, 128)
+        assert np.array_equal(y, golden_ops[f"rope_{pos}"])
+        y = ops.ggml_rope_custom(dev(xs[0].reshape(1, 8, 64)), p, 64, 2, tab64).cpu().numpy().reshape(8, 64)
+        assert np.array_equal(y, golden_ops[f"rope_neox_{pos}"])
+
+
+def test_norm_weight_bias_and_wide_rows(ops, oracle):
+    rng = np.random.default_rng(9)
+    for n in (256, 4096, 8192, 12288):
+        x = rng.standard_normal((2, n), dtype=np.float32)
+        w = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        b = (0.1 * rng.standard_normal(n)).astype(np.float32)
+        ref = oracle.rms_norm(x, 1e-5) * w
+        assert np.abs(ops.ggml_rms_norm(dev(x), 1e-5, dev(w)).cpu().numpy() - ref).max() <= 1e-6
+        ref = oracle.norm(x, 1e-5) * w + b
+        assert np.abs(ops.ggml_norm(dev(x), 1e-5, dev(w), dev(b)).cpu().numpy() - ref).max() <= 2e-6
+
+
+@pytest.mark.parametrize("n_head,n_head_kv,hd", [(4, 4, 64), (8, 2, 128), (8, 8, 32)])
+def test_attention_decode_vs_oracle(ops, oracle, n_head, n_head_kv, hd):
+    """Feed 40 positions one by one; compare with the CPU restatement of llm_build_kqv (same FP16 roundings)."""
+    rng = np.random.default_rng(n_head * 100 + hd)
+    n_ctx, dkv, d = 64, n_head_kv * hd, n_head * hd
+    kc = torch.zeros(1, n_ctx, dkv, dtype=torch.float16, device="cuda")
+    vc = torch.zeros(1, n_ctx, dkv, dtype=torch.float16, device="cuda")
+    K = np.zeros((n_ctx, dkv), np.float16)
+    V = np.zeros((n_ctx, dkv), np.float16)
+    group = n_head // n_head_kv
+    for pos in range(40):
+        q = rng.standard_normal((1, d), dtype=np.float32)
+        k = rng.standard_normal((1, dkv), dtype=np.float32)
+        v = rng.standard_normal((1, dkv), dtype=np.float32)
+        out = ops.attention_decode(dev(q), dev(k), dev(v), kc, vc, torch.tensor([pos], dtype=torch.int32, device="cuda"),
+                                   n_head, n_head_kv).cpu().numpy()[0]
+        K[pos], V[pos] = k[0].astype(np.float16), v[0].astype(np.float16)
+        ref = np.zeros(d, np.float32)
+        scale = np.float32(1.0) / np.sqrt(np.float32(hd))
+        for h in range(n_head):
+            hk = h // group
+            q16 = q[0, h * hd:(h + 1) * hd].astype(np.float16).astype(np.float32)
+            s = (K[:pos + 1, hk * hd:(hk + 1) * hd].astype(np.float32) @ q16) * scale
+            p = oracle.soft_max(s.astype(np.float32)[None, :])[0].astype(np.float16).astype(np.float32)
+            ref[h * hd:(h + 1) * hd] = p @ V[:pos + 1, hk * hd:(hk + 1) * hd].astype(np.float32)
+        assert np.abs(out - ref).max() <= 2e-3, pos
+    assert np.array_equal(kc[0].cpu().numpy()[:40], K[:40])
