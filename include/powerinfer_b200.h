@@ -138,6 +138,127 @@ int pi_attention_decode(const float * q, const float * k, const float * v, void 
                         const int32_t * seq, const int32_t * pos, int T, int n_head, int n_head_kv, int head_dim,
                         int n_ctx, float * out, void * stream);
 
+/* ---- the decode token loop ------------------------------------------------------------------------------ */
+
+/* One step of llama_decode (llama.cpp:6764-7006) over device-resident weights for up to max_batch sequences, one new
+ * token each (examples/batched-bench/batched-bench.cpp:205-216), for the three sparse architectures the reference
+ * builds graphs for: llama (llama.cpp:4949-5084), falcon (5326-5468), opt (5086-5204).  The launch sequence of a step
+ * is captured once per batch size and replayed as a CUDA graph. */
+
+#define PI_ARCH_LLAMA   0
+#define PI_ARCH_FALCON  1
+#define PI_ARCH_OPT     2
+#define PI_MAX_BATCH    32
+#define PI_MAX_RANKS    8
+
+typedef struct {
+    int arch, wtype;                 /* PI_ARCH_*, PI_TYPE_* of the 2-D weights (predictor and embeddings are F16) */
+    int n_layer, d, n_ff, n_head, n_head_kv, rank, n_vocab, n_ctx, n_pos;   /* n_pos: rows of pos_embd (opt) */
+    float norm_eps, rope_base, threshold;
+    int max_batch;
+    int n_ranks, rank_id;            /* neuron / head sharding over GPUs; 1, 0 for a single GPU */
+} pi_engine_config;
+
+/* Per-layer device pointers.  With n_ranks > 1 a rank holds the slice [rank_id*n/n_ranks, (rank_id+1)*n/n_ranks) of the
+ * FFN neurons and of the query / KV heads:
+ *   wqkv  [(dq + 2 dkv), d]   rows: this rank's Q heads, then its K heads, then its V heads (dq = d/n_ranks)
+ *   wo    [d, dq]             the columns of attn_output that multiply this rank's heads
+ *   fc1   [rank, d] (replicated)   fc2 [n_ff/n_ranks, rank]   gate/up/down_t [n_ff/n_ranks, d]
+ * 2-D weights are in `wtype` (Q4_0 in the planar layout), fc1/fc2 F16, vectors F32.  Unused pointers are NULL
+ * (gate for falcon/opt, biases for llama, attn_norm2 unless falcon-40B style, ffn_norm for falcon). */
+typedef struct {
+    const float * attn_norm_w, * attn_norm_b, * attn_norm2_w, * attn_norm2_b;
+    const void  * wqkv; const float * bqkv;
+    const void  * wo;   const float * bo;
+    const float * ffn_norm_w, * ffn_norm_b;
+    const void  * fc1, * fc2;
+    const void  * gate, * up, * down_t;
+    const float * up_b, * down_b;
+} pi_layer_weights;
+
+typedef struct {
+    const void  * tok_embd;          /* F16 [n_vocab, d] */
+    const void  * pos_embd;          /* F16 [n_pos, d], opt only */
+    const float * out_norm_w, * out_norm_b;
+    const void  * output;            /* [n_vocab, d] in wtype; NULL: tied to tok_embd (opt, llama.cpp:5199) */
+} pi_model_weights;
+
+/* Peer mailboxes for the per-layer exchange of partial d_model vectors (n_ranks > 1).  Every rank owns a mailbox
+ * [2, n_ranks, slot_floats] F32 and flags [2, n_ranks] u32 in ITS OWN memory; peers write into it with plain stores
+ * (the mapped addresses of every rank's mailbox and flags, own included, are listed here), nobody reads remote memory.
+ * slot_floats >= max_batch * d.  `epoch` and `ticket` are zero-initialised u32 words in this rank's memory. */
+typedef struct {
+    int n_ranks, rank_id;
+    int64_t slot_floats;
+    float * mailbox_local; unsigned int * flags_local;
+    float * mailbox_peer[PI_MAX_RANKS]; unsigned int * flags_peer[PI_MAX_RANKS];
+    unsigned int * epoch, * ticket;
+} pi_exchange;
+
+typedef struct pi_engine pi_engine;
+
+size_t pi_engine_workspace_bytes(const pi_engine_config * cfg);    /* 0 when cfg is invalid (see pi_last_error) */
+size_t pi_engine_kv_bytes(const pi_engine_config * cfg);           /* bytes of EACH of k_cache and v_cache */
+
+/* Replaces llama_new_context_with_model + the per-call graph build (llama.cpp:6408-6753, 6846-6850).  The engine keeps
+ * the pointers it is given: weights, workspace (256-byte aligned) and the FP16 KV caches [n_layer, max_batch, n_ctx,
+ * dkv] must stay valid and are owned by the caller.  Synchronises `stream` once. */
+int  pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * globals, const pi_layer_weights * layers,
+                      void * workspace, size_t workspace_bytes, void * k_cache, void * v_cache, void * stream,
+                      pi_engine ** out);
+void pi_engine_destroy(pi_engine * e);
+int  pi_engine_set_exchange(pi_engine * e, const pi_exchange * x);
+
+/* Device-side I/O of a step: tokens int32 [max_batch], pos int32 [max_batch] (position of each sequence's new token),
+ * logits F32 [max_batch, n_vocab], argmax int32 [max_batch] (llama_sample_token_greedy, llama.cpp:8617). */
+int  pi_engine_io(pi_engine * e, int32_t ** tokens, int32_t ** pos, float ** logits, int32_t ** argmax);
+
+/* Enqueue one step for T sequences on `stream`; inputs are read from / results left in the pi_engine_io buffers. */
+int  pi_engine_decode(pi_engine * e, int T, void * stream);
+
+/* Greedy feedback on the device: tokens[t] = argmax[t], pos[t] += 1 (clamped to the context), for a free-running
+ * decode loop that never leaves the GPU. */
+int  pi_engine_advance(pi_engine * e, int T, void * stream);
+
+/* llama_decode + llama_get_logits with HOST buffers (llama.cpp:10672, 6960-6978): copies T token ids and positions to the
+ * device, runs the step, copies back T*n_vocab logits (host_logits != NULL) and T greedy ids (host_argmax != NULL), and
+ * synchronises `stream`. */
+int  pi_engine_decode_host(pi_engine * e, const int32_t * host_tokens, const int32_t * host_pos, int T,
+                           float * host_logits, int32_t * host_argmax, void * stream);
+
+/* Same step launched kernel by kernel with CUDA events around each stage; adds the milliseconds of each stage to
+ * host_ms[PI_N_STAGES] and the number of kernel launches to *host_launches.  Synchronises. */
+#define PI_STAGE_NORM      0
+#define PI_STAGE_QKV       1
+#define PI_STAGE_ATTN      2
+#define PI_STAGE_WO        3
+#define PI_STAGE_PRED      4
+#define PI_STAGE_COMPACT   5
+#define PI_STAGE_UPGATE    6
+#define PI_STAGE_DOWN      7
+#define PI_STAGE_LM_HEAD   8
+#define PI_STAGE_EXCHANGE  9
+#define PI_STAGE_OTHER    10
+#define PI_N_STAGES       11
+int  pi_engine_profile_step(pi_engine * e, int T, float * host_ms, int * host_launches, void * stream);
+
+/* Device status word: 0, or PI_ERR_TIMEOUT after an exchange wait ran out.  Synchronises `stream`. */
+int  pi_engine_status(pi_engine * e, void * stream);
+
+/* For tests: device pointers of the predictor logits F32 [T, n_ff/n_ranks], active list and count that the LAST layer
+ * of the last step left behind. */
+int  pi_engine_debug(pi_engine * e, float ** pred, int32_t ** list, int32_t ** count);
+/* For tests: keep every layer's predictor logits.  pred_trace F32 [n_layer, max_batch, n_ff/n_ranks] (NULL: off). */
+int  pi_engine_set_trace(pi_engine * e, float * pred_trace);
+int  pi_engine_launches(pi_engine * e);                            /* kernels enqueued by one step of the last batch size run */
+
+/* ---- plumbing for multi-GPU mailboxes (these DO allocate; nothing else does) ----------------------------- */
+int  pi_device_malloc(void ** ptr, size_t bytes);                  /* cudaMalloc + zero fill */
+int  pi_device_free(void * ptr);
+int  pi_ipc_export(void * ptr, void * host_handle64);              /* cudaIpcGetMemHandle -> 64 bytes */
+int  pi_ipc_import(const void * host_handle64, void ** ptr);       /* cudaIpcOpenMemHandle */
+int  pi_ipc_close(void * ptr);
+
 #ifdef __cplusplus
 }
 #endif

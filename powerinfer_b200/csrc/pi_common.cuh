@@ -143,9 +143,14 @@ int launch_reduce_partials(const float * partial, int n_groups, int T, int64_t n
 struct NormArgs {
     const float * x = nullptr; int T = 1; int64_t n = 0; int rms = 1; float eps = 0.f;
     const float * w = nullptr; const float * b = nullptr;
-    // optional prologue: the vector to normalise is sum_j partial[j, t, :] (+ in_bias) (+ residual[t, :]) instead of x,
-    // and is written to x_out (the new residual stream)
-    const float * partial = nullptr; int n_groups = 0; const float * residual = nullptr; const float * in_bias = nullptr;
+    // optional prologue: the vector to normalise is ((sum_j partial[j, t, :] | x) + in_bias + residual[t, :]) + residual2[t, :]
+    // and is written to x_out (the new residual stream; may alias residual or residual2)
+    const float * partial = nullptr; int n_groups = 0; const float * residual = nullptr; const float * residual2 = nullptr;
+    const float * in_bias = nullptr;
+    int64_t partial_stride = 0;        // floats between consecutive partials (0: T * n)
+    // when the partials are another ranks' mailbox slots: wait (bounded) until every flag reached *wait_epoch first;
+    // the slot set in use is parity (*wait_epoch & 1): partial += parity * n_groups * partial_stride
+    const unsigned int * wait_flags = nullptr; const unsigned int * wait_epoch = nullptr; unsigned int * status = nullptr;
     float * x_out = nullptr;
     float * y = nullptr;               // optional F32 output
     int act_type = 0; ActBuf act;      // optional activation planes of the normalised vector (0: none, else PI_TYPE_*)
@@ -160,11 +165,17 @@ struct AttnArgs {
     __half * k_cache = nullptr; __half * v_cache = nullptr;
     const int32_t * seq = nullptr; const int32_t * pos = nullptr;
     int T = 1, n_head = 0, n_head_kv = 0, head_dim = 0, n_ctx = 0;
+    int64_t q_stride = 0, kv_stride = 0;               // floats between tokens of q and of k / v (0: dense)
     const float * cs = nullptr; int neox = 0;          // fused RoPE of q and k from the angle table (nullptr: already rotated)
     float * out = nullptr;                             // optional F32 [T, n_head*head_dim]
     int out_act_type = 0; ActBuf out_act;              // optional activation planes of the output
 };
 int launch_attention(const AttnArgs & a, cudaStream_t st);
+
+// v = sum_g partial[g, t, :] (+ extra[t, :]) is written into slot rank_id of every rank's mailbox, then the flags are
+// raised to the next epoch (see pi_exchange in the public header)
+int launch_exchange_push(const pi_exchange & x, const float * partial, int n_groups, int T, int64_t n, const float * extra,
+                         unsigned int * status, cudaStream_t st);
 
 // ------------------------------------------------------------------------------------ device primitives
 #ifdef __CUDACC__

@@ -17,7 +17,8 @@ static constexpr int NORM_CHUNKS = 2;
 
 struct NormP {
     const float * x; int64_t n; int rms; float eps; const float * w; const float * b;
-    const float * partial; int n_groups; int T; const float * residual; const float * in_bias; float * x_out;
+    const float * partial; int n_groups; int T; const float * residual; const float * residual2; const float * in_bias; float * x_out;
+    int64_t partial_stride; const unsigned int * wait_flags; const unsigned int * wait_epoch; unsigned int * status;
     float * y; int act_type; ActBuf act; int act2_type; ActBuf act2; int act2_src;
 };
 
@@ -73,7 +74,28 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
     __shared__ double s_red[32];
     const int t = blockIdx.x;
     const int64_t n = p.n;
-    const size_t tn = (size_t)p.T * n;
+    const size_t tn = p.partial_stride ? (size_t)p.partial_stride : (size_t)p.T * n;
+    const float * partial = p.partial;
+    if (p.wait_flags) {
+        // the partials are mailbox slots written by the other ranks: wait for their flags, but never forever
+        const unsigned int epoch = *p.wait_epoch;
+        const unsigned int par = epoch & 1u;
+        if (threadIdx.x < (unsigned)p.n_groups) {
+            const volatile unsigned int * f = p.wait_flags + par * p.n_groups + threadIdx.x;
+            const long long t0 = clock64();
+            bool ok_flag = false;
+            for (;;) {
+                unsigned int seen;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f));
+                if ((int)(seen - epoch) >= 0) { ok_flag = true; break; }
+                if (clock64() - t0 > 2000000000LL) break;          // about a second
+                __nanosleep(64);
+            }
+            if (!ok_flag) atomicOr(p.status, 1u);
+        }
+        __syncthreads();
+        partial += (size_t)par * p.n_groups * tn;
+    }
     float v[NORM_CHUNKS][8];
     bool ok[NORM_CHUNKS];
 #pragma unroll
@@ -86,8 +108,8 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
         if (ok[k]) {
         if (p.partial) {
             for (int g = 0; g < p.n_groups; g++) {
-                const float4 a = *reinterpret_cast<const float4 *>(p.partial + (size_t)g * tn + o);
-                const float4 b = *reinterpret_cast<const float4 *>(p.partial + (size_t)g * tn + o + 4);
+                const float4 a = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)g * tn + o));
+                const float4 b = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)g * tn + o + 4));
                 v[k][0] += a.x; v[k][1] += a.y; v[k][2] += a.z; v[k][3] += a.w;
                 v[k][4] += b.x; v[k][5] += b.y; v[k][6] += b.z; v[k][7] += b.w;
             }
@@ -104,6 +126,10 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
         if (p.residual) {
 #pragma unroll
             for (int j = 0; j < 8; j++) v[k][j] += p.residual[o + j];
+        }
+        if (p.residual2) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[k][j] += p.residual2[o + j];
         }
         if (p.x_out) {
             *reinterpret_cast<float4 *>(p.x_out + o)     = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
@@ -169,7 +195,8 @@ int launch_norm(const NormArgs & a, cudaStream_t st) {
                (long long)a.n, NORM_CHUNKS * 1024 * 8);
     NormP p;
     p.x = a.x; p.n = a.n; p.rms = a.rms; p.eps = a.eps; p.w = a.w; p.b = a.b;
-    p.partial = a.partial; p.n_groups = a.n_groups; p.T = a.T; p.residual = a.residual; p.in_bias = a.in_bias; p.x_out = a.x_out;
+    p.partial = a.partial; p.n_groups = a.n_groups; p.T = a.T; p.residual = a.residual; p.residual2 = a.residual2; p.in_bias = a.in_bias; p.x_out = a.x_out;
+    p.partial_stride = a.partial_stride; p.wait_flags = a.wait_flags; p.wait_epoch = a.wait_epoch; p.status = a.status;
     p.y = a.y; p.act_type = a.act_type; p.act = a.act; p.act2_type = a.act2_type; p.act2 = a.act2; p.act2_src = a.act2_src;
     int threads = (int)((a.n / 8 + NORM_CHUNKS - 1) / NORM_CHUNKS);
     threads = min(1024, max(32, (threads + 31) / 32 * 32));
@@ -222,7 +249,7 @@ static constexpr int ATTN_THREADS = 256;
 struct AttnP {
     const float * q; const float * k; const float * v; __half * k_cache; __half * v_cache;
     const int32_t * seq; const int32_t * pos; int n_head, n_head_kv, hd, n_ctx;
-    const float * cs; int neox; int sc_floats;
+    const float * cs; int neox; int sc_floats; int64_t q_stride, kv_stride;
     float * out; ActBuf out_act; int out_act_type;
 };
 
@@ -244,9 +271,9 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     __half * v16 = k16 + hd;                                     // [hd] the new token's V
     __half * p16 = v16 + hd;                                     // [n_ctx] probabilities in FP16
 
-    const float * qh = p.q + ((size_t)t * p.n_head + h) * hd;
-    const float * kh = p.k + ((size_t)t * p.n_head_kv + hk) * hd;
-    const float * vh = p.v + ((size_t)t * p.n_head_kv + hk) * hd;
+    const float * qh = p.q + (size_t)t * p.q_stride + (size_t)h * hd;
+    const float * kh = p.k + (size_t)t * p.kv_stride + (size_t)hk * hd;
+    const float * vh = p.v + (size_t)t * p.kv_stride + (size_t)hk * hd;
     for (int e = tid; e < hd; e += ATTN_THREADS) v16[e] = __float2half_rn(vh[e]);
     if (p.cs) {
         for (int k = tid; k < half; k += ATTN_THREADS) {
@@ -355,6 +382,8 @@ int launch_attention(const AttnArgs & a, cudaStream_t st) {
     AttnP p;
     p.q = a.q; p.k = a.k; p.v = a.v; p.k_cache = a.k_cache; p.v_cache = a.v_cache; p.seq = a.seq; p.pos = a.pos;
     p.n_head = a.n_head; p.n_head_kv = a.n_head_kv; p.hd = a.head_dim; p.n_ctx = a.n_ctx;
+    p.q_stride = a.q_stride ? a.q_stride : (int64_t)a.n_head * a.head_dim;
+    p.kv_stride = a.kv_stride ? a.kv_stride : (int64_t)a.n_head_kv * a.head_dim;
     p.cs = a.cs; p.neox = a.neox; p.out = a.out; p.out_act = a.out_act; p.out_act_type = a.out_act_type;
     // sc must hold max(n_ctx, slices*hd) floats
     const int slices = ATTN_THREADS / (a.head_dim / 2) > 0 ? ATTN_THREADS / (a.head_dim / 2) : 1;

@@ -169,18 +169,25 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_gemv(const GemvP p) {
 
 template <int WT, int TT, bool SPARSE, bool GATED>
 static int launch_inst(const GemvP & p, size_t smem, cudaStream_t st) {
-    static int blocks_per_sm[16] = {0};
+    // resident CTAs per SM for this instantiation, remembered per (device, shared-memory size) so that replays and
+    // stream captures never query the runtime again
+    struct Slot { size_t smem; int bps; };
+    static Slot cache[16][8] = {};
+    static bool attr_done[16] = {false};
     int dev = 0;
     PI_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16) { set_error("gemv: device ordinal %d not supported", dev); return PI_ERR_UNSUPPORTED; }
     auto kern = k_gemv<WT, TT, SPARSE, GATED>;
-    if (dev < 16 && blocks_per_sm[dev] == 0) {
+    if (!attr_done[dev]) {
         PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_done[dev] = true;
     }
-    int bps = dev < 16 ? blocks_per_sm[dev] : 0;
-    if (bps == 0 || smem > 24 * 1024) {
+    int bps = 0;
+    for (auto & s : cache[dev]) if (s.bps && s.smem == smem) bps = s.bps;
+    if (!bps) {
         PI_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, kern, GEMV_THREADS, smem));
         if (bps < 1) { set_error("gemv: activation of %zu bytes does not fit in shared memory", smem); return PI_ERR_INVALID; }
-        if (dev < 16 && smem <= 24 * 1024) blocks_per_sm[dev] = bps;
+        for (auto & s : cache[dev]) if (!s.bps) { s.smem = smem; s.bps = bps; break; }
     }
     const int warps_per_block = GEMV_THREADS / 32;
     int grid = sm_count() * bps;

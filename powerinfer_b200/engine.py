@@ -1,0 +1,354 @@
+"""Host-side driver of the decode engine: weight upload / sharding, buffers, and the llama_decode-style step.
+
+Mirrors the reference's calling sequence (llama.h): build a model once (llama_load_model_from_file +
+llama_new_context_with_model), then `decode(tokens, pos)` per step (llama_decode) and read `logits`
+(llama_get_logits) or the greedy ids (llama_sample_token_greedy).  All compute happens in
+libpowerinfer_b200.so; torch provides device memory, streams and (for sharded runs) the process group used
+to hand IPC handles around.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import synth
+from ._lib import PI_TYPE_F16, PI_TYPE_Q4_0, check, lib
+
+PI_MAX_RANKS = 8
+N_STAGES = 11
+STAGE_NAMES = ["norm", "qkv", "attention", "out_proj", "predictor", "compact", "up_gate", "down", "lm_head", "exchange", "other"]
+
+_vp = C.c_void_p
+
+
+class EngineConfig(C.Structure):
+    _fields_ = [("arch", C.c_int), ("wtype", C.c_int), ("n_layer", C.c_int), ("d", C.c_int), ("n_ff", C.c_int),
+                ("n_head", C.c_int), ("n_head_kv", C.c_int), ("rank", C.c_int), ("n_vocab", C.c_int), ("n_ctx", C.c_int),
+                ("n_pos", C.c_int), ("norm_eps", C.c_float), ("rope_base", C.c_float), ("threshold", C.c_float),
+                ("max_batch", C.c_int), ("n_ranks", C.c_int), ("rank_id", C.c_int)]
+
+
+class LayerWeights(C.Structure):
+    _fields_ = [(n, _vp) for n in ("attn_norm_w", "attn_norm_b", "attn_norm2_w", "attn_norm2_b", "wqkv", "bqkv", "wo", "bo",
+                                   "ffn_norm_w", "ffn_norm_b", "fc1", "fc2", "gate", "up", "down_t", "up_b", "down_b")]
+
+
+class ModelWeights(C.Structure):
+    _fields_ = [(n, _vp) for n in ("tok_embd", "pos_embd", "out_norm_w", "out_norm_b", "output")]
+
+
+class Exchange(C.Structure):
+    _fields_ = [("n_ranks", C.c_int), ("rank_id", C.c_int), ("slot_floats", C.c_int64),
+                ("mailbox_local", _vp), ("flags_local", _vp),
+                ("mailbox_peer", _vp * PI_MAX_RANKS), ("flags_peer", _vp * PI_MAX_RANKS),
+                ("epoch", _vp), ("ticket", _vp)]
+
+
+for _name, _res, _args in [
+    ("pi_engine_workspace_bytes", C.c_size_t, [C.POINTER(EngineConfig)]),
+    ("pi_engine_kv_bytes", C.c_size_t, [C.POINTER(EngineConfig)]),
+    ("pi_engine_create", C.c_int, [C.POINTER(EngineConfig), C.POINTER(ModelWeights), C.POINTER(LayerWeights), _vp, C.c_size_t,
+                                   _vp, _vp, _vp, C.POINTER(_vp)]),
+    ("pi_engine_destroy", None, [_vp]),
+    ("pi_engine_set_exchange", C.c_int, [_vp, C.POINTER(Exchange)]),
+    ("pi_engine_io", C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp)]),
+    ("pi_engine_decode", C.c_int, [_vp, C.c_int, _vp]),
+    ("pi_engine_advance", C.c_int, [_vp, C.c_int, _vp]),
+    ("pi_engine_decode_host", C.c_int, [_vp, _vp, _vp, C.c_int, _vp, _vp, _vp]),
+    ("pi_engine_profile_step", C.c_int, [_vp, C.c_int, _vp, C.POINTER(C.c_int), _vp]),
+    ("pi_engine_status", C.c_int, [_vp, _vp]),
+    ("pi_engine_debug", C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp)]),
+    ("pi_engine_launches", C.c_int, [_vp]),
+    ("pi_engine_set_trace", C.c_int, [_vp, _vp]),
+    ("pi_device_malloc", C.c_int, [C.POINTER(_vp), C.c_size_t]),
+    ("pi_device_free", C.c_int, [_vp]),
+    ("pi_ipc_export", C.c_int, [_vp, _vp]),
+    ("pi_ipc_import", C.c_int, [_vp, C.POINTER(_vp)]),
+    ("pi_ipc_close", C.c_int, [_vp]),
+]:
+    _fn = getattr(lib, _name)
+    _fn.restype, _fn.argtypes = _res, _args
+
+ENGINE_EXPORTS = ["pi_engine_workspace_bytes", "pi_engine_kv_bytes", "pi_engine_create", "pi_engine_destroy",
+                  "pi_engine_set_exchange", "pi_engine_io", "pi_engine_decode", "pi_engine_advance", "pi_engine_decode_host",
+                  "pi_engine_profile_step", "pi_engine_status", "pi_engine_debug", "pi_engine_launches", "pi_engine_set_trace",
+                  "pi_device_malloc", "pi_device_free", "pi_ipc_export", "pi_ipc_import", "pi_ipc_close"]
+
+
+# ------------------------------------------------------------------------------------------------ sharding (host logic)
+
+def shard_rows(a, n_ranks: int, rank: int):
+    n = a.shape[0] // n_ranks
+    return a[rank * n:(rank + 1) * n]
+
+
+def shard_cols(a, wtype: int, n_ranks: int, rank: int):
+    """Column slice of a [rows, cols] weight: F16 elements, or Q4_0 block bytes (18 per 32 columns)."""
+    unit = 18 if (wtype == PI_TYPE_Q4_0 and a.dtype in (np.uint8, torch.uint8)) else 1
+    per = a.shape[1] // n_ranks
+    assert per % unit == 0
+    return a[:, rank * per:(rank + 1) * per]
+
+
+def shard_layer(spec: synth.ModelSpec, t: dict, il: int, n_ranks: int, rank: int) -> dict:
+    """The slice of layer `il` that rank `rank` holds: its FFN neurons (rows of fc2 / up / gate / down_t, a contiguous
+    range of whole 32-neuron blocks) and its heads (rows of q/k/v, columns of attn_output).  Works on numpy arrays and
+    torch tensors alike.  Returns the engine's tensor names (wqkv, bqkv, wo, ...)."""
+    p = f"blk.{il}."
+    cat = (lambda xs: torch.cat(xs, 0)) if isinstance(t[p + "fc1.weight"], torch.Tensor) else (lambda xs: np.concatenate(xs, 0))
+    g = lambda k: t.get(p + k)
+    d, dkv = spec.d, spec.d_kv
+    out = {}
+    for k in ("attn_norm.weight", "attn_norm.bias", "attn_norm_2.weight", "attn_norm_2.bias", "ffn_norm.weight", "ffn_norm.bias"):
+        out[k] = g(k)
+    if spec.arch == synth.ARCH_FALCON:
+        w = g("attn_qkv.weight")
+        q, k_, v = w[:d], w[d:d + dkv], w[d + dkv:]
+        bq = bk = bv = None
+    else:
+        q, k_, v = g("attn_q.weight"), g("attn_k.weight"), g("attn_v.weight")
+        bq, bk, bv = g("attn_q.bias"), g("attn_k.bias"), g("attn_v.bias")
+    out["wqkv"] = cat([shard_rows(q, n_ranks, rank), shard_rows(k_, n_ranks, rank), shard_rows(v, n_ranks, rank)])
+    out["bqkv"] = None if bq is None else cat([shard_rows(bq, n_ranks, rank), shard_rows(bk, n_ranks, rank), shard_rows(bv, n_ranks, rank)])
+    out["wo"] = shard_cols(g("attn_output.weight"), spec.wtype, n_ranks, rank)
+    out["bo"] = g("attn_output.bias")
+    out["fc1"] = g("fc1.weight")
+    out["fc2"] = shard_rows(g("fc2.weight"), n_ranks, rank)
+    out["gate"] = None if g("ffn_gate.weight") is None else shard_rows(g("ffn_gate.weight"), n_ranks, rank)
+    out["up"] = shard_rows(g("ffn_up.weight"), n_ranks, rank)
+    out["down_t"] = shard_rows(g("ffn_down_t.weight"), n_ranks, rank)
+    out["up_b"] = None if g("ffn_up.bias") is None else shard_rows(g("ffn_up.bias"), n_ranks, rank)
+    out["down_b"] = g("ffn_down_t.bias")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ device side
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(a):
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        a = torch.from_numpy(np.ascontiguousarray(a))
+    return a.contiguous().cuda()
+
+
+def _upload2d(a, wtype: int):
+    """F16 [rows, cols] stays as is; Q4_0 ggml block bytes [rows, cols/32*18] are re-laid out (pi_q4_0_repack)."""
+    a = _dev(a)
+    if a.dtype == torch.float16:
+        return a
+    assert a.dtype == torch.uint8 and wtype == PI_TYPE_Q4_0
+    rows, ncols = a.shape[0], a.shape[1] // 18 * 32
+    out = torch.empty_like(a)
+    check(lib.pi_q4_0_repack(a.data_ptr(), out.data_ptr(), rows, ncols, _stream()))
+    return out
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+class DecodeEngine:
+    """One rank of the decode loop.  `tensors` holds the FULL model under the reference's GGUF tensor names (numpy or
+    torch); this rank uploads its slice."""
+
+    def __init__(self, spec: synth.ModelSpec, tensors: dict, max_batch: int = 1, n_ranks: int = 1, rank: int = 0,
+                 local_layers: list | None = None):
+        self.spec, self.max_batch, self.n_ranks, self.rank = spec, max_batch, n_ranks, rank
+        n_pos = synth.OPT_N_POS if spec.arch == synth.ARCH_OPT else 0
+        self.cfg = EngineConfig(spec.arch, spec.wtype, spec.n_layer, spec.d, spec.n_ff, spec.n_head, spec.n_head_kv, spec.rank,
+                                spec.n_vocab, spec.n_ctx, n_pos, spec.norm_eps, spec.rope_base, spec.threshold, max_batch,
+                                n_ranks, rank)
+        ws_bytes = lib.pi_engine_workspace_bytes(C.byref(self.cfg))
+        if ws_bytes == 0:
+            check(1)
+        self.keep = []                       # device tensors the engine points into
+
+        def hold(x):
+            if x is not None:
+                self.keep.append(x)
+            return x
+
+        self.layers = (LayerWeights * spec.n_layer)()
+        for il in range(spec.n_layer):
+            sl = local_layers[il] if local_layers is not None else shard_layer(spec, tensors, il, n_ranks, rank)
+            L = self.layers[il]
+            for name in ("attn_norm.weight", "attn_norm.bias", "attn_norm_2.weight", "attn_norm_2.bias", "ffn_norm.weight", "ffn_norm.bias"):
+                field = {"attn_norm.weight": "attn_norm_w", "attn_norm.bias": "attn_norm_b", "attn_norm_2.weight": "attn_norm2_w",
+                         "attn_norm_2.bias": "attn_norm2_b", "ffn_norm.weight": "ffn_norm_w", "ffn_norm.bias": "ffn_norm_b"}[name]
+                setattr(L, field, _ptr(hold(_dev(sl.get(name)))))
+            for name in ("wqkv", "wo", "gate", "up", "down_t"):
+                a = sl.get(name)
+                setattr(L, name, _ptr(hold(None if a is None else _upload2d(a, spec.wtype))))
+            for name in ("fc1", "fc2"):
+                setattr(L, name, _ptr(hold(_dev(sl[name]))))
+            for name in ("bqkv", "bo", "up_b", "down_b"):
+                setattr(L, name, _ptr(hold(_dev(sl.get(name)))))
+        g = tensors
+        self.globals = ModelWeights(
+            _ptr(hold(_dev(g["token_embd.weight"]))), _ptr(hold(_dev(g.get("position_embd.weight")))),
+            _ptr(hold(_dev(g["output_norm.weight"]))), _ptr(hold(_dev(g.get("output_norm.bias")))),
+            _ptr(hold(None if g.get("output.weight") is None else _upload2d(g["output.weight"], spec.wtype))))
+        kv_bytes = lib.pi_engine_kv_bytes(C.byref(self.cfg))
+        self.k_cache = torch.zeros(kv_bytes // 2, dtype=torch.float16, device="cuda")
+        self.v_cache = torch.zeros(kv_bytes // 2, dtype=torch.float16, device="cuda")
+        self.ws = torch.empty(ws_bytes + 256, dtype=torch.uint8, device="cuda")
+        off = (-self.ws.data_ptr()) % 256
+        self.handle = _vp()
+        # the step is captured into a CUDA graph, which the legacy default stream cannot do: the engine owns a stream
+        self.stream = torch.cuda.Stream()
+        self.st = self.stream.cuda_stream
+        torch.cuda.synchronize()
+        check(lib.pi_engine_create(C.byref(self.cfg), C.byref(self.globals), self.layers, self.ws.data_ptr() + off, ws_bytes,
+                                   self.k_cache.data_ptr(), self.v_cache.data_ptr(), self.st, C.byref(self.handle)))
+        tok, pos, logits, amax = _vp(), _vp(), _vp(), _vp()
+        check(lib.pi_engine_io(self.handle, C.byref(tok), C.byref(pos), C.byref(logits), C.byref(amax)))
+        self.io = (tok.value, pos.value, logits.value, amax.value)
+        # pinned host staging for the host-buffer entry point
+        self.h_tokens = torch.zeros(max_batch, dtype=torch.int32).pin_memory()
+        self.h_pos = torch.zeros(max_batch, dtype=torch.int32).pin_memory()
+        self.h_logits = torch.zeros(max_batch, spec.n_vocab, dtype=torch.float32).pin_memory()
+        self.h_argmax = torch.zeros(max_batch, dtype=torch.int32).pin_memory()
+        self._xch_mem = None
+
+    # ---- llama_decode + llama_get_logits with host buffers
+    def decode(self, tokens, pos, want_logits: bool = True):
+        T = len(tokens)
+        self.h_tokens[:T] = torch.as_tensor(tokens, dtype=torch.int32)
+        self.h_pos[:T] = torch.as_tensor(pos, dtype=torch.int32)
+        check(lib.pi_engine_decode_host(self.handle, self.h_tokens.data_ptr(), self.h_pos.data_ptr(), T,
+                                        self.h_logits.data_ptr() if want_logits else None, self.h_argmax.data_ptr(), self.st))
+        return (self.h_logits[:T].numpy() if want_logits else None), self.h_argmax[:T].numpy()
+
+    def decode_host_raw(self, T: int, want_logits: bool = True):
+        """The same call with the staging buffers already filled (benchmark inner loop: no Python-side copies)."""
+        check(lib.pi_engine_decode_host(self.handle, self.h_tokens.data_ptr(), self.h_pos.data_ptr(), T,
+                                        self.h_logits.data_ptr() if want_logits else None, self.h_argmax.data_ptr(), self.st))
+
+    # ---- device-resident step: inputs already in the engine's device buffers
+    def set_inputs_device(self, tokens, pos):
+        T = len(tokens)
+        self.h_tokens[:T] = torch.as_tensor(tokens, dtype=torch.int32)
+        self.h_pos[:T] = torch.as_tensor(pos, dtype=torch.int32)
+        with torch.cuda.stream(self.stream):
+            self.device_view("tokens", T).copy_(self.h_tokens[:T], non_blocking=True)
+            self.device_view("pos", T).copy_(self.h_pos[:T], non_blocking=True)
+        self.stream.synchronize()            # the pinned staging buffers are reused by the next call
+
+    def step_device(self, T: int):
+        check(lib.pi_engine_decode(self.handle, T, self.st))
+
+    def advance(self, T: int):
+        """tokens <- argmax, pos += 1 on the device (free-running greedy decode)."""
+        check(lib.pi_engine_advance(self.handle, T, self.st))
+
+    def device_view(self, what: str, T: int):
+        """torch view of an engine I/O buffer: tokens / pos / argmax int32 [T], logits float32 [T, n_vocab]."""
+        idx = {"tokens": 0, "pos": 1, "logits": 2, "argmax": 3}[what]
+        n = T * self.spec.n_vocab if what == "logits" else T
+        dt = torch.float32 if what == "logits" else torch.int32
+        return _wrap_device(self.io[idx], n, dt).view(T, -1) if what == "logits" else _wrap_device(self.io[idx], n, dt)
+
+    def profile_step(self, T: int):
+        ms = (C.c_float * N_STAGES)()
+        launches = C.c_int(0)
+        check(lib.pi_engine_profile_step(self.handle, T, ms, C.byref(launches), self.st))
+        return {STAGE_NAMES[i]: ms[i] for i in range(N_STAGES)}, launches.value
+
+    def launches(self) -> int:
+        return lib.pi_engine_launches(self.handle)
+
+    def status(self):
+        check(lib.pi_engine_status(self.handle, self.st))
+
+    def enable_trace(self):
+        """Keep every layer's predictor logits of a step (tests compare active sets layer by layer)."""
+        F = self.spec.n_ff // self.n_ranks
+        self.trace = torch.zeros(self.spec.n_layer, self.max_batch, F, dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        check(lib.pi_engine_set_trace(self.handle, self.trace.data_ptr()))
+
+    def predictor_trace(self, T: int) -> np.ndarray:
+        torch.cuda.synchronize()
+        return self.trace[:, :T].cpu().numpy()
+
+    def last_layer_predictor(self, T: int):
+        pred, lst, cnt = _vp(), _vp(), _vp()
+        check(lib.pi_engine_debug(self.handle, C.byref(pred), C.byref(lst), C.byref(cnt)))
+        F = self.spec.n_ff // self.n_ranks
+        torch.cuda.synchronize()
+        n = int(_wrap_device(cnt.value, 1, torch.int32).item())
+        return (_wrap_device(pred.value, T * F, torch.float32).view(T, F).cpu().numpy(),
+                _wrap_device(lst.value, F, torch.int32)[:n].cpu().numpy())
+
+    # ---- sharded runs: mailboxes in every rank's memory, addresses exchanged through the process group
+    def setup_exchange(self, group=None):
+        import torch.distributed as dist
+        assert self.n_ranks > 1
+        slot = self.max_batch * self.spec.d
+        mbox_bytes = 2 * self.n_ranks * slot * 4
+        flag_bytes = 256
+        total = mbox_bytes + 2 * flag_bytes
+        base = _vp()
+        check(lib.pi_device_malloc(C.byref(base), total))
+        handle = (C.c_char * 64)()
+        check(lib.pi_ipc_export(base, handle))
+        mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device="cuda")
+        allh = [torch.empty_like(mine) for _ in range(self.n_ranks)]
+        dist.all_gather(allh, mine, group=group)
+        x = Exchange()
+        x.n_ranks, x.rank_id, x.slot_floats = self.n_ranks, self.rank, slot
+        self._peer_ptrs = []
+        for r in range(self.n_ranks):
+            if r == self.rank:
+                p = base.value
+            else:
+                hb = bytes(allh[r].cpu().tolist())
+                pp = _vp()
+                check(lib.pi_ipc_import(hb, C.byref(pp)))
+                p = pp.value
+                self._peer_ptrs.append(p)
+            x.mailbox_peer[r] = p
+            x.flags_peer[r] = p + mbox_bytes
+        x.mailbox_local = base.value
+        x.flags_local = base.value + mbox_bytes
+        x.epoch = base.value + mbox_bytes + flag_bytes
+        x.ticket = base.value + mbox_bytes + flag_bytes + 64
+        self._xch_mem = base
+        self.xch = x
+        check(lib.pi_engine_set_exchange(self.handle, C.byref(x)))
+        dist.barrier(group=group)
+
+    def close(self):
+        if getattr(self, "handle", None) and self.handle.value:
+            torch.cuda.synchronize()
+            lib.pi_engine_destroy(self.handle)
+            self.handle = _vp()
+            for p in getattr(self, "_peer_ptrs", []):
+                lib.pi_ipc_close(p)
+            if self._xch_mem is not None:
+                lib.pi_device_free(self._xch_mem)
+                self._xch_mem = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class _Cai:
+    """Minimal __cuda_array_interface__ holder so torch can view memory the engine carved from its workspace."""
+
+    def __init__(self, ptr, n, typestr):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def _wrap_device(ptr: int, n: int, dtype):
+    return torch.as_tensor(_Cai(ptr, n, "<f4" if dtype == torch.float32 else "<i4"), device="cuda")

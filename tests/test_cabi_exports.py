@@ -23,8 +23,8 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_binding_covers_header_and_host_helpers_work():
-    from powerinfer_b200 import _lib
-    assert set(_lib.EXPORTS) == set(declared_symbols())
+    from powerinfer_b200 import _lib, engine
+    assert set(_lib.EXPORTS) | set(engine.ENGINE_EXPORTS) == set(declared_symbols())
     assert _lib.lib.pi_version() >= 1
     assert _lib.lib.pi_row_bytes(_lib.PI_TYPE_F16, 4096) == 8192
     assert _lib.lib.pi_row_bytes(_lib.PI_TYPE_Q4_0, 4096) == 2304
