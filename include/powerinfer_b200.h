@@ -250,6 +250,8 @@ int  pi_engine_status(pi_engine * e, void * stream);
 int  pi_engine_debug(pi_engine * e, float ** pred, int32_t ** list, int32_t ** count);
 /* For tests: keep every layer's predictor logits.  pred_trace F32 [n_layer, max_batch, n_ff/n_ranks] (NULL: off). */
 int  pi_engine_set_trace(pi_engine * e, float * pred_trace);
+/* Sum of the active-list lengths (this rank's neurons) over all layers and steps since the last reset.  Synchronises. */
+int  pi_engine_active_total(pi_engine * e, int reset, unsigned long long * host_total, void * stream);
 int  pi_engine_launches(pi_engine * e);                            /* kernels enqueued by one step of the last batch size run */
 
 /* ---- plumbing for multi-GPU mailboxes (these DO allocate; nothing else does) ----------------------------- */

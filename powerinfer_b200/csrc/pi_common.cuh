@@ -118,6 +118,7 @@ struct CompactArgs {
     const float * fill_bias = nullptr; int fill_relu = 0;  // set to 0, or to (relu of) fill_bias[g] (what the graph's bias add leaves there)
     uint32_t * masks = nullptr;        // scratch: one word per 32 local rows
     unsigned int * ticket = nullptr;   // scratch: one word, must be 0 on entry, is 0 again on exit
+    unsigned long long * total = nullptr;   // optional running sum of the counts (statistics)
 };
 int launch_compact(const CompactArgs & a, cudaStream_t st);
 

@@ -90,6 +90,7 @@ struct pi_engine {
     ActBuf act_a, act_q, act_p, act_o;       // FFN input, QKV input, predictor input (FP16), out-proj input
     __half * k_cache, * v_cache;             // [n_layer, max_batch, n_ctx, dkv]
     unsigned int * status;                   // device word: bit 0 = an exchange wait ran out
+    unsigned long long * active_total;       // device counter: sum of active-list lengths over layers and steps
     pi_exchange xch;
     cudaGraphExec_t graphs[PI_MAX_BATCH + 1];
     bool warmed[PI_MAX_BATCH + 1];
@@ -122,7 +123,7 @@ static void carve(pi_engine * e, void * ws, size_t ws_bytes, bool dry, size_t * 
     const int T = e->T_max;
     const size_t d = c.d, F = e->F;
     e->tokens = cv.take<int32_t>(T); e->pos = cv.take<int32_t>(T); e->seq_ids = cv.take<int32_t>(T); e->argmax = cv.take<int32_t>(T);
-    e->status = cv.take<unsigned int>(1);
+    e->status = cv.take<unsigned int>(1); e->active_total = cv.take<unsigned long long>(1);
     e->x = cv.take<float>(T * d); e->attn_out = cv.take<float>(T * d); e->ffn_vec = cv.take<float>(T * d);
     e->qkv = cv.take<float>((size_t)T * (e->dq + 2 * e->dkv));
     e->pred = cv.take<float>(T * F); e->h = cv.take<float>(T * F);
@@ -213,6 +214,7 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
     if (ce == cudaSuccess) ce = cudaMemsetAsync(e->ticket, 0, 4, st);
     if (ce == cudaSuccess) ce = cudaMemsetAsync(e->count, 0, 4, st);
     if (ce == cudaSuccess) ce = cudaMemsetAsync(e->status, 0, 4, st);
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(e->active_total, 0, 8, st);
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);            // the host vectors above die at return
     if (ce != cudaSuccess) { delete e; return cuda_fail(ce, "engine_create"); }
     *out = e;
@@ -249,18 +251,40 @@ int pi_engine_set_exchange(pi_engine * e, const pi_exchange * x) {
 
 namespace {
 
-struct StageTimer {            // optional per-stage CUDA-event timing (profile mode only)
-    bool on = false; cudaStream_t st = nullptr; float * acc = nullptr; cudaEvent_t a = nullptr, b = nullptr;
-    int begin() { if (on) PI_CUDA(cudaEventRecord(a, st)); return PI_OK; }
-    int end(int stage) {
+// Optional per-stage CUDA-event timing (profile mode only).  Events are queued around every stage and read after the
+// whole step has drained, so the GPU never idles between a start event and its kernel.
+struct StageTimer {
+    bool on = false; cudaStream_t st = nullptr;
+    std::vector<cudaEvent_t> pool; std::vector<int> stage_of; size_t used = 0;
+    cudaEvent_t next() {
+        if (used == pool.size()) { cudaEvent_t ev = nullptr; if (cudaEventCreate(&ev) != cudaSuccess) return nullptr; pool.push_back(ev); }
+        return pool[used++];
+    }
+    int begin() {
         if (!on) return PI_OK;
-        PI_CUDA(cudaEventRecord(b, st));
-        PI_CUDA(cudaEventSynchronize(b));
-        float ms = 0.f;
-        PI_CUDA(cudaEventElapsedTime(&ms, a, b));
-        acc[stage] += ms;
+        cudaEvent_t a = next();
+        if (!a) return PI_ERR_CUDA;
+        PI_CUDA(cudaEventRecord(a, st));
         return PI_OK;
     }
+    int end(int stage) {
+        if (!on) return PI_OK;
+        cudaEvent_t b = next();
+        if (!b) return PI_ERR_CUDA;
+        PI_CUDA(cudaEventRecord(b, st));
+        stage_of.push_back(stage);
+        return PI_OK;
+    }
+    int collect(float * acc) {
+        PI_CUDA(cudaStreamSynchronize(st));
+        for (size_t i = 0; i < stage_of.size(); i++) {
+            float ms = 0.f;
+            PI_CUDA(cudaEventElapsedTime(&ms, pool[2 * i], pool[2 * i + 1]));
+            acc[stage_of[i]] += ms;
+        }
+        return PI_OK;
+    }
+    ~StageTimer() { for (auto ev : pool) cudaEventDestroy(ev); }
 };
 
 #define STAGE(stage, n_kernels, call)                    \
@@ -421,7 +445,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
         {
             CompactArgs ca;
             ca.idx = pred; ca.idx_stride = F; ca.T = T; ca.threshold = c.threshold; ca.n_local = F;
-            ca.list = e->list; ca.count = e->count; ca.masks = e->masks; ca.ticket = e->ticket;
+            ca.list = e->list; ca.count = e->count; ca.masks = e->masks; ca.ticket = e->ticket; ca.total = e->active_total;
             if (wt == PI_TYPE_Q4_0) { ca.zero_dst = e->h; ca.zero_stride = F; ca.fill_bias = L->up_b; ca.fill_relu = 1; }
             STAGE(PI_STAGE_COMPACT, 1, launch_compact(ca, st));
         }
@@ -529,15 +553,11 @@ int pi_engine_profile_step(pi_engine * e, int T, float * host_ms, int * host_lau
     PI_REQUIRE(host_ms, "engine_profile_step: null output");
     cudaStream_t st = (cudaStream_t)stream;
     StageTimer tm;
-    tm.on = true; tm.st = st; tm.acc = host_ms;
-    PI_CUDA(cudaEventCreate(&tm.a));
-    PI_CUDA(cudaEventCreate(&tm.b));
+    tm.on = true; tm.st = st;
     rc = enqueue_step(e, T, st, tm);
-    cudaEventDestroy(tm.a); cudaEventDestroy(tm.b);
-    if (rc) return rc;
+    if (rc) { cudaStreamSynchronize(st); return rc; }
     if (host_launches) *host_launches = e->launches;
-    PI_CUDA(cudaStreamSynchronize(st));
-    return PI_OK;
+    return tm.collect(host_ms);
 }
 
 int pi_engine_status(pi_engine * e, void * stream) {
@@ -565,6 +585,15 @@ int pi_engine_debug(pi_engine * e, float ** pred, int32_t ** list, int32_t ** co
 }
 
 int pi_engine_launches(pi_engine * e) { return e ? e->launches : 0; }
+
+int pi_engine_active_total(pi_engine * e, int reset, unsigned long long * host_total, void * stream) {
+    PI_REQUIRE(e && host_total, "engine_active_total: null");
+    cudaStream_t st = (cudaStream_t)stream;
+    PI_CUDA(cudaMemcpyAsync(host_total, e->active_total, 8, cudaMemcpyDeviceToHost, st));
+    if (reset) PI_CUDA(cudaMemsetAsync(e->active_total, 0, 8, st));
+    PI_CUDA(cudaStreamSynchronize(st));
+    return PI_OK;
+}
 
 #pragma GCC visibility pop
 }  // extern "C"

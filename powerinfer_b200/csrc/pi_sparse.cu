@@ -20,6 +20,7 @@ struct CompactP {
     uint32_t * masks; unsigned int * ticket;
     float * zero_dst; int64_t zero_stride;
     const float * fill_bias; int fill_relu;
+    unsigned long long * total;
 };
 
 __global__ void __launch_bounds__(COMPACT_THREADS) k_compact(const CompactP p) {
@@ -78,7 +79,10 @@ __global__ void __launch_bounds__(COMPACT_THREADS) k_compact(const CompactP p) {
             p.list[off++] = c * 32 + bit;
         }
     }
-    if (tid == COMPACT_THREADS - 1) { *p.count = base + incl; *p.ticket = 0u; }
+    if (tid == COMPACT_THREADS - 1) {
+        *p.count = base + incl; *p.ticket = 0u;
+        if (p.total) *p.total += (unsigned long long)(base + incl);      // only this thread of this CTA ever writes it
+    }
 }
 
 int launch_compact(const CompactArgs & a, cudaStream_t st) {
@@ -86,7 +90,7 @@ int launch_compact(const CompactArgs & a, cudaStream_t st) {
     p.idx = a.idx; p.idx_stride = a.idx_stride; p.T = a.T; p.threshold = a.threshold;
     p.n_local = (int)a.n_local; p.bucket = a.bucket; p.list = a.list; p.count = a.count;
     p.masks = a.masks; p.ticket = a.ticket;
-    p.zero_dst = a.zero_dst; p.zero_stride = a.zero_stride; p.fill_bias = a.fill_bias; p.fill_relu = a.fill_relu;
+    p.zero_dst = a.zero_dst; p.zero_stride = a.zero_stride; p.fill_bias = a.fill_bias; p.fill_relu = a.fill_relu; p.total = a.total;
     const int n_chunks = (int)((a.n_local + 31) / 32);
     int grid = (n_chunks + COMPACT_THREADS / 32 - 1) / (COMPACT_THREADS / 32);
     grid = max(1, min(grid, sm_count()));

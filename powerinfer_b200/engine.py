@@ -62,6 +62,7 @@ for _name, _res, _args in [
     ("pi_engine_debug", C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp)]),
     ("pi_engine_launches", C.c_int, [_vp]),
     ("pi_engine_set_trace", C.c_int, [_vp, _vp]),
+    ("pi_engine_active_total", C.c_int, [_vp, C.c_int, C.POINTER(C.c_uint64), _vp]),
     ("pi_device_malloc", C.c_int, [C.POINTER(_vp), C.c_size_t]),
     ("pi_device_free", C.c_int, [_vp]),
     ("pi_ipc_export", C.c_int, [_vp, _vp]),
@@ -73,7 +74,7 @@ for _name, _res, _args in [
 
 ENGINE_EXPORTS = ["pi_engine_workspace_bytes", "pi_engine_kv_bytes", "pi_engine_create", "pi_engine_destroy",
                   "pi_engine_set_exchange", "pi_engine_io", "pi_engine_decode", "pi_engine_advance", "pi_engine_decode_host",
-                  "pi_engine_profile_step", "pi_engine_status", "pi_engine_debug", "pi_engine_launches", "pi_engine_set_trace",
+                  "pi_engine_profile_step", "pi_engine_status", "pi_engine_debug", "pi_engine_launches", "pi_engine_set_trace", "pi_engine_active_total",
                   "pi_device_malloc", "pi_device_free", "pi_ipc_export", "pi_ipc_import", "pi_ipc_close"]
 
 
@@ -260,6 +261,11 @@ class DecodeEngine:
         launches = C.c_int(0)
         check(lib.pi_engine_profile_step(self.handle, T, ms, C.byref(launches), self.st))
         return {STAGE_NAMES[i]: ms[i] for i in range(N_STAGES)}, launches.value
+
+    def active_total(self, reset: bool = True) -> int:
+        v = C.c_uint64(0)
+        check(lib.pi_engine_active_total(self.handle, 1 if reset else 0, C.byref(v), self.st))
+        return v.value
 
     def launches(self) -> int:
         return lib.pi_engine_launches(self.handle)
