@@ -43,14 +43,14 @@ static int check_w(int wtype, int64_t ncols, const void * W) {
     return PI_OK;
 }
 
-struct SparseScratch { int32_t * list; int32_t * count; unsigned int * ticket; uint32_t * masks; };
+struct SparseScratch { int32_t * list; int32_t * count; unsigned int * ticket; unsigned int * status; uint32_t * masks; };
 
 static bool carve_sparse(Scratch & s, int64_t n_rows, SparseScratch & o) {
     o.list = (int32_t *)s.take((size_t)n_rows * 4);
     int32_t * ct = (int32_t *)s.take(256);
     o.masks = (uint32_t *)s.take((size_t)((n_rows + 31) / 32) * 4);
     if (!o.list || !ct || !o.masks) return false;
-    o.count = ct; o.ticket = (unsigned int *)(ct + 1);
+    o.count = ct; o.ticket = (unsigned int *)(ct + 1); o.status = (unsigned int *)(ct + 2);
     return true;
 }
 
@@ -172,7 +172,7 @@ int pi_mul_mat_idx(int wtype, const void * W, int64_t n_w_rows, int64_t ncols,
     if (!aligned(workspace, 256) || !actp || !carve_sparse(s, n_w_rows, ss)) { set_error("mul_mat_idx: workspace too small or misaligned"); return PI_ERR_WORKSPACE; }
     ActBuf act = act_carve(wtype, ncols, T, &actp);
     if (bucket) PI_CUDA(cudaMemsetAsync(dst, 0, (size_t)T * n_dst_rows * 4, st));      // rows held elsewhere read 0
-    PI_CUDA(cudaMemsetAsync(ss.count, 0, 8, st));                                       // count and ticket
+    PI_CUDA(cudaMemsetAsync(ss.count, 0, 12, st));                                      // count, ticket, status
     if (n_w_rows == 0) return PI_OK;
     if ((rc = launch_convert_act(wtype, x, ncols, ncols, T, act, st))) return rc;
     CompactArgs c;
@@ -183,7 +183,7 @@ int pi_mul_mat_idx(int wtype, const void * W, int64_t n_w_rows, int64_t ncols,
     GemvArgs g;
     g.wtype = wtype; g.W = W; g.nrows = n_w_rows; g.ncols = ncols; g.x = act.view(); g.T = T;
     g.list = ss.list; g.count = ss.count; g.bucket = bucket; g.idx = idx; g.idx_stride = idx_stride; g.threshold = threshold;
-    g.dst = dst; g.dst_stride = n_dst_rows;
+    g.dst = dst; g.dst_stride = n_dst_rows; g.status = ss.status;
     return launch_gemv(g, st);
 }
 
@@ -210,18 +210,19 @@ int pi_axpy(int wtype, const void * Wt, int64_t n_w_rows, int64_t ncols,
     }
     float * partial = ok ? (float *)s.take((size_t)G * T * ncols * 4) : nullptr;
     if (!ok || !partial) { set_error("axpy: workspace too small or misaligned"); return PI_ERR_WORKSPACE; }
-    PI_CUDA(cudaMemsetAsync(ss.count, 0, 8, st));
+    PI_CUDA(cudaMemsetAsync(ss.count, 0, 12, st));                                      // count, ticket, status
     CompactArgs c;
     c.idx = idx; c.idx_stride = idx_stride; c.T = T; c.threshold = threshold; c.n_local = n_w_rows; c.bucket = bucket;
     c.list = ss.list; c.count = ss.count; c.masks = ss.masks; c.ticket = ss.ticket;
     if ((rc = launch_compact(c, st))) return rc;
-    if (wtype == PI_TYPE_Q4_0 && (rc = launch_neuron_q8(h, h_stride, h_stride, T, cq, cd, st))) return rc;
+    if (wtype == PI_TYPE_Q4_0 && T > 1 && (rc = launch_neuron_q8(h, h_stride, h_stride, T, cq, cd, st))) return rc;
     AxpyArgs a;
     a.wtype = wtype; a.Wt = Wt; a.nrows = n_w_rows; a.ncols = ncols; a.h = h; a.h_stride = h_stride; a.T = T;
     a.list = ss.list; a.count = ss.count; a.bucket = bucket; a.idx = idx; a.idx_stride = idx_stride; a.threshold = threshold;
-    a.cq = cq; a.cd = cd; a.c_stride = h_stride; a.partial = partial; a.n_groups = G;
-    if ((rc = launch_axpy(a, st))) return rc;
-    return launch_reduce_partials(partial, G, T, ncols, nullptr, nullptr, dst, st);
+    a.cq = cq; a.cd = cd; a.c_stride = h_stride; a.partial = partial; a.n_groups = G; a.status = ss.status;
+    int used = G;
+    if ((rc = launch_axpy(a, st, &used))) return rc;
+    return launch_reduce_partials(partial, used, T, ncols, nullptr, nullptr, dst, st);
 }
 
 int pi_norm(const float * x, int T, int64_t n, int rms, float eps, const float * w, const float * b, float * y, void * stream) {

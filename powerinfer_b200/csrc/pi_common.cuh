@@ -105,8 +105,11 @@ struct GemvArgs {
     __half * dst16 = nullptr;          // optional FP16 copy of the result [T, dst_stride] (feeds an F16 mat-vec)
     // second matrix sharing the row selection (gate with up): dst = relu(W2 row . x) * (W row . x)
     const void * W2 = nullptr;
+    unsigned int * status = nullptr;   // device status word; when given, T == 1 shapes use the bulk-copy ring kernel
+    bool pdl = false;                  // launch with programmatic dependent launch (the kernel waits for its producer itself)
 };
 int launch_gemv(const GemvArgs & a, cudaStream_t st);
+int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaStream_t st);   // PI_ERR_UNSUPPORTED: not eligible
 
 // predictor logits -> compacted list of LOCAL rows active for >= 1 token; also writes zeros (or relu(bias)) into
 // h_init [T, h_stride] for rows that are inactive for a token when h_init != nullptr
@@ -119,6 +122,7 @@ struct CompactArgs {
     uint32_t * masks = nullptr;        // scratch: one word per 32 local rows
     unsigned int * ticket = nullptr;   // scratch: one word, must be 0 on entry, is 0 again on exit
     unsigned long long * total = nullptr;   // optional running sum of the counts (statistics)
+    bool pdl = false;
 };
 int launch_compact(const CompactArgs & a, cudaStream_t st);
 
@@ -130,16 +134,19 @@ struct AxpyArgs {
     const float * idx = nullptr; int64_t idx_stride = 0; float threshold = 0.f;
     // Q4_0: coefficient planes made by launch_neuron_q8 (int8 by global id, float scale per 32-neuron block)
     const int8_t * cq = nullptr; const float * cd = nullptr; int64_t c_stride = 0;
-    float * partial = nullptr; int n_groups = 0;                      // [n_groups, T, ncols]
+    float * partial = nullptr; int n_groups = 0;                      // [n_groups, T, ncols]: room for n_groups partial vectors
+    unsigned int * status = nullptr;                                  // device status word (bit 1: a copy wait ran out); enables the
+                                                                      // bulk-copy pipelined kernel for T == 1
+    bool pdl = false;
 };
 int axpy_groups(int wtype, int64_t ncols, int T);                     // row groups the launcher will use
-int launch_axpy(const AxpyArgs & a, cudaStream_t st);
+int launch_axpy(const AxpyArgs & a, cudaStream_t st, int * groups_used = nullptr);   // groups_used: partial vectors written
 // h F32 [T, stride] -> Q8_0 over 32-neuron blocks: cq int8 [T, stride], cd float [T, stride/32]
 int launch_neuron_q8(const float * h, int64_t stride, int64_t n, int T, int8_t * cq, float * cd, cudaStream_t st);
 
 // sum partial [n_groups, T, n] in group order (+ residual + bias) -> dst [T, n]
 int launch_reduce_partials(const float * partial, int n_groups, int T, int64_t n, const float * residual,
-                           const float * bias, float * dst, cudaStream_t st);
+                           const float * bias, float * dst, cudaStream_t st, bool pdl = false);
 
 struct NormArgs {
     const float * x = nullptr; int T = 1; int64_t n = 0; int rms = 1; float eps = 0.f;
@@ -156,6 +163,7 @@ struct NormArgs {
     float * y = nullptr;               // optional F32 output
     int act_type = 0; ActBuf act;      // optional activation planes of the normalised vector (0: none, else PI_TYPE_*)
     int act2_type = 0; ActBuf act2; int act2_src = 1;   // second set of planes, of the input (src 0) or the output (src 1)
+    bool pdl = false;
 };
 int launch_norm(const NormArgs & a, cudaStream_t st);
 
@@ -170,6 +178,7 @@ struct AttnArgs {
     const float * cs = nullptr; int neox = 0;          // fused RoPE of q and k from the angle table (nullptr: already rotated)
     float * out = nullptr;                             // optional F32 [T, n_head*head_dim]
     int out_act_type = 0; ActBuf out_act;              // optional activation planes of the output
+    bool pdl = false;
 };
 int launch_attention(const AttnArgs & a, cudaStream_t st);
 
@@ -180,6 +189,24 @@ int launch_exchange_push(const pi_exchange & x, const float * partial, int n_gro
 
 // ------------------------------------------------------------------------------------ device primitives
 #ifdef __CUDACC__
+
+// Programmatic dependent launch.  A kernel launched with launch_k(..., pdl = true) may start while its predecessor in the
+// stream is still running; it must call pdl_wait() before it reads anything the predecessor wrote and before it writes
+// anything the predecessor may still read (weights are immutable, so prefetching them before the wait is safe).
+// pdl_launch() lets the NEXT kernel be scheduled early.  Both are no-ops for a normally launched kernel.
+__device__ __forceinline__ void pdl_wait()   { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 
 __device__ __forceinline__ uint4 ldg_stream(const void * p) {     // read-once weights: bypass L1 allocation
     uint4 v;

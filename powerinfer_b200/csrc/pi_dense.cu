@@ -74,6 +74,8 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
     __shared__ double s_red[32];
     const int t = blockIdx.x;
     const int64_t n = p.n;
+    pdl_wait();
+    pdl_launch();
     const size_t tn = p.partial_stride ? (size_t)p.partial_stride : (size_t)p.T * n;
     const float * partial = p.partial;
     if (p.wait_flags) {
@@ -200,8 +202,7 @@ int launch_norm(const NormArgs & a, cudaStream_t st) {
     p.y = a.y; p.act_type = a.act_type; p.act = a.act; p.act2_type = a.act2_type; p.act2 = a.act2; p.act2_src = a.act2_src;
     int threads = (int)((a.n / 8 + NORM_CHUNKS - 1) / NORM_CHUNKS);
     threads = min(1024, max(32, (threads + 31) / 32 * 32));
-    k_norm<<<a.T, threads, 0, st>>>(p);
-    PI_LAUNCH_CHECK("k_norm");
+    PI_CUDA(launch_k(k_norm, dim3(a.T), dim3(threads), 0, st, a.pdl, p));
     return PI_OK;
 }
 
@@ -244,7 +245,9 @@ int launch_rope(float * x, int T, int n_heads, int head_dim, const int32_t * pos
 // (rounded to FP16, exactly what was stored) so no CTA depends on another one's store.
 // CPU-path numerics: q and the probabilities are rounded to FP16 before the dot products; exp() goes through FP16
 // in and out (the reference uses a table of FP16(expf(FP16))); the normaliser is summed in double.
-static constexpr int ATTN_THREADS = 256;
+// Latency-bound (the whole KV of a layer is ~1 MB): the score pass gives every thread one cached position and issues
+// its head_dim/8 128-bit loads back to back; the value pass splits positions over ATTN_THREADS/(head_dim/8) slices.
+static constexpr int ATTN_THREADS = 512;
 
 struct AttnP {
     const float * q; const float * k; const float * v; __half * k_cache; __half * v_cache;
@@ -253,21 +256,31 @@ struct AttnP {
     float * out; ActBuf out_act; int out_act_type;
 };
 
+__device__ __forceinline__ float dot8(const uint4 kv, const float * __restrict__ q) {
+    const float2 k0 = h2f(kv.x), k1 = h2f(kv.y), k2 = h2f(kv.z), k3 = h2f(kv.w);
+    float a = k0.x * q[0];
+    a = fmaf(k0.y, q[1], a); a = fmaf(k1.x, q[2], a); a = fmaf(k1.y, q[3], a);
+    a = fmaf(k2.x, q[4], a); a = fmaf(k2.y, q[5], a); a = fmaf(k3.x, q[6], a); a = fmaf(k3.y, q[7], a);
+    return a;
+}
+
 __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ double s_red[32];
+    __shared__ double s_red[ATTN_THREADS / 32];
     __shared__ float s_max[ATTN_THREADS / 32];
     const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const int hd = p.hd, half = hd / 2;
+    const int hd = p.hd, half = hd / 2, chunks = hd / 8;
     const int group = p.n_head / p.n_head_kv, hk = h / group;
     const int dkv = p.n_head_kv * hd;
+    pdl_wait();
+    pdl_launch();
     const int pos = p.pos[t];
     const int sq = p.seq ? p.seq[t] : 0;
     if (pos < 0 || pos >= p.n_ctx) return;                       // never index the cache out of range
 
     float *  sc  = reinterpret_cast<float *>(smem_raw);          // scores, then exp values, then the output slices
-    __half * q16 = reinterpret_cast<__half *>(sc + p.sc_floats); // [hd]   (sc_floats = max(n_ctx, slices*hd))
-    __half * k16 = q16 + hd;                                     // [hd] the new token's K
+    float *  q32 = sc + p.sc_floats;                             // [hd] q rounded to FP16, widened
+    __half * k16 = reinterpret_cast<__half *>(q32 + hd);         // [hd] the new token's K
     __half * v16 = k16 + hd;                                     // [hd] the new token's V
     __half * p16 = v16 + hd;                                     // [n_ctx] probabilities in FP16
 
@@ -281,12 +294,12 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
             const int i0 = p.neox ? k : 2 * k, i1 = p.neox ? k + half : 2 * k + 1;
             float o0, o1;
             rope_pair(qh[i0], qh[i1], a.x, a.y, o0, o1);
-            q16[i0] = __float2half_rn(o0); q16[i1] = __float2half_rn(o1);
+            q32[i0] = round_f16(o0); q32[i1] = round_f16(o1);
             rope_pair(kh[i0], kh[i1], a.x, a.y, o0, o1);
             k16[i0] = __float2half_rn(o0); k16[i1] = __float2half_rn(o1);
         }
     } else {
-        for (int e = tid; e < hd; e += ATTN_THREADS) { q16[e] = __float2half_rn(qh[e]); k16[e] = __float2half_rn(kh[e]); }
+        for (int e = tid; e < hd; e += ATTN_THREADS) { q32[e] = round_f16(qh[e]); k16[e] = __float2half_rn(kh[e]); }
     }
     __syncthreads();
     __half * kc = p.k_cache + (size_t)sq * p.n_ctx * dkv + (size_t)hk * hd;
@@ -298,21 +311,30 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
         }
     }
 
-    // ---- scores: one warp per position, lanes split head_dim
+    // ---- scores: one thread per position; the new token's K comes from shared memory
     const float scale = 1.0f / sqrtf((float)hd);
     float mx = -INFINITY;
-    for (int j = wid; j <= pos; j += ATTN_THREADS / 32) {
-        const __half * kr = j == pos ? k16 : kc + (size_t)j * dkv;
+    for (int j = tid; j <= pos; j += ATTN_THREADS) {
         float a = 0.f;
-        for (int e = lane * 2; e < hd; e += 64) {
-            const float2 kk = __half22float2(*reinterpret_cast<const __half2 *>(kr + e));
-            const float2 qq = __half22float2(*reinterpret_cast<const __half2 *>(q16 + e));
-            a = fmaf(kk.x, qq.x, a); a = fmaf(kk.y, qq.y, a);
+        if (j < pos) {
+            const uint4 * kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * dkv);
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int c = 0; c < chunks; c += 4) {
+                uint4 kv[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) kv[u] = __ldg(kr + c + u);               // chunks % 4 == 0 (head_dim % 32 == 0)
+#pragma unroll
+                for (int u = 0; u < 4; u++) part[u] += dot8(kv[u], q32 + (c + u) * 8);
+            }
+            a = (part[0] + part[1]) + (part[2] + part[3]);
+        } else {
+            for (int c = 0; c < chunks; c++) a += dot8(reinterpret_cast<const uint4 *>(k16)[c], q32 + c * 8);
         }
-        a = warp_sum(a) * scale;
-        if (lane == 0) sc[j] = a;
+        a *= scale;
+        sc[j] = a;
         mx = fmaxf(mx, a);
     }
+    mx = warp_max(mx);
     if (lane == 0) s_max[wid] = mx;
     __syncthreads();
     mx = s_max[0];
@@ -322,15 +344,15 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     // ---- softmax (ggml.c:10708-10777)
     double part = 0.0;
     for (int j = tid; j <= pos; j += ATTN_THREADS) {
-        const float arg = __half2float(__float2half_rn(sc[j] - mx));
-        const float e = __half2float(__float2half_rn(expf(arg)));
+        const float arg = round_f16(sc[j] - mx);
+        const float e = round_f16(expf(arg));
         sc[j] = e;
         part += (double)e;
     }
+    part = warp_sum_d(part);
+    if (lane == 0) s_red[wid] = part;
+    __syncthreads();
     {
-        part = warp_sum_d(part);
-        if (lane == 0) s_red[wid] = part;
-        __syncthreads();
         double tot = 0.0;
         for (int i = 0; i < ATTN_THREADS / 32; i++) tot += s_red[i];
         const float inv = (float)(1.0 / tot);
@@ -338,28 +360,44 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     }
     __syncthreads();
 
-    // ---- out[e] = sum_j p_j V[j, e]: threads split (e pairs) x (position slices), slices reduced through smem
-    const int pairs = half;                                        // hd/2 half2 columns
-    const int slices = ATTN_THREADS / pairs > 0 ? ATTN_THREADS / pairs : 1;
-    float * red = sc;                                              // scores are dead: reuse as [slices][hd]
-    float ax = 0.f, ay = 0.f;
-    const int e2 = tid % pairs, sl = tid / pairs;
+    // ---- out[e] = sum_j p_j V[j, e]: thread = (chunk of 8 columns, slice of positions); slices reduced through smem
+    const int slices = ATTN_THREADS / chunks;
+    const int c8 = tid % chunks, sl = tid / chunks;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (sl < slices) {
-        for (int j = sl; j <= pos; j += slices) {
-            const __half * vr = j == pos ? v16 : vc + (size_t)j * dkv;
-            const float2 vv = __half22float2(*reinterpret_cast<const __half2 *>(vr + 2 * e2));
-            const float pj = __half2float(p16[j]);
-            ax = fmaf(pj, vv.x, ax); ay = fmaf(pj, vv.y, ay);
+        for (int j0 = sl; j0 <= pos; j0 += slices * 4) {
+            uint4 vv[4]; float pj[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int j = j0 + u * slices;
+                pj[u] = 0.f; vv[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (j <= pos) {
+                    pj[u] = __half2float(p16[j]);
+                    vv[u] = j == pos ? reinterpret_cast<const uint4 *>(v16)[c8]
+                                     : __ldg(reinterpret_cast<const uint4 *>(vc + (size_t)j * dkv) + c8);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float2 v0 = h2f(vv[u].x), v1 = h2f(vv[u].y), v2 = h2f(vv[u].z), v3 = h2f(vv[u].w);
+                acc[0] = fmaf(pj[u], v0.x, acc[0]); acc[1] = fmaf(pj[u], v0.y, acc[1]);
+                acc[2] = fmaf(pj[u], v1.x, acc[2]); acc[3] = fmaf(pj[u], v1.y, acc[3]);
+                acc[4] = fmaf(pj[u], v2.x, acc[4]); acc[5] = fmaf(pj[u], v2.y, acc[5]);
+                acc[6] = fmaf(pj[u], v3.x, acc[6]); acc[7] = fmaf(pj[u], v3.y, acc[7]);
+            }
         }
     }
-    __syncthreads();                                               // everyone is done reading sc as probabilities
-    if (sl < slices) { red[sl * hd + 2 * e2] = ax; red[sl * hd + 2 * e2 + 1] = ay; }
+    float * red = sc;                                              // exp values are dead: reuse as [slices][hd]
+    if (sl < slices) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) red[sl * hd + c8 * 8 + j] = acc[j];
+    }
     __syncthreads();
     for (int e = tid; e < hd; e += ATTN_THREADS) {
         float o = 0.f;
         for (int s = 0; s < slices; s++) o += red[s * hd + e];
         if (p.out) p.out[((size_t)t * p.n_head + h) * hd + e] = o;
-        red[e] = o;                                                // slice 0 row now holds the final value
+        red[e] = o;                                                // slice 0 row now holds the final value (own column only)
     }
     if (p.out_act_type) {
         __syncthreads();
@@ -386,9 +424,9 @@ int launch_attention(const AttnArgs & a, cudaStream_t st) {
     p.kv_stride = a.kv_stride ? a.kv_stride : (int64_t)a.n_head_kv * a.head_dim;
     p.cs = a.cs; p.neox = a.neox; p.out = a.out; p.out_act = a.out_act; p.out_act_type = a.out_act_type;
     // sc must hold max(n_ctx, slices*hd) floats
-    const int slices = ATTN_THREADS / (a.head_dim / 2) > 0 ? ATTN_THREADS / (a.head_dim / 2) : 1;
-    const size_t sc_floats = (size_t)max(a.n_ctx, slices * a.head_dim);
-    const size_t smem = sc_floats * 4 + (size_t)3 * a.head_dim * 2 + (size_t)a.n_ctx * 2 + 16;
+    const int slices = ATTN_THREADS / (a.head_dim / 8);
+    const size_t sc_floats = (size_t)((max(a.n_ctx, slices * a.head_dim) + 3) / 4 * 4);
+    const size_t smem = sc_floats * 4 + (size_t)a.head_dim * 4 + (size_t)2 * a.head_dim * 2 + (size_t)a.n_ctx * 2 + 16;
     p.sc_floats = (int)sc_floats;
     static bool attr_set[16] = {false};
     int dev = 0;
@@ -399,8 +437,7 @@ int launch_attention(const AttnArgs & a, cudaStream_t st) {
     }
     PI_REQUIRE(smem <= 200 * 1024, "attention: n_ctx=%d needs %zu bytes of shared memory", a.n_ctx, smem);
     const dim3 grid(a.n_head, a.T);
-    k_attention<<<grid, ATTN_THREADS, smem, st>>>(p);
-    PI_LAUNCH_CHECK("k_attention");
+    PI_CUDA(launch_k(k_attention, grid, dim3(ATTN_THREADS), smem, st, a.pdl, p));
     return PI_OK;
 }
 

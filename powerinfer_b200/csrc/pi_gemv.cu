@@ -12,7 +12,8 @@ namespace pi {
 
 static constexpr int QK = 32;
 static constexpr int GEMV_THREADS = 256;
-static constexpr int UNROLL = 4;
+static constexpr int GEMV_WARPS = GEMV_THREADS / 32;
+static constexpr int LOADS = 16;          // 128-bit weight loads one lane keeps in flight (split over the rows it works on)
 
 struct GemvP {
     const uint8_t * W; const uint8_t * W2;
@@ -24,37 +25,9 @@ struct GemvP {
     float * dst; __half * dst16; int64_t dst_stride;
 };
 
-// dot of one FP16 row with TT staged FP16 activation vectors
-template <int TT>
-__device__ __forceinline__ void row_dot_f16(const uint8_t * __restrict__ row, int ncols, const __half * __restrict__ xs,
-                                            int lane, float (&acc)[TT]) {
-    for (int c0 = lane * 8; c0 < ncols; c0 += 256 * UNROLL) {
-        uint4 w[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; u++) {
-            const int c = c0 + u * 256;
-            if (c < ncols) w[u] = ldg_stream(row + (size_t)c * 2);
-        }
-#pragma unroll
-        for (int u = 0; u < UNROLL; u++) {
-            const int c = c0 + u * 256;
-            if (c < ncols) {
-                const float2 w0 = h2f(w[u].x), w1 = h2f(w[u].y), w2 = h2f(w[u].z), w3 = h2f(w[u].w);
-#pragma unroll
-                for (int t = 0; t < TT; t++) {
-                    const uint4 xv = *reinterpret_cast<const uint4 *>(xs + (size_t)t * ncols + c);
-                    const float2 x0 = h2f(xv.x), x1 = h2f(xv.y), x2 = h2f(xv.z), x3 = h2f(xv.w);
-                    float a = acc[t];
-                    a = fmaf(w0.x, x0.x, a); a = fmaf(w0.y, x0.y, a);
-                    a = fmaf(w1.x, x1.x, a); a = fmaf(w1.y, x1.y, a);
-                    a = fmaf(w2.x, x2.x, a); a = fmaf(w2.y, x2.y, a);
-                    a = fmaf(w3.x, x3.x, a); a = fmaf(w3.y, x3.y, a);
-                    acc[t] = a;
-                }
-            }
-        }
-    }
-}
+struct SmemQ8 {            // staged Q8_0 planes of TT tokens
+    const uint4 * lo; const uint4 * hi; const float * d; const int * s;
+};
 
 // Integer dot of one Q4_0 block (16 bytes of nibbles) with one Q8_0 block held as two planes (values 0..15, 16..31).
 // Nibbles are taken as 0..15 and the offset of 8 is removed with the block's int8 sum: sum((q-8) x) = sum(q x) - 8 sum(x).
@@ -71,43 +44,99 @@ __device__ __forceinline__ int block_dot_q4_q8(const uint4 q, const uint4 lo, co
     return sumi - 8 * s8;
 }
 
-struct SmemQ8 {            // staged Q8_0 planes of TT tokens
-    const uint4 * lo; const uint4 * hi; const float * d; const int * s;
-};
-
-template <int TT>
-__device__ __forceinline__ void row_dot_q4(const uint8_t * __restrict__ row, int nb, const SmemQ8 xs, int lane,
-                                           float (&acc)[TT]) {
-    const uint4 * qrow = reinterpret_cast<const uint4 *>(row);
-    const __half * srow = reinterpret_cast<const __half *>(row + (size_t)nb * 16);
-    for (int b0 = lane; b0 < nb; b0 += 32 * UNROLL) {
-        uint4 q[UNROLL];
-        __half sc[UNROLL];
+// Dots of NR weight rows (same column range [c_lo, c_hi) of each) with TT staged activation vectors.  All NR x U loads of
+// a column batch are issued before any of them is consumed.  FP16: a lane owns 8 consecutive columns per 256-column
+// step.  rows[i] == nullptr skips row i.
+template <int TT, int NR>
+__device__ __forceinline__ void rows_dot_f16(const uint8_t * const (&rows)[NR], int c_lo, int c_hi, int ncols,
+                                             const __half * __restrict__ xs, int lane, float (&acc)[NR][TT]) {
+    constexpr int U = LOADS / NR;
+    for (int c0 = c_lo + lane * 8; c0 < c_hi; c0 += 256 * U) {
+        uint4 w[NR][U];
 #pragma unroll
-        for (int u = 0; u < UNROLL; u++) {
-            const int b = b0 + u * 32;
-            if (b < nb) { q[u] = ldg_stream(qrow + b); sc[u] = __ldg(srow + b); }
-        }
+        for (int r = 0; r < NR; r++)
 #pragma unroll
-        for (int u = 0; u < UNROLL; u++) {
-            const int b = b0 + u * 32;
-            if (b < nb) {
-                const float d4 = __half2float(sc[u]);
+            for (int u = 0; u < U; u++) {
+                const int c = c0 + u * 256;
+                if (rows[r] && c < c_hi) w[r][u] = ldg_stream(rows[r] + (size_t)c * 2);
+            }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int c = c0 + u * 256;
+            if (c < c_hi) {
 #pragma unroll
                 for (int t = 0; t < TT; t++) {
-                    const int i = t * nb + b;
-                    const int sumi = block_dot_q4_q8(q[u], xs.lo[i], xs.hi[i], xs.s[i]);
-                    acc[t] = fmaf((float)sumi, d4 * xs.d[i], acc[t]);
+                    const uint4 xv = *reinterpret_cast<const uint4 *>(xs + (size_t)t * ncols + c);
+                    const float2 x0 = h2f(xv.x), x1 = h2f(xv.y), x2 = h2f(xv.z), x3 = h2f(xv.w);
+#pragma unroll
+                    for (int r = 0; r < NR; r++) {
+                        if (!rows[r]) continue;
+                        const float2 w0 = h2f(w[r][u].x), w1 = h2f(w[r][u].y), w2 = h2f(w[r][u].z), w3 = h2f(w[r][u].w);
+                        float a = acc[r][t];
+                        a = fmaf(w0.x, x0.x, a); a = fmaf(w0.y, x0.y, a);
+                        a = fmaf(w1.x, x1.x, a); a = fmaf(w1.y, x1.y, a);
+                        a = fmaf(w2.x, x2.x, a); a = fmaf(w2.y, x2.y, a);
+                        a = fmaf(w3.x, x3.x, a); a = fmaf(w3.y, x3.y, a);
+                        acc[r][t] = a;
+                    }
                 }
             }
         }
     }
 }
 
-template <int WT, int TT, bool SPARSE, bool GATED>
+// planar Q4_0: a lane owns one 32-column block per 32-block step; [b_lo, b_hi) is the block range
+template <int TT, int NR>
+__device__ __forceinline__ void rows_dot_q4(const uint8_t * const (&rows)[NR], int b_lo, int b_hi, int nb, const SmemQ8 xs,
+                                            int lane, float (&acc)[NR][TT]) {
+    constexpr int U = LOADS / NR;
+    for (int b0 = b_lo + lane; b0 < b_hi; b0 += 32 * U) {
+        uint4 q[NR][U];
+        __half sc[NR][U];
+#pragma unroll
+        for (int r = 0; r < NR; r++)
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int b = b0 + u * 32;
+                if (rows[r] && b < b_hi) {
+                    q[r][u] = ldg_stream(reinterpret_cast<const uint4 *>(rows[r]) + b);
+                    sc[r][u] = __ldg(reinterpret_cast<const __half *>(rows[r] + (size_t)nb * 16) + b);
+                }
+            }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int b = b0 + u * 32;
+            if (b < b_hi) {
+#pragma unroll
+                for (int t = 0; t < TT; t++) {
+                    const int i = t * nb + b;
+                    const uint4 lo = xs.lo[i], hi = xs.hi[i];
+                    const int s8 = xs.s[i];
+                    const float d8 = xs.d[i];
+#pragma unroll
+                    for (int r = 0; r < NR; r++) {
+                        if (!rows[r]) continue;
+                        const int sumi = block_dot_q4_q8(q[r][u], lo, hi, s8);
+                        acc[r][t] = fmaf((float)sumi, __half2float(sc[r][u]) * d8, acc[r][t]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// One work item = one row (dense) or one list entry (sparse), optionally split column-wise over SPLIT warps of the same
+// CTA.  A warp works on PAIR items at once (and on the gate row of each, when GATED), so NR = PAIR x (GATED ? 2 : 1) rows
+// are streamed together.  The CTA-level loop is uniform, so the shared-memory combine of split rows may synchronise.
+template <int WT, int TT, bool SPARSE, bool GATED, int SPLIT, int PAIR>
 __global__ void __launch_bounds__(GEMV_THREADS) k_gemv(const GemvP p) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int tid = threadIdx.x, lane = tid & 31;
+    __shared__ float s_part[GEMV_WARPS][PAIR * (GATED ? 2 : 1)][TT];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_wait();
+    pdl_launch();
+    constexpr int NR = PAIR * (GATED ? 2 : 1);
+    constexpr int ITEMS_PER_CTA = (GEMV_WARPS / SPLIT) * PAIR;
 
     // ---- stage the activation of TT tokens
     SmemQ8 xq;
@@ -128,47 +157,89 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_gemv(const GemvP p) {
     }
     __syncthreads();
 
-    const int warps_total = gridDim.x * (GEMV_THREADS / 32);
-    const int gw = blockIdx.x * (GEMV_THREADS / 32) + (tid >> 5);
     const int n_items = SPARSE ? min(*p.count, p.nrows) : p.nrows;
+    const int part = warp % SPLIT;
+    const int slot = warp / SPLIT;                                  // which of the CTA's concurrent items this warp serves
 
-    for (int it = gw; it < n_items; it += warps_total) {
-        const int r = SPARSE ? p.list[it] : it;
-        if (SPARSE && (unsigned)r >= (unsigned)p.nrows) continue;       // a damaged list must not turn into a wild read
-        float acc[TT], acc2[TT];
+    for (int base = blockIdx.x * ITEMS_PER_CTA; base < n_items; base += gridDim.x * ITEMS_PER_CTA) {
+        int r[PAIR];
+        const uint8_t * rows[NR];
+        float acc[NR][TT];
 #pragma unroll
-        for (int t = 0; t < TT; t++) { acc[t] = 0.f; acc2[t] = 0.f; }
-        const uint8_t * row = p.W + (size_t)r * p.row_bytes;
+        for (int k = 0; k < PAIR; k++) {
+            const int it = base + slot * PAIR + k;
+            int rr = -1;
+            if (it < n_items) {
+                rr = SPARSE ? p.list[it] : it;
+                if ((unsigned)rr >= (unsigned)p.nrows) rr = -1;    // a damaged list must not turn into a wild read
+            }
+            r[k] = rr;
+            rows[k] = rr >= 0 ? p.W + (size_t)rr * p.row_bytes : nullptr;
+            if (GATED) rows[PAIR + k] = rr >= 0 ? p.W2 + (size_t)rr * p.row_bytes : nullptr;
+        }
+#pragma unroll
+        for (int i = 0; i < NR; i++)
+#pragma unroll
+            for (int t = 0; t < TT; t++) acc[i][t] = 0.f;
+
         if (WT == PI_TYPE_F16) {
-            row_dot_f16<TT>(row, p.ncols, xh, lane, acc);
-            if (GATED) row_dot_f16<TT>(p.W2 + (size_t)r * p.row_bytes, p.ncols, xh, lane, acc2);
+            const int per = p.ncols / SPLIT;                          // SPLIT > 1 only when ncols % (256 * SPLIT) == 0
+            rows_dot_f16<TT, NR>(rows, part * per, (part + 1) * per, p.ncols, xh, lane, acc);
         } else {
-            row_dot_q4<TT>(row, p.nb, xq, lane, acc);
-            if (GATED) row_dot_q4<TT>(p.W2 + (size_t)r * p.row_bytes, p.nb, xq, lane, acc2);
+            const int per = p.nb / SPLIT;
+            rows_dot_q4<TT, NR>(rows, part * per, (part + 1) * per, p.nb, xq, lane, acc);
         }
 #pragma unroll
-        for (int t = 0; t < TT; t++) { acc[t] = warp_sum(acc[t]); if (GATED) acc2[t] = warp_sum(acc2[t]); }
+        for (int i = 0; i < NR; i++)
+#pragma unroll
+            for (int t = 0; t < TT; t++) acc[i][t] = warp_sum(acc[i][t]);
 
-        const int64_t g = SPARSE && p.bucket ? p.bucket[r] : r;
-        if (lane < TT) {
-            float v = 0.f, v2 = 0.f;
+        if (SPLIT > 1) {
+            if (lane == 0) {
 #pragma unroll
-            for (int t = 0; t < TT; t++) if (lane == t) { v = acc[t]; v2 = acc2[t]; }
-            const int t = lane;
-            bool active = true;
-            if (SPARSE) active = p.idx[(size_t)t * p.idx_stride + g] >= p.threshold;
-            float o = active ? v : 0.f;
-            if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
-            if (p.bias) o += p.bias[g];
-            if (p.relu) o = fmaxf(o, 0.f);
-            if (p.dst)   p.dst[(size_t)t * p.dst_stride + g] = o;
-            if (p.dst16) p.dst16[(size_t)t * p.dst_stride + g] = __float2half_rn(o);
+                for (int i = 0; i < NR; i++)
+#pragma unroll
+                    for (int t = 0; t < TT; t++) s_part[warp][i][t] = acc[i][t];
+            }
+            __syncthreads();
+            if (part == 0) {
+#pragma unroll
+                for (int i = 0; i < NR; i++)
+#pragma unroll
+                    for (int t = 0; t < TT; t++) {
+                        float v = s_part[warp][i][t];
+                        for (int q = 1; q < SPLIT; q++) v += s_part[warp + q][i][t];
+                        acc[i][t] = v;
+                    }
+            }
         }
+        if (part == 0) {
+#pragma unroll
+            for (int k = 0; k < PAIR; k++) {
+                if (r[k] < 0) continue;
+                const int64_t g = SPARSE && p.bucket ? p.bucket[r[k]] : r[k];
+                if (lane < TT) {
+                    float v = 0.f, v2 = 0.f;
+#pragma unroll
+                    for (int t = 0; t < TT; t++) if (lane == t) { v = acc[k][t]; if (GATED) v2 = acc[PAIR + k][t]; }
+                    const int t = lane;
+                    bool active = true;
+                    if (SPARSE) active = p.idx[(size_t)t * p.idx_stride + g] >= p.threshold;
+                    float o = active ? v : 0.f;
+                    if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
+                    if (p.bias) o += p.bias[g];
+                    if (p.relu) o = fmaxf(o, 0.f);
+                    if (p.dst)   p.dst[(size_t)t * p.dst_stride + g] = o;
+                    if (p.dst16) p.dst16[(size_t)t * p.dst_stride + g] = __float2half_rn(o);
+                }
+            }
+        }
+        if (SPLIT > 1) __syncthreads();                               // s_part is reused by the next iteration
     }
 }
 
-template <int WT, int TT, bool SPARSE, bool GATED>
-static int launch_inst(const GemvP & p, size_t smem, cudaStream_t st) {
+template <int WT, int TT, bool SPARSE, bool GATED, int SPLIT, int PAIR>
+static int launch_inst(const GemvP & p, size_t smem, cudaStream_t st, bool pdl) {
     // resident CTAs per SM for this instantiation, remembered per (device, shared-memory size) so that replays and
     // stream captures never query the runtime again
     struct Slot { size_t smem; int bps; };
@@ -177,7 +248,7 @@ static int launch_inst(const GemvP & p, size_t smem, cudaStream_t st) {
     int dev = 0;
     PI_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 16) { set_error("gemv: device ordinal %d not supported", dev); return PI_ERR_UNSUPPORTED; }
-    auto kern = k_gemv<WT, TT, SPARSE, GATED>;
+    auto kern = k_gemv<WT, TT, SPARSE, GATED, SPLIT, PAIR>;
     if (!attr_done[dev]) {
         PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_done[dev] = true;
@@ -189,34 +260,50 @@ static int launch_inst(const GemvP & p, size_t smem, cudaStream_t st) {
         if (bps < 1) { set_error("gemv: activation of %zu bytes does not fit in shared memory", smem); return PI_ERR_INVALID; }
         for (auto & s : cache[dev]) if (!s.bps) { s.smem = smem; s.bps = bps; break; }
     }
-    const int warps_per_block = GEMV_THREADS / 32;
+    constexpr int items_per_cta = (GEMV_WARPS / SPLIT) * PAIR;
     int grid = sm_count() * bps;
-    if (!SPARSE) grid = (int)imin64(grid, (p.nrows + warps_per_block - 1) / warps_per_block);
+    if (!SPARSE) grid = (int)imin64(grid, (p.nrows + items_per_cta - 1) / items_per_cta);
     if (grid < 1) grid = 1;
-    kern<<<grid, GEMV_THREADS, smem, st>>>(p);
-    PI_LAUNCH_CHECK("k_gemv");
+    PI_CUDA(launch_k(kern, dim3(grid), dim3(GEMV_THREADS), smem, st, pdl, p));
     return PI_OK;
 }
 
 template <int WT, int TT>
-static int launch_tt(const GemvP & p, bool sparse, bool gated, size_t smem, cudaStream_t st) {
-    if (!sparse) return launch_inst<WT, TT, false, false>(p, smem, st);
-    if (gated)   return launch_inst<WT, TT, true, true>(p, smem, st);
-    return launch_inst<WT, TT, true, false>(p, smem, st);
+static int launch_tt(const GemvP & p, bool sparse, bool gated, size_t smem, cudaStream_t st, bool pdl) {
+    if (TT == 1) {
+        // batch 1 is latency-bound: stream two items per warp, and split long rows of short matrices over 2 or 4 warps
+        // so that enough bytes are in flight (the predictor's fc1 has only `rank` rows of d_model columns)
+        if (gated) return launch_inst<WT, 1, true, true, 1, 2>(p, smem, st, pdl);
+        if (sparse) return launch_inst<WT, 1, true, false, 1, 2>(p, smem, st, pdl);
+        const int unit = WT == PI_TYPE_F16 ? 256 : 32 * 32;          // columns one warp step covers
+        const int64_t warps_wanted = (int64_t)sm_count() * 24;
+        if (p.nrows * 2 <= warps_wanted && p.ncols % (unit * 4) == 0 && p.ncols >= unit * 16)
+            return launch_inst<WT, 1, false, false, 4, 1>(p, smem, st, pdl);
+        if (p.nrows <= warps_wanted && p.ncols % (unit * 2) == 0 && p.ncols >= unit * 8)
+            return launch_inst<WT, 1, false, false, 2, 1>(p, smem, st, pdl);
+        return launch_inst<WT, 1, false, false, 1, 2>(p, smem, st, pdl);
+    }
+    if (!sparse) return launch_inst<WT, TT, false, false, 1, 1>(p, smem, st, pdl);
+    if (gated)   return launch_inst<WT, TT, true, true, 1, 1>(p, smem, st, pdl);
+    return launch_inst<WT, TT, true, false, 1, 1>(p, smem, st, pdl);
 }
 
 template <int WT>
-static int launch_wt(const GemvP & p, int tt, bool sparse, bool gated, size_t smem, cudaStream_t st) {
+static int launch_wt(const GemvP & p, int tt, bool sparse, bool gated, size_t smem, cudaStream_t st, bool pdl) {
     switch (tt) {
-        case 1: return launch_tt<WT, 1>(p, sparse, gated, smem, st);
-        case 2: return launch_tt<WT, 2>(p, sparse, gated, smem, st);
-        case 4: return launch_tt<WT, 4>(p, sparse, gated, smem, st);
-        default: return launch_tt<WT, 8>(p, sparse, gated, smem, st);
+        case 1: return launch_tt<WT, 1>(p, sparse, gated, smem, st, pdl);
+        case 2: return launch_tt<WT, 2>(p, sparse, gated, smem, st, pdl);
+        case 4: return launch_tt<WT, 4>(p, sparse, gated, smem, st, pdl);
+        default: return launch_tt<WT, 8>(p, sparse, gated, smem, st, pdl);
     }
 }
 
 int launch_gemv(const GemvArgs & a, cudaStream_t st) {
     if (a.T <= 0 || a.nrows <= 0) return PI_OK;
+    if (a.T == 1 && a.status) {
+        const int rc = launch_gemv_ring(a, a.status, a.pdl, st);
+        if (rc != PI_ERR_UNSUPPORTED) return rc;
+    }
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
     const int nb = (int)(a.ncols / QK);
     // tokens are processed in chunks of at most 8 (weights are re-read per chunk; decode batches are <= 32)
@@ -242,8 +329,8 @@ int launch_gemv(const GemvArgs & a, cudaStream_t st) {
         p.dst_stride = a.dst_stride;
         const size_t smem = q4 ? (size_t)tt * nb * 40 : (size_t)tt * a.ncols * 2;
         const bool sparse = a.list != nullptr;
-        const int rc = q4 ? launch_wt<PI_TYPE_Q4_0>(p, tt, sparse, a.W2 != nullptr, smem, st)
-                          : launch_wt<PI_TYPE_F16>(p, tt, sparse, a.W2 != nullptr, smem, st);
+        const int rc = q4 ? launch_wt<PI_TYPE_Q4_0>(p, tt, sparse, a.W2 != nullptr, smem, st, a.pdl)
+                          : launch_wt<PI_TYPE_F16>(p, tt, sparse, a.W2 != nullptr, smem, st, a.pdl);
         if (rc != PI_OK) return rc;
         t0 += tt;
     }

@@ -1,0 +1,327 @@
+// Batch-1 mat-vec with the weights streamed through a shared-memory ring by the bulk-copy engine.
+//
+// One persistent CTA per SM.  A stage of the ring holds R weight rows (R consecutive rows of a dense matrix: ONE bulk
+// copy; R rows named by the active list for ggml_mul_mat_idx: R copies, plus the R gate rows when the gate matrix rides
+// along).  An mbarrier per stage counts the bytes that land; the 8 consumer warps then read the rows from shared
+// memory (conflict-free 128-bit reads), so the bytes in flight per SM are set by the ring size (~190 KB), not by
+// registers or occupancy, and DRAM sees large sequential requests.
+// Weights never depend on the previous kernel, so with programmatic dependent launch the first ring fill of a dense
+// matrix is issued BEFORE griddepcontrol.wait: it overlaps the tail of whatever produced the activation.
+// cp.async.bulk here is the plain (non-tensor, non-multicast) form; sources are this GPU's own memory.
+// Every mbarrier wait is bounded: on expiry the CTA sets bit 2 of *status, stops, and drains its copies.
+#include "pi_common.cuh"
+
+namespace pi {
+
+static constexpr int QK = 32;
+static constexpr int RING_THREADS = 256;
+static constexpr int RING_WARPS = 8;
+static constexpr int RING_MAX_ITEMS = 1024;            // list entries one CTA may own
+
+__device__ __forceinline__ uint32_t r_smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void r_mbar_init(uint64_t * bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(r_smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void r_mbar_expect_tx(uint64_t * bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(r_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool r_mbar_try_wait(uint64_t * bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(r_smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void r_bulk_g2s(void * dst, const void * src, unsigned bytes, uint64_t * bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(r_smem_u32(dst)), "l"(src), "r"(bytes), "r"(r_smem_u32(bar)) : "memory");
+}
+
+struct RingP {
+    const uint8_t * W; const uint8_t * W2;
+    int64_t row_bytes; int nrows; int ncols; int nb;
+    Act x;
+    const int32_t * list; const int32_t * count; const int32_t * bucket;
+    const float * idx; float threshold;
+    const float * bias; int relu;
+    float * dst; __half * dst16;
+    unsigned int * status;
+    int R, split, stages, max_items; size_t stage_bytes;
+};
+
+__device__ __forceinline__ int r_block_dot(const uint4 q, const uint4 lo, const uint4 hi, int s8) {
+    int sumi = 0;
+    sumi = __dp4a((int)(q.x & 0x0F0F0F0Fu), (int)lo.x, sumi);
+    sumi = __dp4a((int)((q.x >> 4) & 0x0F0F0F0Fu), (int)hi.x, sumi);
+    sumi = __dp4a((int)(q.y & 0x0F0F0F0Fu), (int)lo.y, sumi);
+    sumi = __dp4a((int)((q.y >> 4) & 0x0F0F0F0Fu), (int)hi.y, sumi);
+    sumi = __dp4a((int)(q.z & 0x0F0F0F0Fu), (int)lo.z, sumi);
+    sumi = __dp4a((int)((q.z >> 4) & 0x0F0F0F0Fu), (int)hi.z, sumi);
+    sumi = __dp4a((int)(q.w & 0x0F0F0F0Fu), (int)lo.w, sumi);
+    sumi = __dp4a((int)((q.w >> 4) & 0x0F0F0F0Fu), (int)hi.w, sumi);
+    return sumi - 8 * s8;
+}
+
+// dot of the staged row (shared memory) with the staged activation over 16-byte units [u_lo, u_hi): FP16: 8 columns per
+// unit; Q4_0: one 32-column block per unit
+template <int WT>
+__device__ __forceinline__ float ring_row_dot(const unsigned char * row, int u_lo, int u_hi, int nb, const unsigned char * xs, int lane) {
+    float acc0 = 0.f, acc1 = 0.f;
+    if (WT == PI_TYPE_F16) {
+        const uint4 * w = reinterpret_cast<const uint4 *>(row);
+        const uint4 * x = reinterpret_cast<const uint4 *>(xs);
+        for (int u = u_lo + lane; u < u_hi; u += 64) {
+            {
+                const uint4 wv = w[u], xv = x[u];
+                const float2 w0 = h2f(wv.x), w1 = h2f(wv.y), w2 = h2f(wv.z), w3 = h2f(wv.w);
+                const float2 x0 = h2f(xv.x), x1 = h2f(xv.y), x2 = h2f(xv.z), x3 = h2f(xv.w);
+                acc0 = fmaf(w0.x, x0.x, acc0); acc0 = fmaf(w0.y, x0.y, acc0); acc0 = fmaf(w1.x, x1.x, acc0); acc0 = fmaf(w1.y, x1.y, acc0);
+                acc0 = fmaf(w2.x, x2.x, acc0); acc0 = fmaf(w2.y, x2.y, acc0); acc0 = fmaf(w3.x, x3.x, acc0); acc0 = fmaf(w3.y, x3.y, acc0);
+            }
+            if (u + 32 < u_hi) {
+                const uint4 wv = w[u + 32], xv = x[u + 32];
+                const float2 w0 = h2f(wv.x), w1 = h2f(wv.y), w2 = h2f(wv.z), w3 = h2f(wv.w);
+                const float2 x0 = h2f(xv.x), x1 = h2f(xv.y), x2 = h2f(xv.z), x3 = h2f(xv.w);
+                acc1 = fmaf(w0.x, x0.x, acc1); acc1 = fmaf(w0.y, x0.y, acc1); acc1 = fmaf(w1.x, x1.x, acc1); acc1 = fmaf(w1.y, x1.y, acc1);
+                acc1 = fmaf(w2.x, x2.x, acc1); acc1 = fmaf(w2.y, x2.y, acc1); acc1 = fmaf(w3.x, x3.x, acc1); acc1 = fmaf(w3.y, x3.y, acc1);
+            }
+        }
+    } else {
+        const uint4 * q = reinterpret_cast<const uint4 *>(row);
+        const __half * sc = reinterpret_cast<const __half *>(row + (size_t)nb * 16);
+        const uint4 * lo = reinterpret_cast<const uint4 *>(xs);
+        const uint4 * hi = lo + nb;
+        const uint2 * ds = reinterpret_cast<const uint2 *>(hi + nb);        // {scale as float bits, int8 sum} per block
+        for (int b = u_lo + lane; b < u_hi; b += 64) {
+            const uint2 m = ds[b];
+            acc0 = fmaf((float)r_block_dot(q[b], lo[b], hi[b], (int)m.y), __half2float(sc[b]) * __uint_as_float(m.x), acc0);
+            if (b + 32 < u_hi) {
+                const int c = b + 32;
+                const uint2 m2 = ds[c];
+                acc1 = fmaf((float)r_block_dot(q[c], lo[c], hi[c], (int)m2.y), __half2float(sc[c]) * __uint_as_float(m2.x), acc1);
+            }
+        }
+    }
+    return acc0 + acc1;
+}
+
+template <int WT, bool SPARSE, bool GATED>
+__global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ float s_part[2][RING_WARPS][2];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const int S = p.stages, R = p.R, split = p.split;
+    const int NM = GATED ? 2 : 1;                                  // matrices riding in one stage
+
+    // shared-memory map: [S] mbarriers | item list | staged activation | ring
+    uint64_t * full = reinterpret_cast<uint64_t *>(smem);
+    int * items = reinterpret_cast<int *>(smem + 8 * 32);
+    const size_t x_bytes = WT == PI_TYPE_F16 ? (size_t)p.ncols * 2 : (size_t)p.nb * 40;
+    unsigned char * xs = smem + (((size_t)8 * 32 + (size_t)4 * p.max_items + 127) & ~(size_t)127);
+    unsigned char * ring = xs + ((x_bytes + 127) & ~(size_t)127);
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) r_mbar_init(full + s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    // stage st of this CTA covers items [ (cta + st*G) * R, +R ) of the row / list sequence
+    int n_items, n_stages;
+    auto stage_first = [&](int st) { return (cta + st * G) * R; };
+    auto issue = [&](int st) {                                       // thread 0 only
+        const int s = st % S;
+        const int first = stage_first(st);
+        const int n = min(R, n_items - first);
+        unsigned char * dstp = ring + (size_t)s * p.stage_bytes;
+        if (!SPARSE) {
+            r_mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
+            r_bulk_g2s(dstp, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
+        } else {
+            r_mbar_expect_tx(full + s, (unsigned)(n * NM * p.row_bytes));
+            for (int k = 0; k < n; k++) {
+                const int r = items[st * R + k];
+                r_bulk_g2s(dstp + (size_t)k * p.row_bytes, p.W + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
+                if (GATED) r_bulk_g2s(dstp + (size_t)(R + k) * p.row_bytes, p.W2 + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
+            }
+        }
+    };
+
+    if (!SPARSE) {
+        // dense: the rows are known now; fill the ring before waiting for the producer of the activation
+        n_items = p.nrows;
+        const int total_stages = (n_items + R - 1) / R;
+        n_stages = cta < total_stages ? (total_stages - cta + G - 1) / G : 0;
+        if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
+    }
+    pdl_wait();
+    pdl_launch();
+    if (SPARSE) {
+        n_items = min(*p.count, p.nrows);
+        const int total_stages = (n_items + R - 1) / R;
+        n_stages = cta < total_stages ? (total_stages - cta + G - 1) / G : 0;
+        n_stages = min(n_stages, p.max_items / R);
+        for (int i = tid; i < n_stages * R; i += RING_THREADS) {
+            const int it = stage_first(i / R) + (i % R);
+            int r = it < n_items ? p.list[it] : 0;
+            items[i] = (unsigned)r < (unsigned)p.nrows ? r : 0;
+        }
+        __syncthreads();
+        if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
+    }
+    // ---- stage the activation
+    if (WT == PI_TYPE_F16) {
+        const uint4 * src = reinterpret_cast<const uint4 *>(p.x.h16);
+        uint4 * dstx = reinterpret_cast<uint4 *>(xs);
+        for (int i = tid; i < p.ncols / 8; i += RING_THREADS) dstx[i] = src[i];
+    } else {
+        uint4 * lo = reinterpret_cast<uint4 *>(xs);
+        uint4 * hi = lo + p.nb;
+        uint2 * ds = reinterpret_cast<uint2 *>(hi + p.nb);
+        for (int i = tid; i < p.nb; i += RING_THREADS) {
+            lo[i] = p.x.lo[i]; hi[i] = p.x.hi[i];
+            ds[i] = make_uint2(__float_as_uint(p.x.d[i]), (unsigned)p.x.s[i]);
+        }
+    }
+    __syncthreads();
+
+    const int units = WT == PI_TYPE_F16 ? p.ncols / 8 : p.nb;       // 16-byte units per row
+    const int per = units / split;
+    bool dead = false;
+    for (int st = 0; st < n_stages; st++) {
+        const int s = st % S;
+        const unsigned parity = (unsigned)(st / S) & 1u;
+        if (!dead) {
+            int spins = 0;
+            bool gave_up = false;
+            while (!r_mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            dead = __syncthreads_or(gave_up) != 0;                   // the whole CTA agrees, so no warp shuffles half-populated
+            if (dead && tid == 0) atomicOr(p.status, 4u);
+        }
+        const unsigned char * base = ring + (size_t)s * p.stage_bytes;
+        const int first = stage_first(st);
+        const int n = min(R, n_items - first);
+        if (split == 1) {
+            for (int k = warp; k < n && !dead; k += RING_WARPS) {
+                float v = warp_sum(ring_row_dot<WT>(base + (size_t)k * p.row_bytes, 0, units, p.nb, xs, lane));
+                float v2 = 0.f;
+                if (GATED) v2 = warp_sum(ring_row_dot<WT>(base + (size_t)(R + k) * p.row_bytes, 0, units, p.nb, xs, lane));
+                if (lane == 0) {
+                    const int r = SPARSE ? items[st * R + k] : first + k;
+                    const int64_t g = SPARSE && p.bucket ? p.bucket[r] : r;
+                    bool active = true;
+                    if (SPARSE) active = p.idx[g] >= p.threshold;
+                    float o = active ? v : 0.f;
+                    if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
+                    if (p.bias) o += p.bias[g];
+                    if (p.relu) o = fmaxf(o, 0.f);
+                    if (p.dst)   p.dst[g] = o;
+                    if (p.dst16) p.dst16[g] = __float2half_rn(o);
+                }
+            }
+            __syncthreads();
+        } else {
+            // R * split == 8: warp = (row k, column part); parts are added in part order after the barrier
+            const int k = warp / split, part = warp % split;
+            float v = 0.f, v2 = 0.f;
+            if (k < n && !dead) {
+                v = warp_sum(ring_row_dot<WT>(base + (size_t)k * p.row_bytes, part * per, (part + 1) * per, p.nb, xs, lane));
+                if (GATED) v2 = warp_sum(ring_row_dot<WT>(base + (size_t)(R + k) * p.row_bytes, part * per, (part + 1) * per, p.nb, xs, lane));
+            }
+            if (lane == 0) { s_part[st & 1][warp][0] = v; s_part[st & 1][warp][1] = v2; }
+            __syncthreads();
+            if (part == 0 && lane == 0 && k < n && !dead) {
+                for (int q = 1; q < split; q++) { v += s_part[st & 1][warp + q][0]; v2 += s_part[st & 1][warp + q][1]; }
+                const int r = SPARSE ? items[st * R + k] : first + k;
+                const int64_t g = SPARSE && p.bucket ? p.bucket[r] : r;
+                bool active = true;
+                if (SPARSE) active = p.idx[g] >= p.threshold;
+                float o = active ? v : 0.f;
+                if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
+                if (p.bias) o += p.bias[g];
+                if (p.relu) o = fmaxf(o, 0.f);
+                if (p.dst)   p.dst[g] = o;
+                if (p.dst16) p.dst16[g] = __float2half_rn(o);
+            }
+        }
+        if (tid == 0 && !dead && st + S < n_stages) issue(st + S);   // the barrier above freed stage s
+    }
+    if (dead && tid == 0) {                                         // do not exit with copies still landing in shared memory
+        for (int s = 0; s < S; s++) { int spins = 0; while (!r_mbar_try_wait(full + s, 0) && !r_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+    }
+}
+
+struct RingPlan { bool ok; int R, split, stages, ctas_per_sm; size_t stage_bytes, smem; int max_items; };
+
+// Four small rings per SM rather than one big one: 32 resident warps hide the shared-memory and ALU latencies of the
+// consumers (with 8 warps the kernel is issue-latency bound), and the copies of the CTAs that are not computing keep
+// 100+ KB per SM in flight.
+static RingPlan ring_plan(int wtype, int64_t nrows, int64_t ncols, bool sparse, bool gated) {
+    RingPlan pl{};
+    const size_t row_bytes = pi_row_bytes(wtype, ncols);
+    if (row_bytes % 16 != 0) return pl;
+    const int units = wtype == PI_TYPE_F16 ? (int)(ncols / 8) : (int)(ncols / QK);
+    const int nm = gated ? 2 : 1;
+    const size_t x_bytes = wtype == PI_TYPE_F16 ? (size_t)ncols * 2 : (size_t)(ncols / QK) * 40;
+    for (int cps = 4; cps >= 1; cps /= 2) {
+        const size_t budget = (size_t)(cps == 4 ? 54 : (cps == 2 ? 110 : 200)) * 1024;
+        const int G = sm_count() * cps;
+        int R = 1;
+        while (R < 64 && (size_t)(2 * R) * nm * row_bytes <= (cps == 4 ? 19 : 36) * 1024) R *= 2;
+        const int split = R >= RING_WARPS ? 1 : RING_WARPS / R;
+        if (split > 1 && units % (split * 32) != 0) continue;
+        const int max_items = sparse ? (int)((((nrows + G - 1) / G + R - 1) / R + 1) * R) : 0;
+        if (max_items > RING_MAX_ITEMS) continue;
+        const size_t head = (((size_t)8 * 32 + (size_t)4 * max_items + 127) & ~size_t(127)) + ((x_bytes + 127) & ~size_t(127));
+        const size_t stage_bytes = ((size_t)R * nm * row_bytes + 127) & ~size_t(127);
+        if (head + 2 * stage_bytes > budget) continue;
+        int S = (int)((budget - head) / stage_bytes);
+        pl.stages = S > 8 ? 8 : S;
+        pl.R = R; pl.split = split; pl.ctas_per_sm = cps; pl.max_items = max_items; pl.stage_bytes = stage_bytes;
+        pl.smem = head + (size_t)pl.stages * stage_bytes;
+        pl.ok = true;
+        return pl;
+    }
+    return pl;
+}
+
+template <int WT, bool SPARSE, bool GATED>
+static int launch_ring_inst(const RingP & p, const RingPlan & pl, bool pdl, cudaStream_t st) {
+    static bool attr_done[16] = {false};
+    int dev = 0;
+    PI_CUDA(cudaGetDevice(&dev));
+    auto kern = k_gemv_ring<WT, SPARSE, GATED>;
+    if (dev >= 0 && dev < 16 && !attr_done[dev]) {
+        PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
+        attr_done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count() * pl.ctas_per_sm); cfg.blockDim = dim3(RING_THREADS); cfg.dynamicSmemBytes = pl.smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    PI_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+    return PI_OK;
+}
+
+// PI_ERR_UNSUPPORTED: shape not eligible, the caller uses the register-streaming kernel instead
+int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaStream_t st) {
+    if (a.T != 1 || !status) return PI_ERR_UNSUPPORTED;
+    const bool sparse = a.list != nullptr, gated = a.W2 != nullptr;
+    const RingPlan pl = ring_plan(a.wtype, a.nrows, a.ncols, sparse, gated);
+    if (!pl.ok) return PI_ERR_UNSUPPORTED;
+    RingP p;
+    p.W = (const uint8_t *)a.W; p.W2 = (const uint8_t *)a.W2; p.row_bytes = (int64_t)pi_row_bytes(a.wtype, a.ncols);
+    p.nrows = (int)a.nrows; p.ncols = (int)a.ncols; p.nb = (int)(a.ncols / QK); p.x = a.x;
+    p.list = a.list; p.count = a.count; p.bucket = a.bucket; p.idx = a.idx; p.threshold = a.threshold;
+    p.bias = a.bias; p.relu = a.relu; p.dst = a.dst; p.dst16 = a.dst16; p.status = status;
+    p.R = pl.R; p.split = pl.split; p.stages = pl.stages; p.max_items = pl.max_items; p.stage_bytes = pl.stage_bytes;
+    const bool q4 = a.wtype == PI_TYPE_Q4_0;
+    if (!sparse) return q4 ? launch_ring_inst<PI_TYPE_Q4_0, false, false>(p, pl, pdl, st) : launch_ring_inst<PI_TYPE_F16, false, false>(p, pl, pdl, st);
+    if (gated)   return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, true>(p, pl, pdl, st)   : launch_ring_inst<PI_TYPE_F16, true, true>(p, pl, pdl, st);
+    return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, false>(p, pl, pdl, st) : launch_ring_inst<PI_TYPE_F16, true, false>(p, pl, pdl, st);
+}
+
+}  // namespace pi

@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(COMPACT_THREADS) k_compact(const CompactP p) {
     const int tid = threadIdx.x, lane = tid & 31;
     const int n_chunks = (p.n_local + 31) / 32;
     const int warps_total = gridDim.x * (COMPACT_THREADS / 32);
+    pdl_wait();
+    pdl_launch();
     for (int c = blockIdx.x * (COMPACT_THREADS / 32) + (tid >> 5); c < n_chunks; c += warps_total) {
         const int r = c * 32 + lane;
         bool any = false;
@@ -94,8 +96,7 @@ int launch_compact(const CompactArgs & a, cudaStream_t st) {
     const int n_chunks = (int)((a.n_local + 31) / 32);
     int grid = (n_chunks + COMPACT_THREADS / 32 - 1) / (COMPACT_THREADS / 32);
     grid = max(1, min(grid, sm_count()));
-    k_compact<<<grid, COMPACT_THREADS, 0, st>>>(p);
-    PI_LAUNCH_CHECK("k_compact");
+    PI_CUDA(launch_k(k_compact, dim3(grid), dim3(COMPACT_THREADS), 0, st, a.pdl, p));
     return PI_OK;
 }
 
@@ -254,19 +255,272 @@ __global__ void __launch_bounds__(AXPY_Q4_THREADS) k_axpy_q4(const AxpyP p) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// axpy for one token, bulk-copy pipelined (the batch-1 decode path).  One persistent CTA per SM walks list entries
+// cta, cta+G, cta+2G, ... in increasing order.  Whole weight rows (contiguous in both layouts: FP16, or planar Q4_0 =
+// nibbles then scales) are staged in shared memory by the bulk-copy engine (cp.async.bulk, non-tensor, no multicast)
+// into a ring of PIPE stages, each guarded by an mbarrier that counts the row's bytes, so a CTA keeps 100+ KB of
+// loads in flight without holding them in registers.  Threads own fixed columns and keep their sums in registers;
+// the per-CTA partial vectors are summed in CTA order afterwards (no atomics, fixed order).
+// The coefficient of each row is made in the prologue with the CPU path's rule: FP16(h) for FP16 rows; for Q4_0 the
+// int8 quant of h within its block of 32 neurons times that block's FP16 scale (ggml.c:14575-14581).
+// Every mbarrier wait is bounded; if one runs out the CTA raises bit 1 of *status, stops consuming and still writes
+// its partial, so a lost copy can never hang the GPU.
+static constexpr int PIPE_THREADS = 256;
+static constexpr int PIPE_MAX_ROWS = 512;               // list entries one CTA may own (F / G, rounded up)
+
+__device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t * bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t * bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t * bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(void * dst, const void * src, unsigned bytes, uint64_t * bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+struct AxpyPipeP {
+    const uint8_t * Wt; int64_t row_bytes; int nrows; int ncols; int nb;
+    const float * h; const int32_t * list; const int32_t * count; const int32_t * bucket;
+    const float * idx; float threshold;
+    float * partial; unsigned int * status; int stages; int max_rows;
+};
+
+static constexpr int PIPE_RS = 4;                       // rows per ring stage (one barrier, one CTA-wide sync per stage)
+
+// Up to 1024 threads per CTA so that 32 warps hide the shared-memory and ALU latencies.  FP16: a thread owns CPT chunks of
+// 8 columns (chunk = tid + k * blockDim).  Q4_0: a thread owns ONE 32-bit word of a block's nibbles = 8 columns
+// (4 low-nibble columns 4i.., 4 high-nibble columns 16+4i..), four threads share a block's scale.
+template <int WT, int CPT>
+__global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nwarp = blockDim.x >> 5;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const int S = p.stages;
+    uint64_t * full = reinterpret_cast<uint64_t *>(smem);                      // [S]
+    int *   rows = reinterpret_cast<int *>(smem + 8 * 32);                     // [max_rows]
+    float * coef = reinterpret_cast<float *>(rows + p.max_rows);               // [max_rows]
+    unsigned char * ring = smem + (((size_t)8 * 32 + (size_t)8 * p.max_rows + 127) & ~(size_t)127);
+    const size_t row_stride = ((size_t)p.row_bytes + 127) & ~(size_t)127;
+    const size_t stage_bytes = row_stride * PIPE_RS;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) mbar_init(full + s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    pdl_wait();
+    pdl_launch();
+    const int n = min(*p.count, p.nrows);
+    int n_mine = cta < n ? (n - cta + G - 1) / G : 0;
+    n_mine = min(n_mine, p.max_rows);
+    const int n_stages = (n_mine + PIPE_RS - 1) / PIPE_RS;
+
+    // ---- prologue: my rows first (one round trip), start the copies, then the coefficients while the rows fly in
+    for (int i = tid; i < n_mine; i += blockDim.x) {
+        const int r = p.list[cta + i * G];
+        rows[i] = (unsigned)r < (unsigned)p.nrows ? r : -1;
+    }
+    __syncthreads();
+    auto issue = [&](int st) {                                       // thread 0 only
+        const int s = st % S;
+        const int cnt = min(PIPE_RS, n_mine - st * PIPE_RS);
+        mbar_expect_tx(full + s, (unsigned)(cnt * p.row_bytes));
+        for (int k = 0; k < cnt; k++) {
+            const int r = rows[st * PIPE_RS + k] < 0 ? 0 : rows[st * PIPE_RS + k];
+            bulk_g2s(ring + s * stage_bytes + k * row_stride, p.Wt + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
+        }
+    };
+    if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
+    for (int i0 = wid; i0 < n_mine; i0 += nwarp * 4) {             // 4 rows per warp per pass: their loads overlap
+        float hv[4], pv[4]; int64_t g[4]; bool ok[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * nwarp;
+            ok[u] = i < n_mine && rows[i] >= 0;
+            const int r = ok[u] ? rows[i] : 0;
+            g[u] = p.bucket ? p.bucket[r] : r;
+            hv[u] = WT == PI_TYPE_F16 ? p.h[g[u]] : p.h[(g[u] & ~(int64_t)31) + lane];
+            pv[u] = p.idx[g[u]];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * nwarp;
+            float c;
+            if (WT == PI_TYPE_F16) {
+                c = round_f16(hv[u]);
+            } else {
+                const float amax = warp_max(fabsf(hv[u]));
+                const float id = amax != 0.0f ? 127.0f / amax : 0.0f;
+                const int q = __float2int_rn(hv[u] * id);
+                const int b8 = __shfl_sync(0xffffffffu, q, (int)(g[u] & 31));
+                c = (float)b8 * round_f16(amax / 127.0f);
+            }
+            if (!ok[u] || !(pv[u] >= p.threshold)) c = 0.f;
+            if (lane == 0 && i < n_mine) coef[i] = c;
+        }
+    }
+    __syncthreads();
+
+    constexpr int NACC = WT == PI_TYPE_F16 ? CPT * 8 : 8;
+    float acc[NACC];
+#pragma unroll
+    for (int j = 0; j < NACC; j++) acc[j] = 0.f;
+    const int n_chunks = p.ncols / 8;
+    const int n_words = p.nb * 4;
+    bool dead = false;
+
+    for (int st = 0; st < n_stages; st++) {
+        const int s = st % S;
+        const unsigned parity = (unsigned)(st / S) & 1u;
+        if (!dead) {
+            int spins = 0;
+            bool gave_up = false;
+            while (!mbar_try_wait(full + s, parity)) {
+                if (++spins > (1 << 20)) { gave_up = true; break; }    // each try_wait already blocks for a while
+            }
+            dead = __syncthreads_or(gave_up) != 0;
+            if (dead && tid == 0) atomicOr(p.status, 2u);
+        }
+        const int cnt = min(PIPE_RS, n_mine - st * PIPE_RS);
+        if (!dead) {
+#pragma unroll
+            for (int k = 0; k < PIPE_RS; k++) {
+                if (k >= cnt) break;
+                const float c = coef[st * PIPE_RS + k];
+                if (c == 0.f) continue;
+                const unsigned char * row = ring + s * stage_bytes + k * row_stride;
+                if (WT == PI_TYPE_F16) {
+#pragma unroll
+                    for (int q = 0; q < CPT; q++) {
+                        const int ch = tid + q * (int)blockDim.x;
+                        if (ch < n_chunks) {
+                            const uint4 w = reinterpret_cast<const uint4 *>(row)[ch];
+                            const float2 w0 = h2f(w.x), w1 = h2f(w.y), w2 = h2f(w.z), w3 = h2f(w.w);
+                            acc[q * 8 + 0] = fmaf(w0.x, c, acc[q * 8 + 0]); acc[q * 8 + 1] = fmaf(w0.y, c, acc[q * 8 + 1]);
+                            acc[q * 8 + 2] = fmaf(w1.x, c, acc[q * 8 + 2]); acc[q * 8 + 3] = fmaf(w1.y, c, acc[q * 8 + 3]);
+                            acc[q * 8 + 4] = fmaf(w2.x, c, acc[q * 8 + 4]); acc[q * 8 + 5] = fmaf(w2.y, c, acc[q * 8 + 5]);
+                            acc[q * 8 + 6] = fmaf(w3.x, c, acc[q * 8 + 6]); acc[q * 8 + 7] = fmaf(w3.y, c, acc[q * 8 + 7]);
+                        }
+                    }
+                } else if (tid < n_words) {
+                    const uint32_t word = reinterpret_cast<const uint32_t *>(row)[tid];
+                    const float sc = c * __half2float(reinterpret_cast<const __half *>(row + (size_t)p.nb * 16)[tid >> 2]);
+                    const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        acc[j]     = fmaf(nib_to_float(lo, j), sc, acc[j]);
+                        acc[4 + j] = fmaf(nib_to_float(hi, j), sc, acc[4 + j]);
+                    }
+                }
+            }
+        }
+        __syncthreads();                                             // everyone is done with stage s
+        if (tid == 0 && !dead && st + S < n_stages) issue(st + S);
+    }
+    // a CTA that gave up must not leave copies in flight into its shared memory: drain what was issued
+    if (dead && tid == 0) {
+        for (int s = 0; s < S; s++) { int spins = 0; while (!mbar_try_wait(full + s, 0) && !mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+    }
+
+    float * out = p.partial + (size_t)cta * p.ncols;
+    if (WT == PI_TYPE_F16) {
+#pragma unroll
+        for (int q = 0; q < CPT; q++) {
+            const int ch = tid + q * (int)blockDim.x;
+            if (ch < n_chunks) {
+                *reinterpret_cast<float4 *>(out + ch * 8)     = make_float4(acc[q * 8 + 0], acc[q * 8 + 1], acc[q * 8 + 2], acc[q * 8 + 3]);
+                *reinterpret_cast<float4 *>(out + ch * 8 + 4) = make_float4(acc[q * 8 + 4], acc[q * 8 + 5], acc[q * 8 + 6], acc[q * 8 + 7]);
+            }
+        }
+    } else if (tid < n_words) {
+        const int b = tid >> 2, i = tid & 3;
+        *reinterpret_cast<float4 *>(out + (size_t)b * QK + 4 * i)      = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4 *>(out + (size_t)b * QK + 16 + 4 * i) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+}
+
+struct PipePlan { bool ok; int threads; int cpt; int stages; int max_rows; size_t smem; int groups; };
+
+static PipePlan pipe_plan(int wtype, int64_t nrows, int64_t ncols) {
+    PipePlan pl{};
+    const int G = sm_count();
+    const size_t row_bytes = pi_row_bytes(wtype, ncols);
+    const size_t row_stride = (row_bytes + 127) & ~size_t(127);
+    pl.groups = G;
+    pl.max_rows = (int)((nrows + G - 1) / G);
+    if (pl.max_rows > PIPE_MAX_ROWS || row_bytes % 16 != 0) return pl;
+    if (wtype == PI_TYPE_Q4_0) {
+        const int nb = (int)(ncols / QK);
+        if (nb * 4 > 1024) return pl;
+        pl.threads = (nb * 4 + 31) / 32 * 32; pl.cpt = 1;
+    } else {
+        const int chunks = (int)(ncols / 8);
+        pl.threads = chunks >= 1024 ? 1024 : (chunks + 31) / 32 * 32;
+        pl.cpt = (chunks + pl.threads - 1) / pl.threads;
+        if (pl.cpt > 2) return pl;
+    }
+    const size_t head = ((size_t)8 * 32 + (size_t)8 * pl.max_rows + 127 + 128) & ~size_t(127);
+    const size_t budget = 200 * 1024;
+    int S = (int)((budget - head) / (row_stride * PIPE_RS));
+    S = S > 16 ? 16 : S;
+    if (S < 2) return pl;
+    pl.stages = S;
+    pl.smem = head + (size_t)S * row_stride * PIPE_RS;
+    pl.ok = true;
+    return pl;
+}
+
+template <int WT, int CPT>
+static int launch_pipe_inst(const AxpyPipeP & p, const PipePlan & pl, cudaStream_t st, bool pdl) {
+    static bool attr_done[16] = {false};
+    int dev = 0;
+    PI_CUDA(cudaGetDevice(&dev));
+    auto kern = k_axpy_pipe<WT, CPT>;
+    if (dev >= 0 && dev < 16 && !attr_done[dev]) {
+        PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
+        attr_done[dev] = true;
+    }
+    PI_CUDA(launch_k(kern, dim3(pl.groups), dim3(pl.threads), pl.smem, st, pdl, p));
+    return PI_OK;
+}
+
 // Row groups: enough CTAs to keep ~6 resident per SM (each holds AXPY_UNROLL x 2 KB of loads in flight), capped
 // so the partial buffer stays small next to the weight bytes.
 int axpy_groups(int wtype, int64_t ncols, int T) {
-    (void)T;
+    (void)T;      // the buffer must fit the larger of the two kernels' group counts: the pipelined one uses one CTA per SM
     const int tiles = wtype == PI_TYPE_Q4_0 ? (int)((ncols / QK + AXPY_Q4_THREADS - 1) / AXPY_Q4_THREADS)
                                             : (int)((ncols / 8 + AXPY_F16_THREADS - 1) / AXPY_F16_THREADS);
     int g = (sm_count() * 6 + tiles - 1) / tiles;
-    return max(1, min(g, 256));
+    return max(sm_count(), min(g, 256));
 }
 
-int launch_axpy(const AxpyArgs & a, cudaStream_t st) {
+int launch_axpy(const AxpyArgs & a, cudaStream_t st, int * groups_used) {
     if (a.T <= 0) return PI_OK;
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
+    if (groups_used) *groups_used = a.n_groups;
+    if (a.T == 1 && a.status) {
+        const PipePlan pl = pipe_plan(a.wtype, a.nrows, a.ncols);
+        if (pl.ok && pl.groups <= a.n_groups) {
+            AxpyPipeP p;
+            p.Wt = (const uint8_t *)a.Wt; p.row_bytes = (int64_t)pi_row_bytes(a.wtype, a.ncols); p.nrows = (int)a.nrows;
+            p.ncols = (int)a.ncols; p.nb = (int)(a.ncols / QK);
+            p.h = a.h; p.list = a.list; p.count = a.count; p.bucket = a.bucket; p.idx = a.idx; p.threshold = a.threshold;
+            p.partial = a.partial; p.status = a.status; p.stages = pl.stages; p.max_rows = pl.max_rows;
+            if (groups_used) *groups_used = pl.groups;
+            if (q4) return launch_pipe_inst<PI_TYPE_Q4_0, 1>(p, pl, st, a.pdl);
+            if (pl.cpt == 1) return launch_pipe_inst<PI_TYPE_F16, 1>(p, pl, st, a.pdl);
+            return launch_pipe_inst<PI_TYPE_F16, 2>(p, pl, st, a.pdl);
+        }
+    }
     AxpyP p;
     p.Wt = (const uint8_t *)a.Wt; p.row_bytes = (int64_t)pi_row_bytes(a.wtype, a.ncols);
     p.nrows = (int)a.nrows; p.ncols = (int)a.ncols; p.nb = (int)(a.ncols / QK);
@@ -299,27 +553,52 @@ int launch_axpy(const AxpyArgs & a, cudaStream_t st) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// dst[t, c] = sum_j partial[j, t, c] (j ascending) + residual[t, c] + bias[c]
-__global__ void k_reduce_partials(const float * __restrict__ partial, int G, int T, int64_t n,
-                                  const float * __restrict__ residual, const float * __restrict__ bias,
-                                  float * __restrict__ dst) {
-    const int64_t total = (int64_t)T * n;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        float s = 0.f;
-        for (int j = 0; j < G; j++) s += partial[(size_t)j * total + i];
-        if (bias) s += bias[i % n];
-        if (residual) s += residual[i];
-        dst[i] = s;
+// dst[t, c] = sum_j partial[j, t, c] (j ascending within each of 16 interleaved classes, classes added in order)
+//             + bias[c] + residual[t, c].  A CTA owns 128 consecutive values; warp w adds groups w, w+16, w+32, ...;
+// the 16 warp sums are then added in warp order.  The order is fixed, so the result is reproducible.
+static constexpr int RED_WARPS = 16;
+
+__global__ void __launch_bounds__(RED_WARPS * 32) k_reduce_partials(const float * __restrict__ partial, int G, int64_t total, int64_t n,
+                                                                     const float * __restrict__ residual, const float * __restrict__ bias,
+                                                                     float * __restrict__ dst) {
+    __shared__ float4 s_part[RED_WARPS][32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    pdl_wait();
+    pdl_launch();
+    const int64_t i4 = (int64_t)blockIdx.x * 32 + lane;                // float4 index
+    const bool ok = i4 * 4 < total;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ok) {
+        for (int j0 = w; j0 < G; j0 += RED_WARPS * 8) {                // 8 loads in flight, added in group order
+            float4 a[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int j = j0 + u * RED_WARPS;
+                a[u] = j < G ? __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)j * total) + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) { v.x += a[u].x; v.y += a[u].y; v.z += a[u].z; v.w += a[u].w; }
+        }
+    }
+    s_part[w][lane] = v;
+    __syncthreads();
+    if (w == 0 && ok) {
+#pragma unroll
+        for (int k = 1; k < RED_WARPS; k++) { const float4 a = s_part[k][lane]; v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w; }
+        const int64_t i = i4 * 4;
+        if (bias) { const int64_t c = i % n; v.x += bias[c]; v.y += bias[c + 1]; v.z += bias[c + 2]; v.w += bias[c + 3]; }
+        if (residual) { const float4 r = *reinterpret_cast<const float4 *>(residual + i); v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w; }
+        *reinterpret_cast<float4 *>(dst + i) = v;
     }
 }
 
 int launch_reduce_partials(const float * partial, int n_groups, int T, int64_t n, const float * residual,
-                           const float * bias, float * dst, cudaStream_t st) {
+                           const float * bias, float * dst, cudaStream_t st, bool pdl) {
     const int64_t total = (int64_t)T * n;
     if (total == 0) return PI_OK;
-    const int grid = (int)imin64((total + 127) / 128, (int64_t)sm_count() * 8);
-    k_reduce_partials<<<grid, 128, 0, st>>>(partial, n_groups, T, n, residual, bias, dst);
-    PI_LAUNCH_CHECK("k_reduce_partials");
+    PI_REQUIRE(n % 4 == 0, "reduce: n must be a multiple of 4");
+    const int grid = (int)((total / 4 + 31) / 32);
+    PI_CUDA(launch_k(k_reduce_partials, dim3(grid), dim3(RED_WARPS * 32), 0, st, pdl, partial, n_groups, total, n, residual, bias, dst));
     return PI_OK;
 }
 
