@@ -97,6 +97,20 @@ int pi_axpy(int wtype, const void * Wt, int64_t n_w_rows, int64_t ncols,
             float * dst,
             void * workspace, size_t workspace_bytes, void * stream);
 
+/* pi_axpy for one token with NO workspace argument and no allocation of any kind.  It has no counterpart in the
+ * reference (whose CUDA back end allocates from its own pool, ggml-cuda.cu:6387-6459): it exists for hosts that own all
+ * device memory and forbid a plug-in to cudaMalloc, and for call sites where allocating is not permitted.  The scratch is a
+ * 24 MiB array inside the library's device image (pi_axpy_static_max_bytes()), held by every GPU that loads the library
+ * for the life of the process.  Limits: one token, n_w_rows and h_stride <= 65536, ncols <= 16384; anything larger is
+ * rejected with PI_ERR_INVALID and a message naming pi_axpy.  The first call on each device looks the array's address up
+ * (cudaGetSymbolAddress, with that device current); make that call before any stream capture begins.  All calls share the
+ * one array: the words that must start at zero are cleared on the stream at the start of every call, and two calls that
+ * overlap on the GPU (different streams, or different host threads) race on it, so serialise them. */
+size_t pi_axpy_static_max_bytes(void);
+int pi_axpy_static(int wtype, const void * Wt, int64_t n_w_rows, int64_t ncols,
+                   const float * h, int64_t h_stride, const float * idx, int64_t idx_stride,
+                   const int32_t * bucket, float threshold, float * dst, void * stream);
+
 /* ---- dense decode nodes ------------------------------------------------------------------------------ */
 
 /* ggml_mul_mat with a weight matrix and T <= 32 activation columns (ggml.c:9598-9807; CUDA ggml-cuda.cu:4310-4414):
