@@ -84,6 +84,22 @@ int launch_quantize_q8_0_ggml(const float * x, void * q8, int64_t nrows, int64_t
 // x F32 [T, n] (row stride x_stride) -> activation planes for `wtype` weights
 int launch_convert_act(int wtype, const float * x, int64_t x_stride, int64_t n, int T, ActBuf out, cudaStream_t st);
 
+// How a consumer kernel builds its own input vector instead of reading activation planes somebody else made
+// (batch 1 only).  v = (vec | sum of n_slots mailbox / partial slots) + bias + res1 + res2, optionally written out as the
+// new residual stream by CTA 0, then optionally normalised (llm_build_norm: rms or layer norm, * w, + b) and rounded to
+// the form the weights consume.  Every CTA recomputes it (a few tens of KB from L2): cheaper than one more launch.
+struct FusedIn {
+    int on = 0;
+    const float * vec = nullptr;
+    const float * slots = nullptr; int n_slots = 0; int64_t slot_stride = 0;
+    const unsigned int * wait_flags = nullptr; const unsigned int * wait_epoch = nullptr;   // slots are mailbox slots of peer ranks
+    const float * bias = nullptr; const float * res1 = nullptr; const float * res2 = nullptr;
+    float * x_out = nullptr;
+    int norm = 0;                      // 0: none, 1: RMSNorm, 2: LayerNorm
+    float eps = 0.f; const float * w = nullptr; const float * b = nullptr;
+    const double * stats = nullptr;    // {sum, sum of squares} of v accumulated by the kernel that produced `vec`: no reduction here
+};
+
 struct GemvArgs {
     int wtype = PI_TYPE_F16;
     const void * W = nullptr;          // [nrows, ncols]
@@ -107,6 +123,10 @@ struct GemvArgs {
     const void * W2 = nullptr;
     unsigned int * status = nullptr;   // device status word; when given, T == 1 shapes use the bulk-copy ring kernel
     bool pdl = false;                  // launch with programmatic dependent launch (the kernel waits for its producer itself)
+    FusedIn fin;                       // ring kernel only: build the input in the prologue (x is then ignored)
+    // ring kernel only: dst[g] = result + res_add[g] (the residual stream), and {sum, sum of squares} of what was written are
+    // added to stats_out (so the next norm needs no reduction of its own)
+    const float * res_add = nullptr; double * stats_out = nullptr;
 };
 int launch_gemv(const GemvArgs & a, cudaStream_t st);
 int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaStream_t st);   // PI_ERR_UNSUPPORTED: not eligible
@@ -146,7 +166,8 @@ int launch_neuron_q8(const float * h, int64_t stride, int64_t n, int T, int8_t *
 
 // sum partial [n_groups, T, n] in group order (+ residual + bias) -> dst [T, n]
 int launch_reduce_partials(const float * partial, int n_groups, int T, int64_t n, const float * residual,
-                           const float * bias, float * dst, cudaStream_t st, bool pdl = false);
+                           const float * bias, float * dst, cudaStream_t st, bool pdl = false,
+                           const float * residual2 = nullptr, double * stats_out = nullptr);
 
 struct NormArgs {
     const float * x = nullptr; int T = 1; int64_t n = 0; int rms = 1; float eps = 0.f;

@@ -74,8 +74,8 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
     __shared__ double s_red[32];
     const int t = blockIdx.x;
     const int64_t n = p.n;
-    pdl_wait();
     pdl_launch();
+    pdl_wait();
     const size_t tn = p.partial_stride ? (size_t)p.partial_stride : (size_t)p.T * n;
     const float * partial = p.partial;
     if (p.wait_flags) {
@@ -272,8 +272,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     const int hd = p.hd, half = hd / 2, chunks = hd / 8;
     const int group = p.n_head / p.n_head_kv, hk = h / group;
     const int dkv = p.n_head_kv * hd;
-    pdl_wait();
     pdl_launch();
+    pdl_wait();
     const int pos = p.pos[t];
     const int sq = p.seq ? p.seq[t] : 0;
     if (pos < 0 || pos >= p.n_ctx) return;                       // never index the cache out of range

@@ -22,8 +22,10 @@ namespace pi {
 // ggml_get_rows on the F16 embedding (+ OPT's learned positions at pos + 2: llama.cpp:5105-5108, 6486-6488)
 __global__ void k_embed(const __half * __restrict__ tok_embd, const __half * __restrict__ pos_embd,
                         const int32_t * __restrict__ tokens, const int32_t * __restrict__ pos, int n_vocab, int n_pos,
-                        int64_t d, float * __restrict__ x) {
+                        int64_t d, float * __restrict__ x, double * __restrict__ stats, int n_stats) {
     const int t = blockIdx.y;
+    if (stats && blockIdx.x == 0 && blockIdx.y == 0)
+        for (int i = threadIdx.x; i < n_stats; i += blockDim.x) stats[i] = 0.0;
     int tok = tokens[t];
     tok = tok < 0 ? 0 : (tok >= n_vocab ? n_vocab - 1 : tok);
     for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < d; c += (int64_t)gridDim.x * blockDim.x) {
@@ -94,7 +96,7 @@ struct pi_engine {
     int G;                                   // axpy row groups
     // device buffers carved from the caller's workspace
     int32_t * tokens, * pos, * seq_ids, * argmax;
-    float * x, * attn_out, * ffn_vec, * qkv, * pred, * h, * partial, * logits, * cs;
+    float * x, * x2, * attn_out, * ffn_vec, * qkv, * pred, * h, * partial, * logits, * cs;
     int32_t * list, * count; unsigned int * ticket; uint32_t * masks;
     int8_t * cq; float * cd;
     __half * hidden16;
@@ -102,12 +104,15 @@ struct pi_engine {
     __half * k_cache, * v_cache;             // [n_layer, max_batch, n_ctx, dkv]
     unsigned int * status;                   // device word: bit 0 = an exchange wait ran out
     unsigned long long * active_total;       // device counter: sum of active-list lengths over layers and steps
+    double * stats;                          // [n_layer + 1][2][2]: {sum, sum of squares} of the vectors the norms read
     pi_exchange xch;
     cudaGraphExec_t graphs[PI_MAX_BATCH + 1];
     bool warmed[PI_MAX_BATCH + 1];
     int launches;                            // kernels enqueued by the last enqueue_step
     float * pred_trace;                      // optional [n_layer, max_batch, F]: keeps every layer's predictor logits
     bool pdl;                                // programmatic dependent launch between the kernels of a step
+    bool fuse;                               // batch 1: consumers build their own normalised input (no norm launches)
+    unsigned skip_mask;                      // PI_SKIP_STAGES: stages left out of the step (timing experiments only; results are garbage)
 };
 
 static size_t up256(size_t v) { return (v + 255) & ~size_t(255); }
@@ -135,8 +140,8 @@ static void carve(pi_engine * e, void * ws, size_t ws_bytes, bool dry, size_t * 
     const int T = e->T_max;
     const size_t d = c.d, F = e->F;
     e->tokens = cv.take<int32_t>(T); e->pos = cv.take<int32_t>(T); e->seq_ids = cv.take<int32_t>(T); e->argmax = cv.take<int32_t>(T);
-    e->status = cv.take<unsigned int>(1); e->active_total = cv.take<unsigned long long>(1);
-    e->x = cv.take<float>(T * d); e->attn_out = cv.take<float>(T * d); e->ffn_vec = cv.take<float>(T * d);
+    e->status = cv.take<unsigned int>(1); e->active_total = cv.take<unsigned long long>(1); e->stats = cv.take<double>((size_t)4 * (c.n_layer + 1));
+    e->x = cv.take<float>(T * d); e->x2 = cv.take<float>(T * d); e->attn_out = cv.take<float>(T * d); e->ffn_vec = cv.take<float>(T * d);
     e->qkv = cv.take<float>((size_t)T * (e->dq + 2 * e->dkv));
     e->pred = cv.take<float>(T * F); e->h = cv.take<float>(T * F);
     e->partial = cv.take<float>((size_t)e->G * T * d);
@@ -216,6 +221,8 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
     memset(&e->xch, 0, sizeof e->xch);
     e->pred_trace = nullptr; e->launches = 0;
     { const char * v = getenv("PI_PDL"); e->pdl = !(v && v[0] == '0'); }
+    { const char * v = getenv("PI_FUSE"); e->fuse = (v && v[0] == '1'); }
+    { const char * v = getenv("PI_SKIP_STAGES"); e->skip_mask = v ? (unsigned)strtoul(v, nullptr, 0) : 0u; }
     cudaStream_t st = (cudaStream_t)stream;
     // one-time device state: sequence ids 0..T-1, zeroed ticket / status, RoPE angle table
     std::vector<int32_t> ids(e->T_max);
@@ -303,6 +310,7 @@ struct StageTimer {
 #define STAGE(stage, n_kernels, call)                    \
     do {                                                 \
         int rc_;                                         \
+        if (e->skip_mask & (1u << (stage))) break;       \
         if ((rc_ = tm.begin())) return rc_;              \
         if ((rc_ = (call))) return rc_;                  \
         if ((rc_ = tm.end(stage))) return rc_;           \
@@ -331,7 +339,10 @@ void norm_inputs(pi_engine * e, int T, const Pending & pd, NormArgs & n) {
     (void)T;
 }
 
+int enqueue_step_fused(pi_engine * e, cudaStream_t st, StageTimer & tm);
+
 int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
+    if (T == 1 && e->fuse && e->c.n_ranks == 1) return enqueue_step_fused(e, st, tm);
     const pi_engine_config & c = e->c;
     const int64_t d = c.d, F = e->F;
     const int wt = c.wtype;
@@ -346,7 +357,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
         const dim3 grid((unsigned)((d + 255) / 256), T);
         if (tm.begin()) return PI_ERR_CUDA;
         k_embed<<<grid, 256, 0, st>>>((const __half *)e->g.tok_embd, (const __half *)e->g.pos_embd, e->tokens, e->pos,
-                                      c.n_vocab, c.n_pos, d, e->x);
+                                      c.n_vocab, c.n_pos, d, e->x, nullptr, 0);
         PI_LAUNCH_CHECK("k_embed");
         if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA;
         e->launches++;
@@ -505,6 +516,144 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             pend.vec = e->ffn_vec;
             pend.res = falcon ? e->attn_out : nullptr;
         }
+    }
+    return PI_OK;
+}
+
+// Batch-1, single-GPU step with the norm launches gone.  The two kernels that finish a residual-stream vector (the
+// out-projection mat-vec, which adds the residual in its epilogue, and the reduction of the axpy partials) also accumulate
+// that vector's {sum, sum of squares}; the mat-vecs that consume the normalised vector (QKV, up/gate, lm head) build it in
+// their prologue from the vector and those two numbers: one pass, no reduction, no extra launch.  The residual stream
+// ping-pongs between two buffers because the producer writes the new one while nothing may still read the old one.
+int enqueue_step_fused(pi_engine * e, cudaStream_t st, StageTimer & tm) {
+    const pi_engine_config & c = e->c;
+    const int T = 1;
+    const int64_t d = c.d, F = e->F;
+    const int wt = c.wtype;
+    const bool falcon = c.arch == PI_ARCH_FALCON;
+    const int norm_kind = c.arch == PI_ARCH_LLAMA ? 1 : 2;
+    const int qkv_rows = e->dq + 2 * e->dkv;
+    const bool pdl = e->pdl && !tm.on;
+    e->launches = 0;
+    float * x_cur = e->x, * x_nxt = e->x2;
+    auto swap_x = [&]() { float * t = x_cur; x_cur = x_nxt; x_nxt = t; };
+    auto stats_of = [&](int il, int which) { return e->stats + ((size_t)il * 2 + which) * 2; };
+    {
+        const dim3 grid((unsigned)((d + 255) / 256), T);
+        if (tm.begin()) return PI_ERR_CUDA;
+        k_embed<<<grid, 256, 0, st>>>((const __half *)e->g.tok_embd, (const __half *)e->g.pos_embd, e->tokens, e->pos,
+                                      c.n_vocab, c.n_pos, d, x_cur, e->stats, 4 * (c.n_layer + 1));
+        PI_LAUNCH_CHECK("k_embed");
+        if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA;
+        e->launches++;
+    }
+    for (int il = 0; il <= c.n_layer; il++) {
+        const bool last = il == c.n_layer;
+        const pi_layer_weights * L = last ? nullptr : &e->layers[il];
+        // statistics of the layer input: layer 0 reads the embedding, whose statistics nobody made (the prologue reduces itself)
+        const double * in_stats = il == 0 ? nullptr : stats_of(il, 0);
+        if (last) {
+            const int out_t = e->g.output ? wt : PI_TYPE_F16;
+            GemvArgs g;
+            g.status = e->status; g.pdl = pdl;
+            g.fin.on = 1; g.fin.vec = x_cur; g.fin.stats = in_stats;
+            g.fin.norm = norm_kind; g.fin.eps = c.norm_eps; g.fin.w = e->g.out_norm_w; g.fin.b = e->g.out_norm_b;
+            g.wtype = out_t; g.W = e->g.output ? e->g.output : e->g.tok_embd; g.nrows = c.n_vocab; g.ncols = d;
+            g.T = T; g.dst = e->logits; g.dst_stride = c.n_vocab;
+            STAGE(PI_STAGE_LM_HEAD, 1, launch_gemv(g, st));
+            if (tm.begin()) return PI_ERR_CUDA;
+            k_argmax<<<T, 1024, 0, st>>>(e->logits, c.n_vocab, e->argmax);
+            PI_LAUNCH_CHECK("k_argmax");
+            if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA;
+            e->launches++;
+            break;
+        }
+        // ---- QKV on norm(layer input)
+        {
+            GemvArgs g;
+            g.status = e->status; g.pdl = pdl;
+            g.fin.on = 1; g.fin.vec = x_cur; g.fin.stats = in_stats;
+            g.fin.norm = norm_kind; g.fin.eps = c.norm_eps;
+            if (falcon && L->attn_norm2_w) { g.fin.w = L->attn_norm2_w; g.fin.b = L->attn_norm2_b; }
+            else                           { g.fin.w = L->attn_norm_w;  g.fin.b = L->attn_norm_b; }
+            g.wtype = wt; g.W = L->wqkv; g.nrows = qkv_rows; g.ncols = d; g.T = T;
+            g.bias = L->bqkv; g.dst = e->qkv; g.dst_stride = qkv_rows;
+            STAGE(PI_STAGE_QKV, 1, launch_gemv(g, st));
+        }
+        {
+            AttnArgs a;
+            a.pdl = pdl;
+            a.q = e->qkv; a.k = e->qkv + e->dq; a.v = e->qkv + e->dq + e->dkv;
+            a.q_stride = qkv_rows; a.kv_stride = qkv_rows;
+            const size_t layer_off = (size_t)il * c.max_batch * c.n_ctx * e->dkv;
+            a.k_cache = e->k_cache + layer_off; a.v_cache = e->v_cache + layer_off;
+            a.seq = e->seq_ids; a.pos = e->pos; a.T = T;
+            a.n_head = c.n_head; a.n_head_kv = c.n_head_kv; a.head_dim = e->hd; a.n_ctx = c.n_ctx;
+            if (c.arch != PI_ARCH_OPT) { a.cs = e->cs; a.neox = falcon; }
+            a.out_act_type = wt; a.out_act = e->act_o;
+            STAGE(PI_STAGE_ATTN, 1, launch_attention(a, st));
+        }
+        // ---- out-projection.  llama / opt: its epilogue finishes ffn_inp = attn_out + x (the new residual stream) and the
+        //      statistics of the FFN norm; falcon keeps attn_out aside, its residual stream does not change here
+        {
+            GemvArgs g;
+            g.status = e->status; g.pdl = pdl;
+            g.wtype = wt; g.W = L->wo; g.nrows = d; g.ncols = e->dq; g.x = e->act_o.view(); g.T = T;
+            g.bias = L->bo; g.dst_stride = d;
+            if (falcon) { g.dst = e->attn_out; }
+            else        { g.dst = x_nxt; g.res_add = x_cur; g.stats_out = stats_of(il, 1); }
+            STAGE(PI_STAGE_WO, 1, launch_gemv(g, st));
+            if (!falcon) swap_x();
+        }
+        // ---- predictor on the (un-normalised) FFN input / layer input
+        float * pred = e->pred_trace ? e->pred_trace + (size_t)il * c.max_batch * F : e->pred;
+        {
+            GemvArgs g1;
+            g1.status = e->status; g1.pdl = pdl;
+            g1.fin.on = 1; g1.fin.vec = x_cur;
+            g1.W = L->fc1; g1.nrows = c.rank; g1.ncols = d; g1.T = T; g1.relu = 1;
+            g1.dst16 = e->hidden16; g1.dst_stride = c.rank;
+            STAGE(PI_STAGE_PRED, 1, launch_gemv(g1, st));
+            Act hx; hx.h16 = e->hidden16;
+            GemvArgs g2;
+            g2.status = e->status; g2.pdl = pdl;
+            g2.W = L->fc2; g2.nrows = F; g2.ncols = c.rank; g2.x = hx; g2.T = T; g2.dst = pred; g2.dst_stride = F;
+            STAGE(PI_STAGE_PRED, 1, launch_gemv(g2, st));
+        }
+        {
+            CompactArgs ca;
+            ca.pdl = pdl;
+            ca.idx = pred; ca.idx_stride = F; ca.T = T; ca.threshold = c.threshold; ca.n_local = F;
+            ca.list = e->list; ca.count = e->count; ca.masks = e->masks; ca.ticket = e->ticket; ca.total = e->active_total;
+            if (wt == PI_TYPE_Q4_0) { ca.zero_dst = e->h; ca.zero_stride = F; ca.fill_bias = L->up_b; ca.fill_relu = 1; }
+            STAGE(PI_STAGE_COMPACT, 1, launch_compact(ca, st));
+        }
+        // ---- up (and gate) over the active rows on the FFN norm (falcon: attn_norm of the layer input)
+        {
+            GemvArgs g;
+            g.status = e->status; g.pdl = pdl;
+            g.fin.on = 1; g.fin.vec = x_cur; g.fin.norm = norm_kind; g.fin.eps = c.norm_eps;
+            if (falcon) { g.fin.w = L->attn_norm_w; g.fin.b = L->attn_norm_b; g.fin.stats = in_stats; }
+            else        { g.fin.w = L->ffn_norm_w;  g.fin.b = L->ffn_norm_b;  g.fin.stats = stats_of(il, 1); }
+            g.wtype = wt; g.W = L->up; g.W2 = L->gate; g.nrows = F; g.ncols = d; g.T = T;
+            g.list = e->list; g.count = e->count; g.idx = pred; g.idx_stride = F; g.threshold = c.threshold;
+            g.bias = L->up_b; g.relu = L->gate ? 0 : 1;
+            g.dst = e->h; g.dst_stride = F;
+            STAGE(PI_STAGE_UPGATE, 1, launch_gemv(g, st));
+        }
+        int used = e->G;
+        {
+            AxpyArgs a;
+            a.pdl = pdl;
+            a.wtype = wt; a.Wt = L->down_t; a.nrows = F; a.ncols = d; a.h = e->h; a.h_stride = F; a.T = T;
+            a.list = e->list; a.count = e->count; a.idx = pred; a.idx_stride = F; a.threshold = c.threshold;
+            a.cq = e->cq; a.cd = e->cd; a.c_stride = F; a.partial = e->partial; a.n_groups = e->G; a.status = e->status;
+            STAGE(PI_STAGE_DOWN, 1, launch_axpy(a, st, &used));
+        }
+        // ---- l_out = (ffn_out + down_b [+ attn_out]) + residual, with the next norm's statistics
+        STAGE(PI_STAGE_DOWN, 1, launch_reduce_partials(e->partial, used, T, d, x_cur, L->down_b, x_nxt, st, pdl,
+                                                       falcon ? e->attn_out : nullptr, stats_of(il + 1, 0)));
+        swap_x();
     }
     return PI_OK;
 }

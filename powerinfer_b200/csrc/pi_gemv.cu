@@ -133,8 +133,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_gemv(const GemvP p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ float s_part[GEMV_WARPS][PAIR * (GATED ? 2 : 1)][TT];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    pdl_wait();
     pdl_launch();
+    pdl_wait();
     constexpr int NR = PAIR * (GATED ? 2 : 1);
     constexpr int ITEMS_PER_CTA = (GEMV_WARPS / SPLIT) * PAIR;
 

@@ -11,6 +11,8 @@
 // Every mbarrier wait is bounded: on expiry the CTA sets bit 2 of *status, stops, and drains its copies.
 #include "pi_common.cuh"
 
+#include <cstdlib>
+
 namespace pi {
 
 static constexpr int QK = 32;
@@ -46,6 +48,8 @@ struct RingP {
     float * dst; __half * dst16;
     unsigned int * status;
     int R, split, stages, max_items; size_t stage_bytes;
+    FusedIn fin;
+    const float * res_add; double * stats_out;
 };
 
 __device__ __forceinline__ int r_block_dot(const uint4 q, const uint4 lo, const uint4 hi, int s8) {
@@ -104,7 +108,186 @@ __device__ __forceinline__ float ring_row_dot(const unsigned char * row, int u_l
     return acc0 + acc1;
 }
 
-template <int WT, bool SPARSE, bool GATED>
+// ---- fused input (see FusedIn): every CTA builds the activation it consumes
+__device__ __forceinline__ double ring_block_sum_d(double v, double * s_red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    v = warp_sum_d(v);
+    __syncthreads();
+    if (lane == 0) s_red[wid] = v;
+    __syncthreads();
+    double t = 0.0;
+#pragma unroll
+    for (int i = 0; i < RING_WARPS; i++) t += s_red[i];
+    return t;
+}
+
+// the 8 values of chunk c8 (columns 8*c8 ..) of v
+__device__ __forceinline__ void fused_load8(const FusedIn & f, const float * slots, int c8, float (&v)[8]) {
+    const size_t o = (size_t)c8 * 8;
+#pragma unroll
+    for (int j = 0; j < 8; j++) v[j] = 0.f;
+    if (f.vec) {
+        const float4 a = __ldcg(reinterpret_cast<const float4 *>(f.vec + o)), b = __ldcg(reinterpret_cast<const float4 *>(f.vec + o + 4));
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        for (int g = 0; g < f.n_slots; g++) {
+            const float * sp = slots + (size_t)g * f.slot_stride + o;
+            const float4 a = __ldcg(reinterpret_cast<const float4 *>(sp)), b = __ldcg(reinterpret_cast<const float4 *>(sp + 4));
+            v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+        }
+    }
+    if (f.bias) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] += f.bias[o + j];
+    }
+    if (f.res1) {
+        const float4 a = __ldcg(reinterpret_cast<const float4 *>(f.res1 + o)), b = __ldcg(reinterpret_cast<const float4 *>(f.res1 + o + 4));
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+    }
+    if (f.res2) {
+        const float4 a = __ldcg(reinterpret_cast<const float4 *>(f.res2 + o)), b = __ldcg(reinterpret_cast<const float4 *>(f.res2 + o + 4));
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+    }
+}
+
+// Builds the staged activation in shared memory (FP16 vector, or Q8_0 planes lo | hi | {scale, sum}) from FusedIn.
+// Values are recomputed in each pass instead of being kept in registers across the kernel's main loop.
+template <int WT>
+__device__ __forceinline__ void ring_build_input(const FusedIn & f, int n, unsigned char * xs, unsigned int * status) {
+    __shared__ double s_red[RING_WARPS];
+    const int tid = threadIdx.x;
+    const int n8 = n / 8, nb = n / QK;
+    const float * slots = f.slots;
+    if (f.wait_flags) {                                             // peers' partial vectors: bounded wait for their flags
+        const unsigned int epoch = *reinterpret_cast<const volatile unsigned int *>(f.wait_epoch);
+        const unsigned int par = epoch & 1u;
+        if (tid < f.n_slots) {
+            const unsigned int * fl = f.wait_flags + par * f.n_slots + tid;
+            const long long t0 = clock64();
+            bool ok = false;
+            for (;;) {
+                unsigned int seen;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(fl));
+                if ((int)(seen - epoch) >= 0) { ok = true; break; }
+                if (clock64() - t0 > 2000000000LL) break;
+                __nanosleep(64);
+            }
+            if (!ok) atomicOr(status, 1u);
+        }
+        __syncthreads();
+        slots += (size_t)par * f.n_slots * f.slot_stride;
+    }
+    float scale = 1.f, mean = 0.f;
+    if (f.norm && f.stats) {
+        const double s1 = __ldcg(f.stats), s2 = __ldcg(f.stats + 1);
+        if (f.norm == 1) {
+            scale = 1.0f / sqrtf((float)(s2 / (double)n) + f.eps);
+        } else {
+            const double m = s1 / (double)n;
+            mean = (float)m;
+            scale = 1.0f / sqrtf((float)(s2 / (double)n - m * m) + f.eps);
+        }
+    } else if (f.norm || (f.x_out && blockIdx.x == 0)) {
+        double s1 = 0.0;
+        for (int c8 = tid; c8 < n8; c8 += RING_THREADS) {
+            float v[8];
+            fused_load8(f, slots, c8, v);
+            if (f.x_out && blockIdx.x == 0) {
+                *reinterpret_cast<float4 *>(f.x_out + (size_t)c8 * 8)     = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4 *>(f.x_out + (size_t)c8 * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) s1 += f.norm == 1 ? (double)(v[j] * v[j]) : (double)v[j];
+        }
+        if (f.norm == 1) {
+            s1 = ring_block_sum_d(s1, s_red);
+            scale = 1.0f / sqrtf((float)(s1 / (double)n) + f.eps);
+        } else if (f.norm == 2) {
+            s1 = ring_block_sum_d(s1, s_red);
+            mean = (float)(s1 / (double)n);
+            double s2 = 0.0;
+            for (int c8 = tid; c8 < n8; c8 += RING_THREADS) {
+                float v[8];
+                fused_load8(f, slots, c8, v);
+#pragma unroll
+                for (int j = 0; j < 8; j++) { const float dv = v[j] - mean; s2 += (double)(dv * dv); }
+            }
+            s2 = ring_block_sum_d(s2, s_red);
+            scale = 1.0f / sqrtf((float)(s2 / (double)n) + f.eps);
+        }
+    }
+    // emit: a thread owns chunk c8; 4 consecutive threads own one Q8_0 block, so every lane takes part in the shuffles.
+    // Two chunks per trip, all their loads (vector, norm weight, norm bias) issued before anything is consumed.
+    const int n8_pad = (n8 + 2 * RING_THREADS - 1) / (2 * RING_THREADS) * (2 * RING_THREADS);
+    for (int c0 = tid; c0 < n8_pad; c0 += 2 * RING_THREADS) {
+        float y[2][8], wv[2][8], bv[2][8];
+        bool valid[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int c8 = c0 + u * RING_THREADS;
+            valid[u] = c8 < n8;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { y[u][j] = 0.f; wv[u][j] = 1.f; bv[u][j] = 0.f; }
+            if (valid[u]) {
+                fused_load8(f, slots, c8, y[u]);
+                if (f.norm && f.w) {
+                    const float4 a = __ldg(reinterpret_cast<const float4 *>(f.w + (size_t)c8 * 8)), b = __ldg(reinterpret_cast<const float4 *>(f.w + (size_t)c8 * 8 + 4));
+                    wv[u][0] = a.x; wv[u][1] = a.y; wv[u][2] = a.z; wv[u][3] = a.w; wv[u][4] = b.x; wv[u][5] = b.y; wv[u][6] = b.z; wv[u][7] = b.w;
+                }
+                if (f.norm && f.b) {
+                    const float4 a = __ldg(reinterpret_cast<const float4 *>(f.b + (size_t)c8 * 8)), b = __ldg(reinterpret_cast<const float4 *>(f.b + (size_t)c8 * 8 + 4));
+                    bv[u][0] = a.x; bv[u][1] = a.y; bv[u][2] = a.z; bv[u][3] = a.w; bv[u][4] = b.x; bv[u][5] = b.y; bv[u][6] = b.z; bv[u][7] = b.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int c8 = c0 + u * RING_THREADS;
+            if (f.norm) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    float r = __fmul_rn(y[u][j] - mean, scale);
+                    if (f.w) r = __fmul_rn(r, wv[u][j]);
+                    if (f.b) r = __fadd_rn(r, bv[u][j]);
+                    y[u][j] = valid[u] ? r : 0.f;
+                }
+            }
+            if (WT == PI_TYPE_F16) {
+                if (valid[u]) {
+                    __half2 hh[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) hh[j] = __floats2half2_rn(y[u][2 * j], y[u][2 * j + 1]);
+                    reinterpret_cast<uint4 *>(xs)[c8] = *reinterpret_cast<uint4 *>(hh);
+                }
+            } else {
+                float amax = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(y[u][j]));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                const float id = amax != 0.0f ? 127.0f / amax : 0.0f;
+                int q[8], sum = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) { q[j] = __float2int_rn(y[u][j] * id); sum += q[j]; }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                if (valid[u]) {
+                    uint2 packed;
+                    packed.x = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+                    packed.y = (uint32_t)(q[4] & 0xFF) | ((uint32_t)(q[5] & 0xFF) << 8) | ((uint32_t)(q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+                    uint4 * lo = reinterpret_cast<uint4 *>(xs);
+                    uint4 * hi = lo + nb;
+                    uint2 * ds = reinterpret_cast<uint2 *>(hi + nb);
+                    const int blk = c8 >> 2, part = c8 & 3;
+                    reinterpret_cast<uint2 *>(part < 2 ? lo + blk : hi + blk)[part & 1] = packed;
+                    if (part == 0) ds[blk] = make_uint2(__float_as_uint(round_f16(amax / 127.0f)), (unsigned)sum);
+                }
+            }
+        }
+    }
+}
+
+template <int WT, bool SPARSE, bool GATED, bool FUSED>
 __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ float s_part[2][RING_WARPS][2];
@@ -120,6 +303,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
     unsigned char * xs = smem + (((size_t)8 * 32 + (size_t)4 * p.max_items + 127) & ~(size_t)127);
     unsigned char * ring = xs + ((x_bytes + 127) & ~(size_t)127);
 
+    pdl_launch();                                                   // let the next kernel become resident and prefetch
     if (tid == 0) {
         for (int s = 0; s < S; s++) r_mbar_init(full + s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -156,7 +340,6 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
         if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
     }
     pdl_wait();
-    pdl_launch();
     if (SPARSE) {
         n_items = min(*p.count, p.nrows);
         const int total_stages = (n_items + R - 1) / R;
@@ -171,7 +354,9 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
         if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
     }
     // ---- stage the activation
-    if (WT == PI_TYPE_F16) {
+    if (FUSED) {
+        ring_build_input<WT>(p.fin, p.ncols, xs, p.status);
+    } else if (WT == PI_TYPE_F16) {
         const uint4 * src = reinterpret_cast<const uint4 *>(p.x.h16);
         uint4 * dstx = reinterpret_cast<uint4 *>(xs);
         for (int i = tid; i < p.ncols / 8; i += RING_THREADS) dstx[i] = src[i];
@@ -189,6 +374,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
     const int units = WT == PI_TYPE_F16 ? p.ncols / 8 : p.nb;       // 16-byte units per row
     const int per = units / split;
     bool dead = false;
+    double st_sum = 0.0, st_sq = 0.0;                               // statistics of what lane 0 of this warp wrote
     for (int st = 0; st < n_stages; st++) {
         const int s = st % S;
         const unsigned parity = (unsigned)(st / S) & 1u;
@@ -216,8 +402,10 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
                     if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
                     if (p.bias) o += p.bias[g];
                     if (p.relu) o = fmaxf(o, 0.f);
+                    if (p.res_add) o += p.res_add[g];
                     if (p.dst)   p.dst[g] = o;
                     if (p.dst16) p.dst16[g] = __float2half_rn(o);
+                    st_sum += (double)o; st_sq += (double)(o * o);
                 }
             }
             __syncthreads();
@@ -241,11 +429,24 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
                 if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
                 if (p.bias) o += p.bias[g];
                 if (p.relu) o = fmaxf(o, 0.f);
+                if (p.res_add) o += p.res_add[g];
                 if (p.dst)   p.dst[g] = o;
                 if (p.dst16) p.dst16[g] = __float2half_rn(o);
+                st_sum += (double)o; st_sq += (double)(o * o);
             }
         }
         if (tid == 0 && !dead && st + S < n_stages) issue(st + S);   // the barrier above freed stage s
+    }
+    if (p.stats_out) {                                              // one pair of atomics per CTA
+        __shared__ double s_stat[RING_WARPS][2];
+        if (lane == 0) { s_stat[warp][0] = st_sum; s_stat[warp][1] = st_sq; }
+        __syncthreads();
+        if (tid == 0) {
+            double a = 0.0, b = 0.0;
+#pragma unroll
+            for (int w = 0; w < RING_WARPS; w++) { a += s_stat[w][0]; b += s_stat[w][1]; }
+            atomicAdd(p.stats_out, a); atomicAdd(p.stats_out + 1, b);
+        }
     }
     if (dead && tid == 0) {                                         // do not exit with copies still landing in shared memory
         for (int s = 0; s < S; s++) { int spins = 0; while (!r_mbar_try_wait(full + s, 0) && !r_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
@@ -254,9 +455,9 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
 
 struct RingPlan { bool ok; int R, split, stages, ctas_per_sm; size_t stage_bytes, smem; int max_items; };
 
-// Four small rings per SM rather than one big one: 32 resident warps hide the shared-memory and ALU latencies of the
-// consumers (with 8 warps the kernel is issue-latency bound), and the copies of the CTAs that are not computing keep
-// 100+ KB per SM in flight.
+// Two 100 KB rings per SM rather than one big one (PI_RING_CPS / PI_RING_KB override): with a single 8-warp CTA the
+// consumers are issue-latency bound, and what matters for bandwidth is ~200 KB of copies in flight per SM; four 54 KB rings
+// measure the same, two 54 KB rings 30 % slower.
 static RingPlan ring_plan(int wtype, int64_t nrows, int64_t ncols, bool sparse, bool gated) {
     RingPlan pl{};
     const size_t row_bytes = pi_row_bytes(wtype, ncols);
@@ -264,11 +465,13 @@ static RingPlan ring_plan(int wtype, int64_t nrows, int64_t ncols, bool sparse, 
     const int units = wtype == PI_TYPE_F16 ? (int)(ncols / 8) : (int)(ncols / QK);
     const int nm = gated ? 2 : 1;
     const size_t x_bytes = wtype == PI_TYPE_F16 ? (size_t)ncols * 2 : (size_t)(ncols / QK) * 40;
-    for (int cps = 4; cps >= 1; cps /= 2) {
-        const size_t budget = (size_t)(cps == 4 ? 54 : (cps == 2 ? 110 : 200)) * 1024;
+    static int cps0 = 0, kb0 = 0;
+    if (!cps0) { const char * v = getenv("PI_RING_CPS"); cps0 = v ? atoi(v) : 2; const char * k = getenv("PI_RING_KB"); kb0 = k ? atoi(k) : 100; }
+    for (int cps = cps0; cps >= 1; cps /= 2) {
+        const size_t budget = (size_t)(cps == cps0 ? kb0 : (cps == 2 ? 110 : 200)) * 1024;
         const int G = sm_count() * cps;
         int R = 1;
-        while (R < 64 && (size_t)(2 * R) * nm * row_bytes <= (cps == 4 ? 19 : 36) * 1024) R *= 2;
+        while (R < 64 && (size_t)(2 * R) * nm * row_bytes <= (budget <= 64 * 1024 ? 19 : 36) * 1024) R *= 2;
         const int split = R >= RING_WARPS ? 1 : RING_WARPS / R;
         if (split > 1 && units % (split * 32) != 0) continue;
         const int max_items = sparse ? (int)((((nrows + G - 1) / G + R - 1) / R + 1) * R) : 0;
@@ -286,12 +489,12 @@ static RingPlan ring_plan(int wtype, int64_t nrows, int64_t ncols, bool sparse, 
     return pl;
 }
 
-template <int WT, bool SPARSE, bool GATED>
+template <int WT, bool SPARSE, bool GATED, bool FUSED>
 static int launch_ring_inst(const RingP & p, const RingPlan & pl, bool pdl, cudaStream_t st) {
     static bool attr_done[16] = {false};
     int dev = 0;
     PI_CUDA(cudaGetDevice(&dev));
-    auto kern = k_gemv_ring<WT, SPARSE, GATED>;
+    auto kern = k_gemv_ring<WT, SPARSE, GATED, FUSED>;
     if (dev >= 0 && dev < 16 && !attr_done[dev]) {
         PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
         attr_done[dev] = true;
@@ -316,12 +519,21 @@ int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaSt
     p.W = (const uint8_t *)a.W; p.W2 = (const uint8_t *)a.W2; p.row_bytes = (int64_t)pi_row_bytes(a.wtype, a.ncols);
     p.nrows = (int)a.nrows; p.ncols = (int)a.ncols; p.nb = (int)(a.ncols / QK); p.x = a.x;
     p.list = a.list; p.count = a.count; p.bucket = a.bucket; p.idx = a.idx; p.threshold = a.threshold;
-    p.bias = a.bias; p.relu = a.relu; p.dst = a.dst; p.dst16 = a.dst16; p.status = status;
+    p.bias = a.bias; p.relu = a.relu; p.dst = a.dst; p.dst16 = a.dst16; p.status = status; p.fin = a.fin; p.res_add = a.res_add; p.stats_out = a.stats_out;
     p.R = pl.R; p.split = pl.split; p.stages = pl.stages; p.max_items = pl.max_items; p.stage_bytes = pl.stage_bytes;
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
-    if (!sparse) return q4 ? launch_ring_inst<PI_TYPE_Q4_0, false, false>(p, pl, pdl, st) : launch_ring_inst<PI_TYPE_F16, false, false>(p, pl, pdl, st);
-    if (gated)   return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, true>(p, pl, pdl, st)   : launch_ring_inst<PI_TYPE_F16, true, true>(p, pl, pdl, st);
-    return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, false>(p, pl, pdl, st) : launch_ring_inst<PI_TYPE_F16, true, false>(p, pl, pdl, st);
+#define PI_RING_DISPATCH(FUSED)                                                                                                            \
+    do {                                                                                                                                   \
+        if (!sparse) return q4 ? launch_ring_inst<PI_TYPE_Q4_0, false, false, FUSED>(p, pl, pdl, st)                                       \
+                               : launch_ring_inst<PI_TYPE_F16, false, false, FUSED>(p, pl, pdl, st);                                       \
+        if (gated)   return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, true, FUSED>(p, pl, pdl, st)                                         \
+                               : launch_ring_inst<PI_TYPE_F16, true, true, FUSED>(p, pl, pdl, st);                                         \
+        return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, false, FUSED>(p, pl, pdl, st)                                                     \
+                  : launch_ring_inst<PI_TYPE_F16, true, false, FUSED>(p, pl, pdl, st);                                                     \
+    } while (0)
+    if (a.fin.on) PI_RING_DISPATCH(true);
+    PI_RING_DISPATCH(false);
+#undef PI_RING_DISPATCH
 }
 
 }  // namespace pi

@@ -2,6 +2,8 @@
 // scatter-accumulate behind ggml_axpy over the rows of ffn_down_t named by that list.
 #include "pi_common.cuh"
 
+#include <cstdlib>
+
 namespace pi {
 
 static constexpr int QK = 32;
@@ -29,8 +31,8 @@ __global__ void __launch_bounds__(COMPACT_THREADS) k_compact(const CompactP p) {
     const int tid = threadIdx.x, lane = tid & 31;
     const int n_chunks = (p.n_local + 31) / 32;
     const int warps_total = gridDim.x * (COMPACT_THREADS / 32);
-    pdl_wait();
     pdl_launch();
+    pdl_wait();
     for (int c = blockIdx.x * (COMPACT_THREADS / 32) + (tid >> 5); c < n_chunks; c += warps_total) {
         const int r = c * 32 + lane;
         bool any = false;
@@ -317,8 +319,8 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    pdl_wait();
     pdl_launch();
+    pdl_wait();
     const int n = min(*p.count, p.nrows);
     int n_mine = cta < n ? (n - cta + G - 1) / G : 0;
     n_mine = min(n_mine, p.max_rows);
@@ -469,7 +471,8 @@ static PipePlan pipe_plan(int wtype, int64_t nrows, int64_t ncols) {
         if (pl.cpt > 2) return pl;
     }
     const size_t head = ((size_t)8 * 32 + (size_t)8 * pl.max_rows + 127 + 128) & ~size_t(127);
-    const size_t budget = 200 * 1024;
+    static size_t budget = 0;
+    if (!budget) { const char * v = getenv("PI_AXPY_KB"); budget = (size_t)(v ? atoi(v) : 200) * 1024; }
     int S = (int)((budget - head) / (row_stride * PIPE_RS));
     S = S > 16 ? 16 : S;
     if (S < 2) return pl;
@@ -560,11 +563,12 @@ static constexpr int RED_WARPS = 16;
 
 __global__ void __launch_bounds__(RED_WARPS * 32) k_reduce_partials(const float * __restrict__ partial, int G, int64_t total, int64_t n,
                                                                      const float * __restrict__ residual, const float * __restrict__ bias,
-                                                                     float * __restrict__ dst) {
+                                                                     float * __restrict__ dst, const float * __restrict__ residual2,
+                                                                     double * __restrict__ stats_out) {
     __shared__ float4 s_part[RED_WARPS][32];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    pdl_wait();
     pdl_launch();
+    pdl_wait();
     const int64_t i4 = (int64_t)blockIdx.x * 32 + lane;                // float4 index
     const bool ok = i4 * 4 < total;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -587,18 +591,25 @@ __global__ void __launch_bounds__(RED_WARPS * 32) k_reduce_partials(const float 
         for (int k = 1; k < RED_WARPS; k++) { const float4 a = s_part[k][lane]; v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w; }
         const int64_t i = i4 * 4;
         if (bias) { const int64_t c = i % n; v.x += bias[c]; v.y += bias[c + 1]; v.z += bias[c + 2]; v.w += bias[c + 3]; }
+        if (residual2) { const float4 r = *reinterpret_cast<const float4 *>(residual2 + i); v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w; }
         if (residual) { const float4 r = *reinterpret_cast<const float4 *>(residual + i); v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w; }
         *reinterpret_cast<float4 *>(dst + i) = v;
+    }
+    if (w == 0 && stats_out) {                                         // the next norm's statistics ride along (T == 1)
+        double s1 = ok ? (double)v.x + (double)v.y + (double)v.z + (double)v.w : 0.0;
+        double s2 = ok ? (double)(v.x * v.x) + (double)(v.y * v.y) + (double)(v.z * v.z) + (double)(v.w * v.w) : 0.0;
+        s1 = warp_sum_d(s1); s2 = warp_sum_d(s2);
+        if (lane == 0) { atomicAdd(stats_out, s1); atomicAdd(stats_out + 1, s2); }
     }
 }
 
 int launch_reduce_partials(const float * partial, int n_groups, int T, int64_t n, const float * residual,
-                           const float * bias, float * dst, cudaStream_t st, bool pdl) {
+                           const float * bias, float * dst, cudaStream_t st, bool pdl, const float * residual2, double * stats_out) {
     const int64_t total = (int64_t)T * n;
     if (total == 0) return PI_OK;
     PI_REQUIRE(n % 4 == 0, "reduce: n must be a multiple of 4");
     const int grid = (int)((total / 4 + 31) / 32);
-    PI_CUDA(launch_k(k_reduce_partials, dim3(grid), dim3(RED_WARPS * 32), 0, st, pdl, partial, n_groups, total, n, residual, bias, dst));
+    PI_CUDA(launch_k(k_reduce_partials, dim3(grid), dim3(RED_WARPS * 32), 0, st, pdl, partial, n_groups, total, n, residual, bias, dst, residual2, stats_out));
     return PI_OK;
 }
 

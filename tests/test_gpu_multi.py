@@ -1,0 +1,92 @@
+"""Sharded decode on 2 GPUs (neuron + head sharding, mailbox exchange over NVLink) against the CPU checker.
+
+Needs two devices; skipped otherwise.  Ranks are child processes with NCCL's NVLS switched off (the process group only
+hands IPC handles around and keeps the ranks in step); the exchange itself uses plain peer stores and bounded waits.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+from powerinfer_b200 import synth  # noqa: E402
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+SPECS = {
+    "llama_f16": synth.ModelSpec(arch=synth.ARCH_LLAMA, wtype=synth.F16, n_layer=3, d=512, n_ff=2048, n_head=8, n_head_kv=2, rank=64,
+                                 firing=0.15, seed=31),
+    "llama_q4_0": synth.ModelSpec(arch=synth.ARCH_LLAMA, wtype=synth.Q4_0, n_layer=2, d=512, n_ff=2048, n_head=4, n_head_kv=2, rank=64,
+                                  firing=0.15, seed=32),
+    "falcon_f16": synth.ModelSpec(arch=synth.ARCH_FALCON, wtype=synth.F16, n_layer=2, d=512, n_ff=2048, n_head=8, n_head_kv=2, rank=64,
+                                  firing=0.15, seed=33),
+    "opt_f16": synth.ModelSpec(arch=synth.ARCH_OPT, wtype=synth.F16, n_layer=2, d=256, n_ff=1280, n_head=4, n_head_kv=4, rank=64,
+                               firing=0.15, seed=34, norm_eps=0.0),
+}
+
+
+def _worker(rank, world, port, name, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from oracle import pio
+    from powerinfer_b200 import engine
+    spec = SPECS[name]
+    t = synth.build_model(spec)
+    eng = engine.DecodeEngine(spec, t, max_batch=2, n_ranks=world, rank=rank)
+    eng.setup_exchange()
+    eng.enable_trace()
+    om = pio.OracleModel(spec, t)
+    worst, n_flip_steps, cur = 0.0, 0, 9
+    F = spec.n_ff // world
+    for pos in range(12):
+        logits, amax = eng.decode([cur], [pos])
+        ref, pred = om.decode(cur, pos, want_pred=True)
+        got = eng.predictor_trace(1)[:, 0]                      # this rank's neurons
+        ref_local = pred[:, rank * F:(rank + 1) * F]
+        flips = (got >= 0) != (ref_local >= 0)
+        assert np.all(np.abs(ref_local[flips]) <= 1e-3)
+        nf = torch.tensor([int(flips.sum())], device="cuda")
+        dist.all_reduce(nf)
+        if int(nf.item()) == 0:
+            worst = max(worst, float(np.abs(logits[0] - ref).max()))
+        else:
+            n_flip_steps += 1
+        cur = int(ref.argmax())
+    eng.status()
+    # a batch of two sequences through the sharded engine equals two single runs of it
+    eng.k_cache.zero_(); eng.v_cache.zero_(); torch.cuda.synchronize(); dist.barrier()
+    a = [eng.decode([11], [0])[0][0].copy(), eng.decode([12], [1])[0][0].copy()]
+    eng.k_cache.zero_(); eng.v_cache.zero_(); torch.cuda.synchronize(); dist.barrier()
+    eng.decode([11, 40], [0, 0])
+    b = eng.decode([12, 41], [1, 1])[0][0].copy()
+    np.save(os.path.join(out_dir, f"{name}_r{rank}.npy"), np.array([worst, n_flip_steps, float(np.abs(a[1] - b).max())]))
+    all_logits = [torch.empty(spec.n_vocab, device="cuda") for _ in range(world)]
+    dist.all_gather(all_logits, torch.from_numpy(b).cuda())
+    assert all(torch.equal(all_logits[0], x) for x in all_logits)   # every rank holds the same logits, bit for bit
+    eng.close()
+    om.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name", sorted(SPECS))
+def test_two_gpu_sharded_decode_matches_reference(tmp_path, name):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 CUDA devices")
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(2, _free_port(), name, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        worst, n_flip_steps, batch_err = np.load(tmp_path / f"{name}_r{r}.npy")
+        assert worst <= 5e-3, worst
+        assert n_flip_steps <= 9          # steps where a borderline neuron (within 1e-3 of the threshold) came out differently
+        assert batch_err <= 1e-3
