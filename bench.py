@@ -196,6 +196,7 @@ def main():
     from powerinfer_b200 import engine, synth_device
 
     torch.cuda.set_device(local_rank)
+    os.environ.setdefault("NCCL_DEBUG", "WARN")          # keep NCCL's version banner off stdout: the JSON line is the only output
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 

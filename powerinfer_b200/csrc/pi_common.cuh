@@ -142,6 +142,8 @@ struct CompactArgs {
     uint32_t * masks = nullptr;        // scratch: one word per 32 local rows
     unsigned int * ticket = nullptr;   // scratch: one word, must be 0 on entry, is 0 again on exit
     unsigned long long * total = nullptr;   // optional running sum of the counts (statistics)
+    // optional balanced split for the fused sparse FFN: parts[n_parts + 1] chunk boundaries, chunk_off[n_chunks + 1] scratch
+    int32_t * parts = nullptr; int n_parts = 0; int32_t * chunk_off = nullptr;
     bool pdl = false;
 };
 int launch_compact(const CompactArgs & a, cudaStream_t st);
@@ -163,6 +165,22 @@ int axpy_groups(int wtype, int64_t ncols, int T);                     // row gro
 int launch_axpy(const AxpyArgs & a, cudaStream_t st, int * groups_used = nullptr);   // groups_used: partial vectors written
 // h F32 [T, stride] -> Q8_0 over 32-neuron blocks: cq int8 [T, stride], cd float [T, stride/32]
 int launch_neuron_q8(const float * h, int64_t stride, int64_t n, int T, int8_t * cq, float * cd, cudaStream_t st);
+
+// Batch-1 fused sparse FFN: up (and gate) mat-vec over the active rows, activation, axpy coefficient and the down
+// accumulation in ONE kernel; each CTA owns a contiguous range of 32-neuron chunks (CompactArgs::parts).
+struct SparseFfnArgs {
+    int wtype = PI_TYPE_F16;
+    const void * up = nullptr; const void * gate = nullptr; const void * down_t = nullptr;
+    int64_t nrows = 0, ncols = 0;
+    Act x;                                         // FFN input in the form the weights consume
+    const uint32_t * masks = nullptr; const int32_t * parts = nullptr; int n_parts = 0;
+    const float * up_b = nullptr;                  // opt: h = relu(up + b)
+    float * partial = nullptr;                     // [n_parts, ncols]
+    unsigned int * status = nullptr;
+    bool pdl = false;
+};
+int sparse_ffn_parts();                            // CTAs (= partial vectors) the fused kernel uses
+int launch_sparse_ffn(const SparseFfnArgs & a, cudaStream_t st);   // PI_ERR_UNSUPPORTED: shape not eligible
 
 // sum partial [n_groups, T, n] in group order (+ residual + bias) -> dst [T, n]
 int launch_reduce_partials(const float * partial, int n_groups, int T, int64_t n, const float * residual,

@@ -112,6 +112,8 @@ struct pi_engine {
     float * pred_trace;                      // optional [n_layer, max_batch, F]: keeps every layer's predictor logits
     bool pdl;                                // programmatic dependent launch between the kernels of a step
     bool fuse;                               // batch 1: consumers build their own normalised input (no norm launches)
+    bool ffn_fused;                          // batch 1: one kernel for up/gate + activation + down (PI_FFN_FUSED=1; off by default: parity-green but measured slower than the two-kernel path)
+    int32_t * parts, * chunk_off;            // balanced chunk split made by the compaction for that kernel
     unsigned skip_mask;                      // PI_SKIP_STAGES: stages left out of the step (timing experiments only; results are garbage)
 };
 
@@ -149,6 +151,7 @@ static void carve(pi_engine * e, void * ws, size_t ws_bytes, bool dry, size_t * 
     e->cs = cv.take<float>((size_t)c.n_ctx * e->hd);
     e->list = cv.take<int32_t>(F); e->count = cv.take<int32_t>(1); e->ticket = cv.take<unsigned int>(1);
     e->masks = cv.take<uint32_t>((F + 31) / 32);
+    e->parts = cv.take<int32_t>(1024); e->chunk_off = cv.take<int32_t>((F + 31) / 32 + 1);
     e->cq = cv.take<int8_t>(T * F); e->cd = cv.take<float>(T * (F / 32 + 1));
     e->hidden16 = cv.take<__half>((size_t)T * c.rank);
     e->act_a = cv.act(c.wtype, c.d, T);
@@ -222,6 +225,7 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
     e->pred_trace = nullptr; e->launches = 0;
     { const char * v = getenv("PI_PDL"); e->pdl = !(v && v[0] == '0'); }
     { const char * v = getenv("PI_FUSE"); e->fuse = (v && v[0] == '1'); }
+    { const char * v = getenv("PI_FFN_FUSED"); e->ffn_fused = (v && v[0] == '1'); }
     { const char * v = getenv("PI_SKIP_STAGES"); e->skip_mask = v ? (unsigned)strtoul(v, nullptr, 0) : 0u; }
     cudaStream_t st = (cudaStream_t)stream;
     // one-time device state: sequence ids 0..T-1, zeroed ticket / status, RoPE angle table
@@ -474,16 +478,36 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             g2.W = L->fc2; g2.nrows = F; g2.ncols = c.rank; g2.x = hx; g2.T = T; g2.dst = pred; g2.dst_stride = F;
             STAGE(PI_STAGE_PRED, (T + 7) / 8, launch_gemv(g2, st));
         }
-        // ---- mask -> active list.  Where a row is inactive for a token the dense hidden vector holds 0 (or relu(bias)):
-        //      the Q4_0 axpy quantises that vector per 32 neurons, and a union list leaves per-token holes.
+        // ---- mask -> active list (and, for batch 1, a balanced split of the 32-neuron chunks over the SMs).
+        //      Where a row is inactive for a token the dense hidden vector holds 0 (or relu(bias)): the Q4_0 axpy quantises
+        //      that vector per 32 neurons, and a union list leaves per-token holes.
+        const bool fuse_ffn = T == 1 && e->ffn_fused;
         {
             CompactArgs ca;
             ca.pdl = pdl;
             ca.idx = pred; ca.idx_stride = F; ca.T = T; ca.threshold = c.threshold; ca.n_local = F;
             ca.list = e->list; ca.count = e->count; ca.masks = e->masks; ca.ticket = e->ticket; ca.total = e->active_total;
-            if (wt == PI_TYPE_Q4_0) { ca.zero_dst = e->h; ca.zero_stride = F; ca.fill_bias = L->up_b; ca.fill_relu = 1; }
+            if (fuse_ffn) { ca.parts = e->parts; ca.n_parts = sparse_ffn_parts(); ca.chunk_off = e->chunk_off; }
+            else if (wt == PI_TYPE_Q4_0) { ca.zero_dst = e->h; ca.zero_stride = F; ca.fill_bias = L->up_b; ca.fill_relu = 1; }
             STAGE(PI_STAGE_COMPACT, 1, launch_compact(ca, st));
         }
+        int used = e->G;
+        bool ffn_done = false;
+        if (fuse_ffn) {
+            // ---- up (+ gate), activation, coefficients and down in one kernel
+            SparseFfnArgs fa;
+            fa.wtype = wt; fa.up = L->up; fa.gate = L->gate; fa.down_t = L->down_t; fa.nrows = F; fa.ncols = d;
+            fa.x = e->act_a.view(); fa.masks = e->masks; fa.parts = e->parts; fa.n_parts = sparse_ffn_parts();
+            fa.up_b = L->up_b; fa.partial = e->partial; fa.status = e->status; fa.pdl = pdl;
+            if (!(e->skip_mask & (1u << PI_STAGE_UPGATE))) {
+                if (tm.begin()) return PI_ERR_CUDA;
+                const int rc = launch_sparse_ffn(fa, st);
+                if (rc == PI_OK) { if (tm.end(PI_STAGE_UPGATE)) return PI_ERR_CUDA; e->launches++; ffn_done = true; used = fa.n_parts; }
+                else if (rc != PI_ERR_UNSUPPORTED) return rc;
+                else if (tm.on) { if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA; }
+            } else { ffn_done = true; used = fa.n_parts; }
+        }
+        if (!ffn_done) {
         // ---- up (and gate) over the active rows: h = relu(gate.x) * (up.x) | relu(up.x + b)
         {
             GemvArgs g;
@@ -496,7 +520,6 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
         }
         // ---- down: axpy over the same list, then the sum over row groups (and, sharded, over ranks)
         if (wt == PI_TYPE_Q4_0 && T > 1) STAGE(PI_STAGE_DOWN, 1, launch_neuron_q8(e->h, F, F, T, e->cq, e->cd, st));
-        int used = e->G;
         {
             AxpyArgs a;
             a.pdl = pdl;
@@ -504,6 +527,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             a.list = e->list; a.count = e->count; a.idx = pred; a.idx_stride = F; a.threshold = c.threshold;
             a.cq = e->cq; a.cd = e->cd; a.c_stride = F; a.partial = e->partial; a.n_groups = e->G; a.status = e->status;
             STAGE(PI_STAGE_DOWN, T == 1 ? 1 : (wt == PI_TYPE_Q4_0 ? (T + 1) / 2 : (T + 3) / 4), launch_axpy(a, st, &used));
+        }
         }
         pend = Pending();
         pend.bias = L->down_b;
@@ -748,7 +772,7 @@ int pi_engine_status(pi_engine * e, void * stream) {
     PI_CUDA(cudaMemcpyAsync(&s, e->status, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     PI_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (s & 1u) { set_error("an exchange wait ran out: a peer rank did not deliver its partial vector"); return PI_ERR_TIMEOUT; }
-    if (s & 6u) { set_error("a bulk-copy wait ran out in a weight-streaming kernel (status %u)", s); return PI_ERR_TIMEOUT; }
+    if (s & 14u) { set_error("a bulk-copy wait ran out in a weight-streaming kernel (status %u)", s); return PI_ERR_TIMEOUT; }
     return PI_OK;
 }
 

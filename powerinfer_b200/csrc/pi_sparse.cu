@@ -23,6 +23,7 @@ struct CompactP {
     float * zero_dst; int64_t zero_stride;
     const float * fill_bias; int fill_relu;
     unsigned long long * total;
+    int32_t * parts; int n_parts; int32_t * chunk_off;
 };
 
 __global__ void __launch_bounds__(COMPACT_THREADS) k_compact(const CompactP p) {
@@ -75,6 +76,11 @@ __global__ void __launch_bounds__(COMPACT_THREADS) k_compact(const CompactP p) {
     int base = 0;
     for (int w = 0; w < (tid >> 5); w++) base += s_warp_sums[w];
     int off = base + incl - mine;
+    if (p.parts) {                                                  // exclusive prefix per 32-row chunk, for the balanced split below
+        int o = off;
+        for (int c = c0; c < c1; c++) { p.chunk_off[c] = o; o += __popc(__ldcg(p.masks + c)); }
+        if (tid == COMPACT_THREADS - 1) p.chunk_off[n_chunks] = base + incl;
+    }
     for (int c = c0; c < c1; c++) {
         uint32_t m = __ldcg(p.masks + c);
         while (m) {
@@ -87,6 +93,28 @@ __global__ void __launch_bounds__(COMPACT_THREADS) k_compact(const CompactP p) {
         *p.count = base + incl; *p.ticket = 0u;
         if (p.total) *p.total += (unsigned long long)(base + incl);      // only this thread of this CTA ever writes it
     }
+    if (p.parts) {
+        // Split the chunks into n_parts contiguous ranges of (nearly) equal active-row count: part j starts at the first
+        // chunk whose exclusive prefix reaches j * total / n_parts.  Whole chunks (32 consecutive neurons) stay together,
+        // which is what the Q4_0 axpy coefficient (quantised per 32 neurons) needs.
+        __shared__ int s_total;
+        if (tid == COMPACT_THREADS - 1) s_total = base + incl;
+        __threadfence_block();
+        __syncthreads();
+        const int total = s_total;
+        for (int j = tid; j <= p.n_parts; j += COMPACT_THREADS) {
+            int lo = 0, hi = n_chunks;                                  // lower_bound over chunk_off[0..n_chunks]
+            if (j == p.n_parts) { lo = n_chunks; }
+            else if (j > 0) {
+                const int target = (int)(((long long)j * total + p.n_parts - 1) / p.n_parts);
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (p.chunk_off[mid] >= target) hi = mid; else lo = mid + 1;
+                }
+            }
+            p.parts[j] = lo;
+        }
+    }
 }
 
 int launch_compact(const CompactArgs & a, cudaStream_t st) {
@@ -95,6 +123,7 @@ int launch_compact(const CompactArgs & a, cudaStream_t st) {
     p.n_local = (int)a.n_local; p.bucket = a.bucket; p.list = a.list; p.count = a.count;
     p.masks = a.masks; p.ticket = a.ticket;
     p.zero_dst = a.zero_dst; p.zero_stride = a.zero_stride; p.fill_bias = a.fill_bias; p.fill_relu = a.fill_relu; p.total = a.total;
+    p.parts = a.parts; p.n_parts = a.n_parts; p.chunk_off = a.chunk_off;
     const int n_chunks = (int)((a.n_local + 31) / 32);
     int grid = (n_chunks + COMPACT_THREADS / 32 - 1) / (COMPACT_THREADS / 32);
     grid = max(1, min(grid, sm_count()));

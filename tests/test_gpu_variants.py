@@ -1,0 +1,52 @@
+"""Alternative launch sequences of the batch-1 step (kept behind environment switches) must give the same results as the
+default one: the fused sparse-FFN kernel (PI_FFN_FUSED=1), consumer-side norms (PI_FUSE=1), no programmatic dependent
+launch (PI_PDL=0).  Each variant runs in a child process because the switches are read when an engine is created."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+SCRIPT = r"""
+import sys, numpy as np
+sys.path.insert(0, %r); sys.path.insert(0, %r + '/tests/golden')
+import torch
+import make_golden as mg
+from powerinfer_b200 import synth, engine
+out = {}
+for name in ('llama_q4_0', 'llama_gqa_f16', 'falcon_f16', 'opt_f16'):
+    spec = mg.MODEL_CASES[name]
+    eng = engine.DecodeEngine(spec, synth.build_model(spec), max_batch=1)
+    logs = []
+    for pos, tok in enumerate([5, 17, 300, 41, 9, 77]):
+        logs.append(eng.decode([tok], [pos])[0][0].copy())
+    eng.status()
+    eng.close()
+    out[name] = np.stack(logs)
+np.savez(sys.argv[1], **out)
+""" % (ROOT, ROOT)
+
+
+def run_variant(tmp_path, tag, env):
+    import numpy as np
+    path = str(tmp_path / f"{tag}.npz")
+    e = dict(os.environ)
+    e.update(env)
+    subprocess.run([sys.executable, "-c", SCRIPT, path], check=True, env=e)
+    return np.load(path)
+
+
+def test_step_variants_agree(tmp_path):
+    import numpy as np
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    base = run_variant(tmp_path, "base", {})
+    for tag, env in (("ffn_fused", {"PI_FFN_FUSED": "1"}), ("fused_norms", {"PI_FUSE": "1"}), ("no_pdl", {"PI_PDL": "0"})):
+        got = run_variant(tmp_path, tag, env)
+        for name in base.files:
+            err = float(np.abs(got[name] - base[name]).max())
+            assert err <= 5e-3, (tag, name, err)      # same math, different summation order / activation re-rounding
