@@ -100,6 +100,9 @@ struct FusedIn {
     const double * stats = nullptr;    // {sum, sum of squares} of v accumulated by the kernel that produced `vec`: no reduction here
 };
 
+// Byte ranges for l2_prefetch() below.
+struct Prefetch { const void * ptr[2] = {nullptr, nullptr}; size_t bytes[2] = {0, 0}; };
+
 struct GemvArgs {
     int wtype = PI_TYPE_F16;
     const void * W = nullptr;          // [nrows, ncols]
@@ -147,6 +150,9 @@ struct CompactArgs {
     bool pdl = false;
 };
 int launch_compact(const CompactArgs & a, cudaStream_t st);
+
+// pulls the byte ranges into L2 (a hint; nothing may depend on it)
+int launch_prefetch(const Prefetch & pf, cudaStream_t st);
 
 struct AxpyArgs {
     int wtype = PI_TYPE_F16;
@@ -235,6 +241,24 @@ int launch_exchange_push(const pi_exchange & x, const float * partial, int n_gro
 // pdl_launch() lets the NEXT kernel be scheduled early.  Both are no-ops for a normally launched kernel.
 __device__ __forceinline__ void pdl_wait()   { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Up to two byte ranges (weights of kernels that run later in the step) to pull into L2.  Every participating thread
+// issues bulk L2 prefetches for 8 KB pieces, pieces interleaved over all participating threads so the range arrives
+// front to back, the order the consumer streams it in.  A hint only: nothing waits for it and nothing depends on it.
+__device__ __forceinline__ void l2_prefetch(const Prefetch & pf, int part, int n_parts, int tid, int nthreads) {
+    constexpr size_t PIECE = 8192;
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        if (!pf.ptr[k]) continue;
+        const size_t bytes = pf.bytes[k] & ~size_t(15);
+        const size_t n_piece = (bytes + PIECE - 1) / PIECE;
+        for (size_t c = (size_t)part * nthreads + tid; c < n_piece; c += (size_t)n_parts * nthreads) {
+            const size_t off = c * PIECE;
+            const unsigned sz = (unsigned)(bytes - off < PIECE ? bytes - off : PIECE);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(reinterpret_cast<const char *>(pf.ptr[k]) + off), "r"(sz) : "memory");
+        }
+    }
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args) {

@@ -191,6 +191,18 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
     }
 }
 
+// One CTA per SM, every thread issues bulk L2 prefetches for its pieces: no shared memory and few registers, so the
+// CTAs fit beside whatever the main chain has resident.
+__global__ void __launch_bounds__(128) k_prefetch(const Prefetch pf) {
+    l2_prefetch(pf, (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, (int)blockDim.x);
+}
+
+int launch_prefetch(const Prefetch & pf, cudaStream_t st) {
+    k_prefetch<<<sm_count(), 128, 0, st>>>(pf);
+    PI_LAUNCH_CHECK("k_prefetch");
+    return PI_OK;
+}
+
 int launch_norm(const NormArgs & a, cudaStream_t st) {
     if (a.T <= 0) return PI_OK;
     PI_REQUIRE(a.n % 8 == 0 && a.n <= (int64_t)NORM_CHUNKS * 1024 * 8, "norm: n=%lld must be a multiple of 8 and <= %d",
@@ -273,10 +285,28 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     const int group = p.n_head / p.n_head_kv, hk = h / group;
     const int dkv = p.n_head_kv * hd;
     pdl_launch();
-    pdl_wait();
+    // ---- before the wait: everything that no kernel of this step writes.  The position is set between steps and the
+    //      cache rows below it were stored by earlier steps, so their loads (the long latency chain of this kernel)
+    //      overlap the tail of the QKV mat-vec.
     const int pos = p.pos[t];
     const int sq = p.seq ? p.seq[t] : 0;
     if (pos < 0 || pos >= p.n_ctx) return;                       // never index the cache out of range
+    __half * kc = p.k_cache + (size_t)sq * p.n_ctx * dkv + (size_t)hk * hd;
+    __half * vc = p.v_cache + (size_t)sq * p.n_ctx * dkv + (size_t)hk * hd;
+    const int slices = ATTN_THREADS / chunks;
+    const int c8 = tid % chunks, sl = tid / chunks;
+    // L2 prefetch hints cost no registers, so this CTA still fits beside the mat-vec CTAs it overlaps with
+    for (int j = tid; j < pos; j += ATTN_THREADS) {
+        const char * kr = reinterpret_cast<const char *>(kc + (size_t)j * dkv);
+        const char * vr = reinterpret_cast<const char *>(vc + (size_t)j * dkv);
+        for (int o = 0; o < hd * 2; o += 128) {
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(kr + o));
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(vr + o));
+        }
+    }
+    float2 cs_reg = make_float2(1.f, 0.f);
+    if (p.cs && tid < half) cs_reg = reinterpret_cast<const float2 *>(p.cs)[(size_t)pos * half + tid];
+    pdl_wait();
 
     float *  sc  = reinterpret_cast<float *>(smem_raw);          // scores, then exp values, then the output slices
     float *  q32 = sc + p.sc_floats;                             // [hd] q rounded to FP16, widened
@@ -289,21 +319,19 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     const float * vh = p.v + (size_t)t * p.kv_stride + (size_t)hk * hd;
     for (int e = tid; e < hd; e += ATTN_THREADS) v16[e] = __float2half_rn(vh[e]);
     if (p.cs) {
-        for (int k = tid; k < half; k += ATTN_THREADS) {
-            const float2 a = reinterpret_cast<const float2 *>(p.cs)[(size_t)pos * half + k];
+        if (tid < half) {                                        // half <= 128 < ATTN_THREADS
+            const int k = tid;
             const int i0 = p.neox ? k : 2 * k, i1 = p.neox ? k + half : 2 * k + 1;
             float o0, o1;
-            rope_pair(qh[i0], qh[i1], a.x, a.y, o0, o1);
+            rope_pair(qh[i0], qh[i1], cs_reg.x, cs_reg.y, o0, o1);
             q32[i0] = round_f16(o0); q32[i1] = round_f16(o1);
-            rope_pair(kh[i0], kh[i1], a.x, a.y, o0, o1);
+            rope_pair(kh[i0], kh[i1], cs_reg.x, cs_reg.y, o0, o1);
             k16[i0] = __float2half_rn(o0); k16[i1] = __float2half_rn(o1);
         }
     } else {
         for (int e = tid; e < hd; e += ATTN_THREADS) { q32[e] = round_f16(qh[e]); k16[e] = __float2half_rn(kh[e]); }
     }
     __syncthreads();
-    __half * kc = p.k_cache + (size_t)sq * p.n_ctx * dkv + (size_t)hk * hd;
-    __half * vc = p.v_cache + (size_t)sq * p.n_ctx * dkv + (size_t)hk * hd;
     if (h % group == 0) {
         for (int e = tid; e < hd; e += ATTN_THREADS) {
             kc[(size_t)pos * dkv + e] = k16[e];
@@ -361,9 +389,14 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     __syncthreads();
 
     // ---- out[e] = sum_j p_j V[j, e]: thread = (chunk of 8 columns, slice of positions); slices reduced through smem
-    const int slices = ATTN_THREADS / chunks;
-    const int c8 = tid % chunks, sl = tid / chunks;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    auto fma8 = [&](float pj, const uint4 vv) {
+        const float2 v0 = h2f(vv.x), v1 = h2f(vv.y), v2 = h2f(vv.z), v3 = h2f(vv.w);
+        acc[0] = fmaf(pj, v0.x, acc[0]); acc[1] = fmaf(pj, v0.y, acc[1]);
+        acc[2] = fmaf(pj, v1.x, acc[2]); acc[3] = fmaf(pj, v1.y, acc[3]);
+        acc[4] = fmaf(pj, v2.x, acc[4]); acc[5] = fmaf(pj, v2.y, acc[5]);
+        acc[6] = fmaf(pj, v3.x, acc[6]); acc[7] = fmaf(pj, v3.y, acc[7]);
+    };
     if (sl < slices) {
         for (int j0 = sl; j0 <= pos; j0 += slices * 4) {
             uint4 vv[4]; float pj[4];
@@ -378,13 +411,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const float2 v0 = h2f(vv[u].x), v1 = h2f(vv[u].y), v2 = h2f(vv[u].z), v3 = h2f(vv[u].w);
-                acc[0] = fmaf(pj[u], v0.x, acc[0]); acc[1] = fmaf(pj[u], v0.y, acc[1]);
-                acc[2] = fmaf(pj[u], v1.x, acc[2]); acc[3] = fmaf(pj[u], v1.y, acc[3]);
-                acc[4] = fmaf(pj[u], v2.x, acc[4]); acc[5] = fmaf(pj[u], v2.y, acc[5]);
-                acc[6] = fmaf(pj[u], v3.x, acc[6]); acc[7] = fmaf(pj[u], v3.y, acc[7]);
-            }
+            for (int u = 0; u < 4; u++) fma8(pj[u], vv[u]);
         }
     }
     float * red = sc;                                              // exp values are dead: reuse as [slices][hd]
@@ -394,10 +421,16 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     }
     __syncthreads();
     for (int e = tid; e < hd; e += ATTN_THREADS) {
-        float o = 0.f;
-        for (int s = 0; s < slices; s++) o += red[s * hd + e];
-        if (p.out) p.out[((size_t)t * p.n_head + h) * hd + e] = o;
-        red[e] = o;                                                // slice 0 row now holds the final value (own column only)
+        float o[4] = {0.f, 0.f, 0.f, 0.f};
+        int s2 = 0;
+        for (; s2 + 4 <= slices; s2 += 4) {                         // 4 independent chains, joined in a fixed order
+#pragma unroll
+            for (int u = 0; u < 4; u++) o[u] += red[(s2 + u) * hd + e];
+        }
+        for (; s2 < slices; s2++) o[0] += red[s2 * hd + e];
+        const float ov = (o[0] + o[1]) + (o[2] + o[3]);
+        if (p.out) p.out[((size_t)t * p.n_head + h) * hd + e] = ov;
+        red[e] = ov;                                               // slice 0 row now holds the final value (own column only)
     }
     if (p.out_act_type) {
         __syncthreads();

@@ -114,6 +114,13 @@ struct pi_engine {
     bool fuse;                               // batch 1: consumers build their own normalised input (no norm launches)
     bool ffn_fused;                          // batch 1: one kernel for up/gate + activation + down (PI_FFN_FUSED=1; off by default: parity-green but measured slower than the two-kernel path)
     int32_t * parts, * chunk_off;            // balanced chunk split made by the compaction for that kernel
+    // Weight streamer (PI_PREFETCH=1; off by default): a second stream (a parallel branch of the step's graph) whose
+    // kernels only pull the weights of the mat-vecs that come next into L2 while the main chain runs kernels that leave
+    // HBM idle (norms, attention, compaction).  Measured slower than no streamer: the latency-bound kernels it overlaps
+    // with slow down behind its traffic by more than the mat-vecs gain.
+    unsigned prefetch;
+    cudaStream_t pf_stream;
+    std::vector<cudaEvent_t> pf_events; size_t pf_used; bool pf_forked;
     unsigned skip_mask;                      // PI_SKIP_STAGES: stages left out of the step (timing experiments only; results are garbage)
 };
 
@@ -226,6 +233,9 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
     { const char * v = getenv("PI_PDL"); e->pdl = !(v && v[0] == '0'); }
     { const char * v = getenv("PI_FUSE"); e->fuse = (v && v[0] == '1'); }
     { const char * v = getenv("PI_FFN_FUSED"); e->ffn_fused = (v && v[0] == '1'); }
+    { const char * v = getenv("PI_PREFETCH"); e->prefetch = v ? (unsigned)strtoul(v, nullptr, 0) : 0u; }
+    e->pf_stream = nullptr; e->pf_used = 0; e->pf_forked = false;
+    if (e->prefetch && cudaStreamCreateWithFlags(&e->pf_stream, cudaStreamNonBlocking) != cudaSuccess) { delete e; return cuda_fail(cudaGetLastError(), "engine_create: stream"); }
     { const char * v = getenv("PI_SKIP_STAGES"); e->skip_mask = v ? (unsigned)strtoul(v, nullptr, 0) : 0u; }
     cudaStream_t st = (cudaStream_t)stream;
     // one-time device state: sequence ids 0..T-1, zeroed ticket / status, RoPE angle table
@@ -248,6 +258,8 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
 void pi_engine_destroy(pi_engine * e) {
     if (!e) return;
     for (auto & g : e->graphs) if (g) cudaGraphExecDestroy(g);
+    for (auto ev : e->pf_events) cudaEventDestroy(ev);
+    if (e->pf_stream) cudaStreamDestroy(e->pf_stream);
     delete e;
 }
 
@@ -345,6 +357,39 @@ void norm_inputs(pi_engine * e, int T, const Pending & pd, NormArgs & n) {
 
 int enqueue_step_fused(pi_engine * e, cudaStream_t st, StageTimer & tm);
 
+static cudaEvent_t pf_event(pi_engine * e) {
+    if (e->pf_used == e->pf_events.size()) {
+        cudaEvent_t ev = nullptr;
+        if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        e->pf_events.push_back(ev);
+    }
+    return e->pf_events[e->pf_used++];
+}
+
+// The streamer branch starts pulling `pf` once everything enqueued on `st` so far has finished.
+static int fork_prefetch(pi_engine * e, cudaStream_t st, const Prefetch & pf) {
+    if (!e->prefetch || !pf.ptr[0]) return PI_OK;
+    cudaEvent_t ev = pf_event(e);
+    PI_REQUIRE(ev, "engine: cannot create an event");
+    PI_CUDA(cudaEventRecord(ev, st));
+    PI_CUDA(cudaStreamWaitEvent(e->pf_stream, ev, 0));
+    const int rc = launch_prefetch(pf, e->pf_stream);
+    if (rc) return rc;
+    e->pf_forked = true; e->launches++;
+    return PI_OK;
+}
+
+// The step is complete only when the streamer branch is (also what lets a stream capture end).
+static int join_prefetch(pi_engine * e, cudaStream_t st) {
+    if (!e->pf_forked) return PI_OK;
+    cudaEvent_t ev = pf_event(e);
+    PI_REQUIRE(ev, "engine: cannot create an event");
+    PI_CUDA(cudaEventRecord(ev, e->pf_stream));
+    PI_CUDA(cudaStreamWaitEvent(st, ev, 0));
+    e->pf_forked = false;
+    return PI_OK;
+}
+
 int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
     if (T == 1 && e->fuse && e->c.n_ranks == 1) return enqueue_step_fused(e, st, tm);
     const pi_engine_config & c = e->c;
@@ -356,6 +401,8 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
     const int qkv_rows = e->dq + 2 * e->dkv;
     const bool pdl = e->pdl && !tm.on;       // profiling wants each kernel alone between its events
     e->launches = 0;
+    e->pf_used = 0; e->pf_forked = false;
+    int rc_pf = PI_OK;
 
     {
         const dim3 grid((unsigned)((d + 255) / 256), T);
@@ -423,6 +470,12 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             g.bias = L->bqkv; g.dst = e->qkv; g.dst_stride = qkv_rows;
             STAGE(PI_STAGE_QKV, (T + 7) / 8, launch_gemv(g, st));
         }
+        if (e->prefetch & 1u) {                                           // HBM is idle during attention: out-projection and fc1 weights
+            Prefetch pf;
+            pf.ptr[0] = L->wo; pf.bytes[0] = (size_t)d * pi_row_bytes(wt, e->dq);
+            pf.ptr[1] = L->fc1; pf.bytes[1] = (size_t)c.rank * d * 2;
+            if ((rc_pf = fork_prefetch(e, st, pf))) return rc_pf;
+        }
         {
             AttnArgs a;
             a.pdl = pdl;
@@ -443,6 +496,11 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             g.bias = c.rank_id == 0 ? L->bo : nullptr;                    // the bias enters the sum over ranks once
             g.dst = e->attn_out; g.dst_stride = d;
             STAGE(PI_STAGE_WO, (T + 7) / 8, launch_gemv(g, st));
+        }
+        if (e->prefetch & 2u || e->prefetch == 1u) {                      // ... the FFN norm and fc1: fc2
+            Prefetch pf;
+            pf.ptr[0] = L->fc2; pf.bytes[0] = (size_t)F * c.rank * 2;
+            if ((rc_pf = fork_prefetch(e, st, pf))) return rc_pf;
         }
 
         // ---- FFN input.  llama / opt: ffn_inp = attn_out + x, then the FFN norm; the complete attention output is needed,
@@ -477,6 +535,11 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             g2.status = e->status; g2.pdl = pdl;
             g2.W = L->fc2; g2.nrows = F; g2.ncols = c.rank; g2.x = hx; g2.T = T; g2.dst = pred; g2.dst_stride = F;
             STAGE(PI_STAGE_PRED, (T + 7) / 8, launch_gemv(g2, st));
+        }
+        if ((e->prefetch & 4u || e->prefetch == 1u) && il + 1 < c.n_layer) {   // ... the sparse FFN (far from saturating HBM): next layer's QKV
+            Prefetch pf;
+            pf.ptr[0] = e->layers[il + 1].wqkv; pf.bytes[0] = (size_t)qkv_rows * pi_row_bytes(wt, d);
+            if ((rc_pf = fork_prefetch(e, st, pf))) return rc_pf;
         }
         // ---- mask -> active list (and, for batch 1, a balanced split of the 32-neuron chunks over the SMs).
         //      Where a row is inactive for a token the dense hidden vector holds 0 (or relu(bias)): the Q4_0 axpy quantises
@@ -541,7 +604,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             pend.res = falcon ? e->attn_out : nullptr;
         }
     }
-    return PI_OK;
+    return join_prefetch(e, st);
 }
 
 // Batch-1, single-GPU step with the norm launches gone.  The two kernels that finish a residual-stream vector (the

@@ -19,6 +19,7 @@ static constexpr int QK = 32;
 static constexpr int RING_THREADS = 256;
 static constexpr int RING_WARPS = 8;
 static constexpr int RING_MAX_ITEMS = 1024;            // list entries one CTA may own
+static constexpr int RING_MAX_VEC = 128;               // row vectors in one stage (rows x matrices)
 
 __device__ __forceinline__ uint32_t r_smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void r_mbar_init(uint64_t * bar, unsigned count) {
@@ -106,6 +107,50 @@ __device__ __forceinline__ float ring_row_dot(const unsigned char * row, int u_l
         }
     }
     return acc0 + acc1;
+}
+
+// RW staged vectors (consecutive, row_bytes apart) against the staged activation over units [u_lo, u_hi): the
+// activation unit is read from shared memory and converted once and used for all RW rows, and the RW sums are
+// independent dependency chains.
+template <int WT, int RW>
+__device__ __forceinline__ void ring_dot_rows(const unsigned char * base, size_t row_bytes, int u_lo, int u_hi, int nb,
+                                              const unsigned char * xs, int lane, float (&acc)[RW]) {
+#pragma unroll
+    for (int r = 0; r < RW; r++) acc[r] = 0.f;
+    if (WT == PI_TYPE_F16) {
+        const uint4 * x = reinterpret_cast<const uint4 *>(xs);
+#pragma unroll 2
+        for (int u = u_lo + lane; u < u_hi; u += 32) {
+            const uint4 xv = x[u];
+            const float2 x0 = h2f(xv.x), x1 = h2f(xv.y), x2 = h2f(xv.z), x3 = h2f(xv.w);
+#pragma unroll
+            for (int r = 0; r < RW; r++) {
+                const uint4 wv = reinterpret_cast<const uint4 *>(base + (size_t)r * row_bytes)[u];
+                const float2 w0 = h2f(wv.x), w1 = h2f(wv.y), w2 = h2f(wv.z), w3 = h2f(wv.w);
+                float a = acc[r];
+                a = fmaf(w0.x, x0.x, a); a = fmaf(w0.y, x0.y, a); a = fmaf(w1.x, x1.x, a); a = fmaf(w1.y, x1.y, a);
+                a = fmaf(w2.x, x2.x, a); a = fmaf(w2.y, x2.y, a); a = fmaf(w3.x, x3.x, a); a = fmaf(w3.y, x3.y, a);
+                acc[r] = a;
+            }
+        }
+    } else {
+        const uint4 * lo = reinterpret_cast<const uint4 *>(xs);
+        const uint4 * hi = lo + nb;
+        const uint2 * ds = reinterpret_cast<const uint2 *>(hi + nb);        // {scale as float bits, int8 sum} per block
+#pragma unroll 2
+        for (int b = u_lo + lane; b < u_hi; b += 32) {
+            const uint4 l = lo[b], h = hi[b];
+            const uint2 m = ds[b];
+            const float d8 = __uint_as_float(m.x);
+#pragma unroll
+            for (int r = 0; r < RW; r++) {
+                const unsigned char * row = base + (size_t)r * row_bytes;
+                const uint4 q = reinterpret_cast<const uint4 *>(row)[b];
+                const float d4 = __half2float(reinterpret_cast<const __half *>(row + (size_t)nb * 16)[b]);
+                acc[r] = fmaf((float)r_block_dot(q, l, h, (int)m.y), d4 * d8, acc[r]);
+            }
+        }
+    }
 }
 
 // ---- fused input (see FusedIn): every CTA builds the activation it consumes
@@ -287,10 +332,10 @@ __device__ __forceinline__ void ring_build_input(const FusedIn & f, int n, unsig
     }
 }
 
-template <int WT, bool SPARSE, bool GATED, bool FUSED>
+template <int WT, bool SPARSE, bool GATED, bool FUSED, int RW>
 __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ float s_part[2][RING_WARPS][2];
+    __shared__ float s_part[2][RING_MAX_VEC][RING_WARPS];          // [stage parity][vector of the stage][column part]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = gridDim.x, cta = blockIdx.x;
     const int S = p.stages, R = p.R, split = p.split;
@@ -371,10 +416,14 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
     }
     __syncthreads();
 
+    // A stage holds NV = R * NM vectors (the R gate rows after the R up rows).  RW consecutive vectors form a group that
+    // one warp reads together; `split` warps share a group, each taking 1/split of the columns.  Partial sums go through
+    // shared memory and are added in part order by the thread that owns the row.
     const int units = WT == PI_TYPE_F16 ? p.ncols / 8 : p.nb;       // 16-byte units per row
     const int per = units / split;
-    bool dead = false;
-    double st_sum = 0.0, st_sq = 0.0;                               // statistics of what lane 0 of this warp wrote
+    const int NV = R * NM, groups = NV / RW;
+    bool dead = false;                                              // warp-uniform
+    double st_sum = 0.0, st_sq = 0.0;                               // statistics of what this thread wrote
     for (int st = 0; st < n_stages; st++) {
         const int s = st % S;
         const unsigned parity = (unsigned)(st / S) & 1u;
@@ -382,63 +431,47 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
             int spins = 0;
             bool gave_up = false;
             while (!r_mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
-            dead = __syncthreads_or(gave_up) != 0;                   // the whole CTA agrees, so no warp shuffles half-populated
-            if (dead && tid == 0) atomicOr(p.status, 4u);
+            dead = __any_sync(0xffffffffu, gave_up) != 0;            // the whole warp agrees, so no shuffle runs half-populated
+            if (dead && lane == 0) atomicOr(p.status, 4u);
         }
         const unsigned char * base = ring + (size_t)s * p.stage_bytes;
         const int first = stage_first(st);
         const int n = min(R, n_items - first);
-        if (split == 1) {
-            for (int k = warp; k < n && !dead; k += RING_WARPS) {
-                float v = warp_sum(ring_row_dot<WT>(base + (size_t)k * p.row_bytes, 0, units, p.nb, xs, lane));
-                float v2 = 0.f;
-                if (GATED) v2 = warp_sum(ring_row_dot<WT>(base + (size_t)(R + k) * p.row_bytes, 0, units, p.nb, xs, lane));
-                if (lane == 0) {
-                    const int r = SPARSE ? items[st * R + k] : first + k;
-                    const int64_t g = SPARSE && p.bucket ? p.bucket[r] : r;
-                    bool active = true;
-                    if (SPARSE) active = p.idx[g] >= p.threshold;
-                    float o = active ? v : 0.f;
-                    if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
-                    if (p.bias) o += p.bias[g];
-                    if (p.relu) o = fmaxf(o, 0.f);
-                    if (p.res_add) o += p.res_add[g];
-                    if (p.dst)   p.dst[g] = o;
-                    if (p.dst16) p.dst16[g] = __float2half_rn(o);
-                    st_sum += (double)o; st_sq += (double)(o * o);
-                }
-            }
-            __syncthreads();
-        } else {
-            // R * split == 8: warp = (row k, column part); parts are added in part order after the barrier
-            const int k = warp / split, part = warp % split;
-            float v = 0.f, v2 = 0.f;
-            if (k < n && !dead) {
-                v = warp_sum(ring_row_dot<WT>(base + (size_t)k * p.row_bytes, part * per, (part + 1) * per, p.nb, xs, lane));
-                if (GATED) v2 = warp_sum(ring_row_dot<WT>(base + (size_t)(R + k) * p.row_bytes, part * per, (part + 1) * per, p.nb, xs, lane));
-            }
-            if (lane == 0) { s_part[st & 1][warp][0] = v; s_part[st & 1][warp][1] = v2; }
-            __syncthreads();
-            if (part == 0 && lane == 0 && k < n && !dead) {
-                for (int q = 1; q < split; q++) { v += s_part[st & 1][warp + q][0]; v2 += s_part[st & 1][warp + q][1]; }
-                const int r = SPARSE ? items[st * R + k] : first + k;
-                const int64_t g = SPARSE && p.bucket ? p.bucket[r] : r;
-                bool active = true;
-                if (SPARSE) active = p.idx[g] >= p.threshold;
-                float o = active ? v : 0.f;
-                if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
-                if (p.bias) o += p.bias[g];
-                if (p.relu) o = fmaxf(o, 0.f);
-                if (p.res_add) o += p.res_add[g];
-                if (p.dst)   p.dst[g] = o;
-                if (p.dst16) p.dst16[g] = __float2half_rn(o);
-                st_sum += (double)o; st_sq += (double)(o * o);
+        float (*part_sums)[RING_WARPS] = s_part[st & 1];
+        for (int g = warp / split; g < groups; g += RING_WARPS / split) {
+            const int part = warp % split;
+            float acc[RW];
+            if (!dead) ring_dot_rows<WT, RW>(base + (size_t)g * RW * p.row_bytes, (size_t)p.row_bytes, part * per, (part + 1) * per, p.nb, xs, lane, acc);
+#pragma unroll
+            for (int r = 0; r < RW; r++) {
+                const float v = dead ? 0.f : warp_sum(acc[r]);
+                if (lane == 0) part_sums[g * RW + r][part] = v;
             }
         }
-        if (tid == 0 && !dead && st + S < n_stages) issue(st + S);   // the barrier above freed stage s
+        __syncthreads();                                             // sums visible; every warp is done with stage s
+        if (tid == 0 && !dead && st + S < n_stages) issue(st + S);
+        if (tid < n) {
+            const int k = tid;
+            float v = part_sums[k][0], v2 = 0.f;
+            for (int q = 1; q < split; q++) v += part_sums[k][q];
+            if (GATED) { v2 = part_sums[R + k][0]; for (int q = 1; q < split; q++) v2 += part_sums[R + k][q]; }
+            const int r = SPARSE ? items[st * R + k] : first + k;
+            const int64_t g = SPARSE && p.bucket ? p.bucket[r] : r;
+            bool active = true;
+            if (SPARSE) active = p.idx[g] >= p.threshold;
+            float o = active ? v : 0.f;
+            if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
+            if (p.bias) o += p.bias[g];
+            if (p.relu) o = fmaxf(o, 0.f);
+            if (p.res_add) o += p.res_add[g];
+            if (p.dst)   p.dst[g] = o;
+            if (p.dst16) p.dst16[g] = __float2half_rn(o);
+            st_sum += (double)o; st_sq += (double)(o * o);
+        }
     }
     if (p.stats_out) {                                              // one pair of atomics per CTA
         __shared__ double s_stat[RING_WARPS][2];
+        st_sum = warp_sum_d(st_sum); st_sq = warp_sum_d(st_sq);
         if (lane == 0) { s_stat[warp][0] = st_sum; s_stat[warp][1] = st_sq; }
         __syncthreads();
         if (tid == 0) {
@@ -448,12 +481,12 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
             atomicAdd(p.stats_out, a); atomicAdd(p.stats_out + 1, b);
         }
     }
-    if (dead && tid == 0) {                                         // do not exit with copies still landing in shared memory
+    if (__syncthreads_or(dead) && tid == 0) {                       // do not exit with copies still landing in shared memory
         for (int s = 0; s < S; s++) { int spins = 0; while (!r_mbar_try_wait(full + s, 0) && !r_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
     }
 }
 
-struct RingPlan { bool ok; int R, split, stages, ctas_per_sm; size_t stage_bytes, smem; int max_items; };
+struct RingPlan { bool ok; int R, split, rw, stages, ctas_per_sm; size_t stage_bytes, smem; int max_items; };
 
 // Two 100 KB rings per SM rather than one big one (PI_RING_CPS / PI_RING_KB override): with a single 8-warp CTA the
 // consumers are issue-latency bound, and what matters for bandwidth is ~200 KB of copies in flight per SM; four 54 KB rings
@@ -465,15 +498,24 @@ static RingPlan ring_plan(int wtype, int64_t nrows, int64_t ncols, bool sparse, 
     const int units = wtype == PI_TYPE_F16 ? (int)(ncols / 8) : (int)(ncols / QK);
     const int nm = gated ? 2 : 1;
     const size_t x_bytes = wtype == PI_TYPE_F16 ? (size_t)ncols * 2 : (size_t)(ncols / QK) * 40;
-    static int cps0 = 0, kb0 = 0;
+    static int cps0 = 0, kb0 = 0, rw0 = 2;
+    if (!cps0) { const char * w = getenv("PI_RING_RW"); rw0 = w ? atoi(w) : 2; if (rw0 != 1 && rw0 != 4) rw0 = 2; }
     if (!cps0) { const char * v = getenv("PI_RING_CPS"); cps0 = v ? atoi(v) : 2; const char * k = getenv("PI_RING_KB"); kb0 = k ? atoi(k) : 100; }
     for (int cps = cps0; cps >= 1; cps /= 2) {
         const size_t budget = (size_t)(cps == cps0 ? kb0 : (cps == 2 ? 110 : 200)) * 1024;
         const int G = sm_count() * cps;
         int R = 1;
         while (R < 64 && (size_t)(2 * R) * nm * row_bytes <= (budget <= 64 * 1024 ? 19 : 36) * 1024) R *= 2;
-        const int split = R >= RING_WARPS ? 1 : RING_WARPS / R;
-        if (split > 1 && units % (split * 32) != 0) continue;
+        // RW vectors per warp (register blocking), `split` warps per group of RW; a warp's column share stays >= 32 units
+        const int nv = R * nm;
+        if (nv > RING_MAX_VEC) continue;
+        int rw = nv < rw0 ? nv : rw0, split = 1;
+        for (;; rw /= 2) {
+            const int groups = nv / rw;
+            split = groups >= RING_WARPS ? 1 : RING_WARPS / groups;
+            if ((units % split == 0 && units / split >= 32) || rw == 1) break;
+        }
+        if (units % split != 0) continue;
         const int max_items = sparse ? (int)((((nrows + G - 1) / G + R - 1) / R + 1) * R) : 0;
         if (max_items > RING_MAX_ITEMS) continue;
         const size_t head = (((size_t)8 * 32 + (size_t)4 * max_items + 127) & ~size_t(127)) + ((x_bytes + 127) & ~size_t(127));
@@ -481,7 +523,7 @@ static RingPlan ring_plan(int wtype, int64_t nrows, int64_t ncols, bool sparse, 
         if (head + 2 * stage_bytes > budget) continue;
         int S = (int)((budget - head) / stage_bytes);
         pl.stages = S > 8 ? 8 : S;
-        pl.R = R; pl.split = split; pl.ctas_per_sm = cps; pl.max_items = max_items; pl.stage_bytes = stage_bytes;
+        pl.R = R; pl.split = split; pl.rw = rw; pl.ctas_per_sm = cps; pl.max_items = max_items; pl.stage_bytes = stage_bytes;
         pl.smem = head + (size_t)pl.stages * stage_bytes;
         pl.ok = true;
         return pl;
@@ -489,12 +531,12 @@ static RingPlan ring_plan(int wtype, int64_t nrows, int64_t ncols, bool sparse, 
     return pl;
 }
 
-template <int WT, bool SPARSE, bool GATED, bool FUSED>
+template <int WT, bool SPARSE, bool GATED, bool FUSED, int RW>
 static int launch_ring_inst(const RingP & p, const RingPlan & pl, bool pdl, cudaStream_t st) {
     static bool attr_done[16] = {false};
     int dev = 0;
     PI_CUDA(cudaGetDevice(&dev));
-    auto kern = k_gemv_ring<WT, SPARSE, GATED, FUSED>;
+    auto kern = k_gemv_ring<WT, SPARSE, GATED, FUSED, RW>;
     if (dev >= 0 && dev < 16 && !attr_done[dev]) {
         PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
         attr_done[dev] = true;
@@ -522,17 +564,24 @@ int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaSt
     p.bias = a.bias; p.relu = a.relu; p.dst = a.dst; p.dst16 = a.dst16; p.status = status; p.fin = a.fin; p.res_add = a.res_add; p.stats_out = a.stats_out;
     p.R = pl.R; p.split = pl.split; p.stages = pl.stages; p.max_items = pl.max_items; p.stage_bytes = pl.stage_bytes;
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
+#define PI_RING_DISPATCH_RW(FUSED, RW)                                                                                                     \
+    do {                                                                                                                                   \
+        if (!sparse) return q4 ? launch_ring_inst<PI_TYPE_Q4_0, false, false, FUSED, RW>(p, pl, pdl, st)                                   \
+                               : launch_ring_inst<PI_TYPE_F16, false, false, FUSED, RW>(p, pl, pdl, st);                                   \
+        if (gated)   return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, true, FUSED, RW>(p, pl, pdl, st)                                     \
+                               : launch_ring_inst<PI_TYPE_F16, true, true, FUSED, RW>(p, pl, pdl, st);                                     \
+        return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, false, FUSED, RW>(p, pl, pdl, st)                                                 \
+                  : launch_ring_inst<PI_TYPE_F16, true, false, FUSED, RW>(p, pl, pdl, st);                                                 \
+    } while (0)
 #define PI_RING_DISPATCH(FUSED)                                                                                                            \
     do {                                                                                                                                   \
-        if (!sparse) return q4 ? launch_ring_inst<PI_TYPE_Q4_0, false, false, FUSED>(p, pl, pdl, st)                                       \
-                               : launch_ring_inst<PI_TYPE_F16, false, false, FUSED>(p, pl, pdl, st);                                       \
-        if (gated)   return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, true, FUSED>(p, pl, pdl, st)                                         \
-                               : launch_ring_inst<PI_TYPE_F16, true, true, FUSED>(p, pl, pdl, st);                                         \
-        return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, false, FUSED>(p, pl, pdl, st)                                                     \
-                  : launch_ring_inst<PI_TYPE_F16, true, false, FUSED>(p, pl, pdl, st);                                                     \
+        if (pl.rw == 4) PI_RING_DISPATCH_RW(FUSED, 4);                                                                                     \
+        if (pl.rw == 2) PI_RING_DISPATCH_RW(FUSED, 2);                                                                                     \
+        PI_RING_DISPATCH_RW(FUSED, 1);                                                                                                     \
     } while (0)
     if (a.fin.on) PI_RING_DISPATCH(true);
     PI_RING_DISPATCH(false);
+#undef PI_RING_DISPATCH_RW
 #undef PI_RING_DISPATCH
 }
 

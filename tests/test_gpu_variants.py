@@ -45,7 +45,7 @@ def test_step_variants_agree(tmp_path):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     base = run_variant(tmp_path, "base", {})
-    for tag, env in (("ffn_fused", {"PI_FFN_FUSED": "1"}), ("fused_norms", {"PI_FUSE": "1"}), ("no_pdl", {"PI_PDL": "0"})):
+    for tag, env in (("ffn_fused", {"PI_FFN_FUSED": "1"}), ("fused_norms", {"PI_FUSE": "1"}), ("no_pdl", {"PI_PDL": "0"}), ("streamer", {"PI_PREFETCH": "1"}), ("rw4", {"PI_RING_RW": "4"})):
         got = run_variant(tmp_path, tag, env)
         for name in base.files:
             err = float(np.abs(got[name] - base[name]).max())
