@@ -75,6 +75,16 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
     const int t = blockIdx.x;
     const int64_t n = p.n;
     pdl_launch();
+    // the norm weights are read once per step, so they are cold: ask for them before the wait (hints cost no registers)
+#pragma unroll
+    for (int k = 0; k < NORM_CHUNKS; k++) {
+        const int64_t c = ((int64_t)k * blockDim.x + threadIdx.x) * 8;
+        if (c < n && (threadIdx.x & 3) == 0) {
+            if (p.w) asm volatile("prefetch.global.L2 [%0];" :: "l"(p.w + c));
+            if (p.b) asm volatile("prefetch.global.L2 [%0];" :: "l"(p.b + c));
+            if (p.in_bias) asm volatile("prefetch.global.L2 [%0];" :: "l"(p.in_bias + c));
+        }
+    }
     pdl_wait();
     const size_t tn = p.partial_stride ? (size_t)p.partial_stride : (size_t)p.T * n;
     const float * partial = p.partial;
@@ -121,18 +131,14 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
             v[k][0] = a.x; v[k][1] = a.y; v[k][2] = a.z; v[k][3] = a.w;
             v[k][4] = b.x; v[k][5] = b.y; v[k][6] = b.z; v[k][7] = b.w;
         }
-        if (p.in_bias) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) v[k][j] += p.in_bias[c + j];
-        }
-        if (p.residual) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) v[k][j] += p.residual[o + j];
-        }
-        if (p.residual2) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) v[k][j] += p.residual2[o + j];
-        }
+        auto add8 = [&](const float * src) {
+            const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
+            v[k][0] += a.x; v[k][1] += a.y; v[k][2] += a.z; v[k][3] += a.w;
+            v[k][4] += b.x; v[k][5] += b.y; v[k][6] += b.z; v[k][7] += b.w;
+        };
+        if (p.in_bias) add8(p.in_bias + c);
+        if (p.residual) add8(p.residual + o);
+        if (p.residual2) add8(p.residual2 + o);
         if (p.x_out) {
             *reinterpret_cast<float4 *>(p.x_out + o)     = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
             *reinterpret_cast<float4 *>(p.x_out + o + 4) = make_float4(v[k][4], v[k][5], v[k][6], v[k][7]);
@@ -173,12 +179,22 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
 #pragma unroll
     for (int k = 0; k < NORM_CHUNKS; k++) {
         const int64_t c = ((int64_t)k * blockDim.x + threadIdx.x) * 8;
-        float y[8];
+        float y[8], wv[8], bv[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) { wv[j] = 1.f; bv[j] = 0.f; }
+        if (ok[k] && p.w) {
+            const float4 a = *reinterpret_cast<const float4 *>(p.w + c), b = *reinterpret_cast<const float4 *>(p.w + c + 4);
+            wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+        }
+        if (ok[k] && p.b) {
+            const float4 a = *reinterpret_cast<const float4 *>(p.b + c), b = *reinterpret_cast<const float4 *>(p.b + c + 4);
+            bv[0] = a.x; bv[1] = a.y; bv[2] = a.z; bv[3] = a.w; bv[4] = b.x; bv[5] = b.y; bv[6] = b.z; bv[7] = b.w;
+        }
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             float r = __fmul_rn(v[k][j], scale);                       // separate roundings, as separate graph nodes give
-            if (ok[k] && p.w) r = __fmul_rn(r, p.w[c + j]);
-            if (ok[k] && p.b) r = __fadd_rn(r, p.b[c + j]);
+            if (ok[k] && p.w) r = __fmul_rn(r, wv[j]);
+            if (ok[k] && p.b) r = __fadd_rn(r, bv[j]);
             y[j] = r;
         }
         if (ok[k] && p.y) {

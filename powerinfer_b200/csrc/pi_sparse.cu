@@ -585,10 +585,10 @@ int launch_axpy(const AxpyArgs & a, cudaStream_t st, int * groups_used) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// dst[t, c] = sum_j partial[j, t, c] (j ascending within each of 16 interleaved classes, classes added in order)
-//             + bias[c] + residual[t, c].  A CTA owns 128 consecutive values; warp w adds groups w, w+16, w+32, ...;
-// the 16 warp sums are then added in warp order.  The order is fixed, so the result is reproducible.
-static constexpr int RED_WARPS = 16;
+// dst[t, c] = sum_j partial[j, t, c] (j ascending within each of 32 interleaved classes, classes added in order)
+//             + bias[c] + residual[t, c].  A CTA owns 128 consecutive values; warp w adds groups w, w+32, w+64, ...;
+// the 32 warp sums are then added in warp order.  The order is fixed, so the result is reproducible.
+static constexpr int RED_WARPS = 32;
 
 __global__ void __launch_bounds__(RED_WARPS * 32) k_reduce_partials(const float * __restrict__ partial, int G, int64_t total, int64_t n,
                                                                      const float * __restrict__ residual, const float * __restrict__ bias,

@@ -111,23 +111,42 @@ def test_free_running_greedy_and_active_sets(engine_mod, name):
 
 @pytest.mark.parametrize("name,T", [("llama_f16", 4), ("llama_q4_0", 3), ("opt_f16", 8)])
 def test_batched_sequences_match_single(engine_mod, name, T):
-    """T sequences, one token each per step (batched-bench style): every sequence must see exactly what it
-    would see alone; the FFN uses the union list with a per-token predicate."""
+    """T sequences, one token each per step (batched-bench style): every sequence must see what it would see alone;
+    the FFN uses the union list with a per-token predicate.  The batched kernels add in a different order than the
+    batch-1 ones, so a neuron within rounding of the threshold may flip: flips must be borderline, and the logits
+    are compared for the sequences whose active sets (and history) agree."""
     spec = mg.MODEL_CASES[name]
     t = synth.build_model(spec)
     rng = np.random.default_rng(5)
     seqs = rng.integers(3, spec.n_vocab, (T, 6))
     single = engine_mod.DecodeEngine(spec, t, max_batch=1)
+    single.enable_trace()
     ref = np.zeros((T, 6, spec.n_vocab), np.float32)
+    ref_pred = [[None] * 6 for _ in range(T)]
     for b in range(T):
         single.k_cache.zero_(); single.v_cache.zero_(); torch.cuda.synchronize()
         for p in range(6):
             ref[b, p] = single.decode([int(seqs[b, p])], [p])[0][0]
+            ref_pred[b][p] = single.predictor_trace(1)[:, 0].copy()
     single.close()
     eng = engine_mod.DecodeEngine(spec, t, max_batch=T)
+    eng.enable_trace()
+    clean = np.ones(T, bool)                                    # no flip so far in this sequence (a flip also changes its KV history)
+    compared = 0
     for p in range(6):
         logits, _ = eng.decode([int(v) for v in seqs[:, p]], [p] * T)
-        assert np.abs(logits - ref[:, p]).max() <= 1e-3
+        tr = eng.predictor_trace(T)
+        for b in range(T):
+            if not clean[b]:
+                continue
+            n_flip, all_borderline = borderline_flips(tr[:, b], ref_pred[b][p], spec.threshold)
+            assert all_borderline
+            if n_flip:
+                clean[b] = False
+                continue
+            assert np.abs(logits[b] - ref[b, p]).max() <= 1e-3
+            compared += 1
+    assert compared >= T * 6 // 2
     eng.close()
 
 
