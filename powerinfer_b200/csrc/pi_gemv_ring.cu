@@ -359,17 +359,20 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
     // stage st of this CTA covers items [ (cta + st*G) * R, +R ) of the row / list sequence
     int n_items, n_stages;
     auto stage_first = [&](int st) { return (cta + st * G) * R; };
-    auto issue = [&](int st) {                                       // thread 0 only
+    auto issue = [&](int st) {                                       // all lanes of warp 0
         const int s = st % S;
         const int first = stage_first(st);
         const int n = min(R, n_items - first);
         unsigned char * dstp = ring + (size_t)s * p.stage_bytes;
         if (!SPARSE) {
-            r_mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
-            r_bulk_g2s(dstp, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
+            if (lane == 0) {
+                r_mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
+                r_bulk_g2s(dstp, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
+            }
         } else {
-            r_mbar_expect_tx(full + s, (unsigned)(n * NM * p.row_bytes));
-            for (int k = 0; k < n; k++) {
+            // the phase cannot complete before the arrive below, whatever the order in which the lanes' copies land
+            if (lane == 0) r_mbar_expect_tx(full + s, (unsigned)(n * NM * p.row_bytes));
+            for (int k = lane; k < n; k += 32) {
                 const int r = items[st * R + k];
                 r_bulk_g2s(dstp + (size_t)k * p.row_bytes, p.W + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
                 if (GATED) r_bulk_g2s(dstp + (size_t)(R + k) * p.row_bytes, p.W2 + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
@@ -382,7 +385,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
         n_items = p.nrows;
         const int total_stages = (n_items + R - 1) / R;
         n_stages = cta < total_stages ? (total_stages - cta + G - 1) / G : 0;
-        if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
+        if (warp == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
     }
     pdl_wait();
     if (SPARSE) {
@@ -396,7 +399,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
             items[i] = (unsigned)r < (unsigned)p.nrows ? r : 0;
         }
         __syncthreads();
-        if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
+        if (warp == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
     }
     // ---- stage the activation
     if (FUSED) {
@@ -449,18 +452,17 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
             }
         }
         __syncthreads();                                             // sums visible; every warp is done with stage s
-        if (tid == 0 && !dead && st + S < n_stages) issue(st + S);
-        if (tid < n) {
-            const int k = tid;
+        if (warp == 0 && !dead && st + S < n_stages) issue(st + S);
+        if (tid >= 32 && tid - 32 < n) {                             // warps 1..: warp 0 is busy refilling the stage
+            const int k = tid - 32;
             float v = part_sums[k][0], v2 = 0.f;
             for (int q = 1; q < split; q++) v += part_sums[k][q];
             if (GATED) { v2 = part_sums[R + k][0]; for (int q = 1; q < split; q++) v2 += part_sums[R + k][q]; }
             const int r = SPARSE ? items[st * R + k] : first + k;
             const int64_t g = SPARSE && p.bucket ? p.bucket[r] : r;
-            bool active = true;
-            if (SPARSE) active = p.idx[g] >= p.threshold;
-            float o = active ? v : 0.f;
-            if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
+            // batch 1: a listed row is an active row (the list was made from the same logits and threshold)
+            float o = v;
+            if (GATED) o = fmaxf(v2, 0.f) * v;
             if (p.bias) o += p.bias[g];
             if (p.relu) o = fmaxf(o, 0.f);
             if (p.res_add) o += p.res_add[g];

@@ -361,16 +361,17 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
         rows[i] = (unsigned)r < (unsigned)p.nrows ? r : -1;
     }
     __syncthreads();
-    auto issue = [&](int st) {                                       // thread 0 only
+    auto issue = [&](int st) {                                       // all lanes of warp 0
         const int s = st % S;
         const int cnt = min(PIPE_RS, n_mine - st * PIPE_RS);
-        mbar_expect_tx(full + s, (unsigned)(cnt * p.row_bytes));
-        for (int k = 0; k < cnt; k++) {
-            const int r = rows[st * PIPE_RS + k] < 0 ? 0 : rows[st * PIPE_RS + k];
-            bulk_g2s(ring + s * stage_bytes + k * row_stride, p.Wt + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
+        // the phase cannot complete before this arrive, whatever the order in which the lanes' copies land
+        if (lane == 0) mbar_expect_tx(full + s, (unsigned)(cnt * p.row_bytes));
+        if (lane < cnt) {
+            const int r = rows[st * PIPE_RS + lane] < 0 ? 0 : rows[st * PIPE_RS + lane];
+            bulk_g2s(ring + s * stage_bytes + lane * row_stride, p.Wt + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
         }
     };
-    if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
+    if (wid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
     for (int i0 = wid; i0 < n_mine; i0 += nwarp * 4) {             // 4 rows per warp per pass: their loads overlap
         float hv[4], pv[4]; int64_t g[4]; bool ok[4];
 #pragma unroll
@@ -407,7 +408,7 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
     for (int j = 0; j < NACC; j++) acc[j] = 0.f;
     const int n_chunks = p.ncols / 8;
     const int n_words = p.nb * 4;
-    bool dead = false;
+    bool dead = false;                                               // warp-uniform
 
     for (int st = 0; st < n_stages; st++) {
         const int s = st % S;
@@ -418,8 +419,8 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
             while (!mbar_try_wait(full + s, parity)) {
                 if (++spins > (1 << 20)) { gave_up = true; break; }    // each try_wait already blocks for a while
             }
-            dead = __syncthreads_or(gave_up) != 0;
-            if (dead && tid == 0) atomicOr(p.status, 2u);
+            dead = __any_sync(0xffffffffu, gave_up) != 0;
+            if (dead && lane == 0) atomicOr(p.status, 2u);
         }
         const int cnt = min(PIPE_RS, n_mine - st * PIPE_RS);
         if (!dead) {
@@ -454,11 +455,13 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
                 }
             }
         }
-        __syncthreads();                                             // everyone is done with stage s
-        if (tid == 0 && !dead && st + S < n_stages) issue(st + S);
+        if (st + S < n_stages) {                                     // block-uniform: the stage is reused, so everyone must be done with it
+            __syncthreads();
+            if (wid == 0 && !dead) issue(st + S);
+        }
     }
     // a CTA that gave up must not leave copies in flight into its shared memory: drain what was issued
-    if (dead && tid == 0) {
+    if (__syncthreads_or(dead) && tid == 0) {
         for (int s = 0; s < S; s++) { int spins = 0; while (!mbar_try_wait(full + s, 0) && !mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
     }
 
