@@ -42,6 +42,14 @@ def measured_peaks():
         return 6650.0, "fallback"
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each stage's kernels from the committed
+# `ncu --set full` capture of the 4-layer case of the same layer shape (profiles/step_kernels_*_ncu_full.md); traffic per
+# launch does not depend on the layer count.  Stages with two kernels give the mean over their launches.
+NCU_TRAFFIC = {
+    "relu-llama-70b-q4_0": {"predictor": (16.82e6 + 58.81e6) / 2, "qkv": 47.22e6, "out_proj": 37.78e6, "up_gate": 30.50e6,
+                            "down": (15.49e6 + 4.86e6) / 2},
+}
+
 # ------------------------------------------------------------------------------------------------ clocks
 
 class ClockSampler:
@@ -283,14 +291,15 @@ def main():
                 ops[st] = {"ms_per_step": round(t_ms, 4), "GBps": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 3)}
         dom = max(ops, key=lambda k: ops[k]["ms_per_step"])
         launches_in_stage = {"qkv": spec.n_layer, "out_proj": spec.n_layer, "predictor": 2 * spec.n_layer, "up_gate": spec.n_layer,
-                             "down": spec.n_layer * (3 if spec.wtype == 2 else 2), "lm_head": 1}[dom]
+                             "down": spec.n_layer * 2, "lm_head": 1}[dom]
         roofline = {"bound": "hbm", "kernel": {"qkv": "k_gemv (dense, QKV rows)", "out_proj": "k_gemv (dense, out-proj)",
                                                "predictor": "k_gemv (dense F16, fc1+fc2)", "up_gate": "k_gemv (gather, up+gate)",
                                                "down": "k_axpy + reduce", "lm_head": "k_gemv (dense, lm head)"}[dom],
                     "achieved": ops[dom]["GBps"], "peak": peak, "unit": "GB/s", "frac": round(ops[dom]["GBps"] / peak, 3),
                     "peak_source": f"of {peak_kind}", "launches_per_step": launches_in_stage,
                     "bytes_per_launch": bytes_tok[dom] / world / launches_in_stage,
-                    "mean_launch_us": round(ops[dom]["ms_per_step"] * 1e3 / launches_in_stage, 2), "traffic": None}
+                    "mean_launch_us": round(ops[dom]["ms_per_step"] * 1e3 / launches_in_stage, 2),
+                    "traffic": NCU_TRAFFIC.get(cfg_name, {}).get(dom) if world == 1 else None}
         step_bytes = bytes_tok["total"] / world
         line = {"metric": metric, "value": K * T / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
