@@ -146,6 +146,122 @@ def cpu_reference(spec, n_threads: int | None = None) -> dict:
             "ms_per_layer": {k: round(v * 1e3, 4) for k, v in t.items()}, "ms_per_token": per_token * 1e3}
 
 
+# ------------------------------------------------------------------------------------------------ sparse-FFN microbench
+
+def sparse_ffn_microbench(args):
+    """One sparse-FFN layer at the Llama-2-13B shape (d 5120, F 13824), FP16 and Q4_0 rows, mean sparsity 50/80/90/95 %
+    under a Zipf(1.1) per-neuron profile, batch 1/4/8/16 with a union mask: ggml_mul_mat_idx (up), ggml_axpy (down) and the
+    whole FFN (up + gate + glue + down) through the C ABI.  Every timed launch sequence rotates over enough distinct copies
+    of the weights that the active rows of consecutive iterations exceed twice the L2 capacity, and is replayed from a
+    CUDA graph so that the host's call overhead is not what is measured.  Bytes: active rows x row bytes per matrix
+    + T*d*4 + T*F*4 (the algorithmic bytes; inactive rows are never read)."""
+    import numpy as np
+    import torch
+    from powerinfer_b200 import ggml_ops as g, synth
+    torch.cuda.set_device(0)
+    d, F = 5120, 13824
+    peak, peak_kind = measured_peaks()
+    reps = max(3, min(args.steps, 20))
+    rng = np.random.default_rng(0)
+    gen = torch.Generator(device="cuda"); gen.manual_seed(0)
+    base = [(torch.randn(F, d, device="cuda", generator=gen) * 0.02).to(torch.float16) for _ in range(3)]
+    table = []
+    only = args.only.split(":") if args.only else None
+    for wtype, wname in ((synth.F16, "F16"), (synth.Q4_0, "Q4_0")):
+        if only and only[0] != wname:
+            continue
+        rowb = 2 * d if wtype == synth.F16 else d // 32 * 18
+        n_copies = 12 if wtype == synth.F16 else 44          # 95 % sparse: 12 x 21 MB / 44 x 6 MB of active rows > 2 x 126 MB
+        if wtype == synth.F16:
+            one = [g.Weight(wtype, b.view(torch.uint8).reshape(-1), F, d) for b in base]
+        else:
+            one = []
+            for b in base:
+                raw = g.quantize_q4_0(b.float())
+                dev = torch.empty_like(raw)
+                from powerinfer_b200._lib import check, lib
+                check(lib.pi_q4_0_repack(raw.data_ptr(), dev.data_ptr(), F, d, torch.cuda.current_stream().cuda_stream))
+                one.append(g.Weight(wtype, dev, F, d))
+        copies = [[g.Weight(wtype, w.data.clone(), F, d) for w in one] for _ in range(n_copies)]
+        for sparsity in (0.5, 0.8, 0.9, 0.95):
+            prof = synth.zipf_profile(F, 1.0 - sparsity)[rng.permutation(F)]
+            for T in (1, 4, 8, 16):
+                if only and (float(only[1]) != sparsity or int(only[2]) != T):
+                    continue
+                mask = rng.random((T, F)) < prof[None, :]
+                a_union = int(mask.any(0).sum())
+                idx = torch.from_numpy(np.where(mask, 1.0, -1.0).astype(np.float32)).cuda()
+                x = (torch.randn(T, d, device="cuda", generator=gen)).to(torch.float16).float()
+                h = torch.relu(torch.randn(T, F, device="cuda", generator=gen)) * torch.from_numpy(mask).cuda()
+                ops = {
+                    "mul_mat_idx": (lambda c: g.ggml_mul_mat_idx(c[0], x, idx), 1),
+                    "axpy": (lambda c: g.ggml_axpy(c[2], h, idx), 1),
+                    "sparse_ffn": (lambda c: g.sparse_ffn(c[0], c[1], c[2], x, idx), 3),
+                }
+                row = {"weights": wname, "sparsity": sparsity, "T": T, "active_union": a_union}
+                for name, (fn, n_mats) in ops.items():
+                    fn(copies[0]); torch.cuda.synchronize()              # sizes the shared workspace before capture
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        for c in copies:
+                            fn(c)
+                    for _ in range(3):
+                        graph.replay()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record()
+                    for _ in range(reps):
+                        graph.replay()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    us = e0.elapsed_time(e1) * 1e3 / (reps * n_copies)
+                    nbytes = n_mats * a_union * rowb + T * d * 4 + T * F * 4
+                    row[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1), "frac_of_measured_peak": round(nbytes / us / 1e3 / peak, 3)}
+                    del graph
+                table.append(row)
+        del copies
+        torch.cuda.empty_cache()
+    # CPU reference beside it: the reference's own ggml operators, all host threads, batch 1
+    cpu = []
+    if not args.no_cpu_baseline and not only:
+        try:
+            from oracle import pio
+            ref = pio.Ref()
+            nth = os.cpu_count() or 1
+            for wtype, wname in ((synth.F16, "F16"), (synth.Q4_0, "Q4_0")):
+                wf = rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.02)
+                W = ref.quantize_q4_0(wf) if wtype == synth.Q4_0 else wf.astype(np.float16)
+                rowb = 2 * d if wtype == synth.F16 else d // 32 * 18
+                xh = rng.standard_normal((1, d), dtype=np.float32)
+                for sparsity in (0.5, 0.8, 0.9, 0.95):
+                    prof = synth.zipf_profile(F, 1.0 - sparsity)[rng.permutation(F)]
+                    m = rng.random((1, F)) < prof[None, :]
+                    idxh = np.where(m, 1.0, -1.0).astype(np.float32)
+                    hh = np.abs(rng.standard_normal((1, F), dtype=np.float32)) * m
+                    ref.mul_mat_idx(wtype, W, F, d, xh, idxh, None, 0.0, nth, 3); t_up = ref.last_time
+                    ref.axpy(wtype, W, F, d, hh, idxh, None, 0.0, nth, 3); t_dn = ref.last_time
+                    a = int(m.sum())
+                    cpu.append({"weights": wname, "sparsity": sparsity, "T": 1, "threads": nth,
+                                "mul_mat_idx": {"us": round(t_up * 1e6, 1), "GBps": round(a * rowb / t_up / 1e9, 1)},
+                                "axpy": {"us": round(t_dn * 1e6, 1), "GBps": round(a * rowb / t_dn / 1e9, 1)},
+                                "sparse_ffn": {"us": round((2 * t_up + t_dn) * 1e6, 1), "GBps": round(3 * a * rowb / (2 * t_up + t_dn) / 1e9, 1)}})
+        except Exception as ex:
+            cpu = [{"unavailable": str(ex)}]
+    head = next((r for r in table if r["weights"] == "F16" and r["sparsity"] == 0.8 and r["T"] == 1), table[0])
+    head_cpu = next((r for r in cpu if r.get("weights") == "F16" and r.get("sparsity") == 0.8), None)
+    line = {"metric": "sparse_ffn_hbm_GBps", "value": head["sparse_ffn"]["GBps"], "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": 3,
+            "ms_per_step": head["sparse_ffn"]["us"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 / q4_0 rows, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "sparse-ffn-13b: one sparse-FFN layer d 5120 F 13824, headline row = FP16, 80 % sparse, batch 1, whole FFN",
+                       "l2": "weights rotate over 12 (F16) / 44 (Q4_0) distinct copies: active rows of consecutive iterations exceed 2 x L2"},
+            "roofline": {"bound": "hbm", "achieved": head["sparse_ffn"]["GBps"], "peak": peak, "unit": "GB/s",
+                         "frac": head["sparse_ffn"]["frac_of_measured_peak"], "peak_source": f"of {peak_kind}", "traffic": None},
+            "cpu_baseline": ({"value": head_cpu["sparse_ffn"]["GBps"], "unit": "GB/s", "cores": head_cpu["threads"], "kind": "reference",
+                              "sample": "reference ggml mul_mat_idx x2 + axpy on the same shape and sparsity, batch 1, best of 3"} if head_cpu else None),
+            "table": table, "cpu_table": cpu}
+    print(json.dumps(line))
+
+
 # ------------------------------------------------------------------------------------------------ main
 
 def main():
@@ -158,10 +274,15 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling captures of a small case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default=None, help="sparse-ffn-13b: one case as WEIGHTS:SPARSITY:T, e.g. F16:0.5:1 (profiling captures)")
     args = ap.parse_args()
     K, W = max(1, args.steps), max(3, args.warmup)
 
     from powerinfer_b200 import configs
+    if args.config == "sparse-ffn-13b":
+        if int(os.environ.get("RANK", "0")) == 0:
+            sparse_ffn_microbench(args)
+        return
     cfg_name = args.config or configs.HEADLINE
     cfg = configs.CONFIGS[cfg_name]
     import dataclasses

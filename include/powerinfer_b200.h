@@ -97,6 +97,17 @@ int pi_axpy(int wtype, const void * Wt, int64_t n_w_rows, int64_t ncols,
             float * dst,
             void * workspace, size_t workspace_bytes, void * stream);
 
+/* The whole sparse FFN of llm_build_ffn_sparse (llama.cpp:4652-4757) for rows held on this device, given the predictor
+ * logits: dst = sum over active r of act_r * down_t[r,:], with act_r = relu(gate[r,:].x) * (up[r,:].x) when gate != NULL
+ * (llama), else relu(up[r,:].x + up_bias[g]) (falcon: up_bias NULL; opt).  One activation conversion, one compaction of
+ * the mask, one gather launch for up and gate together, the axpy and the fixed-order reduction, chained with programmatic
+ * dependent launch; numerically identical to pi_mul_mat_idx (x2) + the relu / mul / add nodes + pi_axpy.
+ * The dense hidden vector (by global neuron id, idx_stride entries per token) lives in the workspace. */
+int pi_sparse_ffn(int wtype, const void * up, const void * gate, const void * down_t, int64_t n_w_rows, int64_t ncols,
+                  const float * x, int T, const float * idx, int64_t idx_stride, const int32_t * bucket, float threshold,
+                  const float * up_bias, float * dst,
+                  void * workspace, size_t workspace_bytes, void * stream);
+
 /* pi_axpy for one token with NO workspace argument and no allocation of any kind.  It has no counterpart in the
  * reference (whose CUDA back end allocates from its own pool, ggml-cuda.cu:6387-6459): it exists for hosts that own all
  * device memory and forbid a plug-in to cudaMalloc, and for call sites where allocating is not permitted.  The scratch is a

@@ -76,6 +76,7 @@ size_t pi_workspace_bytes(int64_t ncols, int64_t nrows, int T) {
     b += act_bytes(PI_TYPE_Q4_0, (m + 31) / 32 * 32, T) + act_bytes(PI_TYPE_F16, m, T) * 2;   // activation planes, predictor hidden
     b += up((size_t)nrows * 4) + 256 + up((size_t)(nrows + 31) / 32 * 4);                    // list, count/ticket, masks
     b += up((size_t)T * nrows) + up((size_t)T * (nrows / 32 + 1) * 4);                       // Q8 coefficients of h
+    b += up((size_t)T * nrows * 4);                                                          // hidden vector of pi_sparse_ffn
     b += up((size_t)256 * T * ncols * 4);                                                    // axpy partials (<= 256 groups)
     return b + 4096;
 }
@@ -223,6 +224,61 @@ int pi_axpy(int wtype, const void * Wt, int64_t n_w_rows, int64_t ncols,
     int used = G;
     if ((rc = launch_axpy(a, st, &used))) return rc;
     return launch_reduce_partials(partial, used, T, ncols, nullptr, nullptr, dst, st);
+}
+
+int pi_sparse_ffn(int wtype, const void * up, const void * gate, const void * down_t, int64_t n_w_rows, int64_t ncols,
+                  const float * x, int T, const float * idx, int64_t idx_stride, const int32_t * bucket, float threshold,
+                  const float * up_bias, float * dst, void * workspace, size_t workspace_bytes, void * stream) {
+    int rc = check_w(wtype, ncols, up);
+    if (rc) return rc;
+    PI_REQUIRE(down_t && x && idx && dst && T >= 0 && n_w_rows >= 0 && idx_stride >= n_w_rows, "sparse_ffn: bad arguments");
+    PI_REQUIRE(bucket || idx_stride >= n_w_rows, "sparse_ffn: idx_stride must cover every neuron id");
+    PI_REQUIRE(wtype != PI_TYPE_Q4_0 || idx_stride % 32 == 0, "sparse_ffn: Q4_0 needs idx_stride %% 32 == 0 (coefficients are quantised per 32 neurons)");
+    if (T == 0) return PI_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n_w_rows == 0) { PI_CUDA(cudaMemsetAsync(dst, 0, (size_t)T * ncols * 4, st)); return PI_OK; }
+    const int64_t F = idx_stride;                                  // the hidden vector is indexed by global neuron id
+    Scratch s(workspace, workspace_bytes);
+    SparseScratch ss;
+    const int G = axpy_groups(wtype, ncols, T);
+    char * actp = (char *)s.take(act_bytes(wtype, ncols, T));
+    bool ok = aligned(workspace, 256) && actp && carve_sparse(s, n_w_rows, ss);
+    float * h = ok ? (float *)s.take((size_t)T * F * 4) : nullptr;
+    int8_t * cq = nullptr; float * cd = nullptr;
+    if (ok && wtype == PI_TYPE_Q4_0) {
+        cq = (int8_t *)s.take((size_t)T * F);
+        cd = (float *)s.take((size_t)T * (F / 32) * 4);
+        ok = cq && cd;
+    }
+    float * partial = ok && h ? (float *)s.take((size_t)G * T * ncols * 4) : nullptr;
+    if (!ok || !h || !partial) { set_error("sparse_ffn: workspace too small or misaligned"); return PI_ERR_WORKSPACE; }
+    ActBuf act = act_carve(wtype, ncols, T, &actp);
+    PI_CUDA(cudaMemsetAsync(ss.count, 0, 12, st));                                      // count, ticket, status
+    if (bucket || T > 1 || wtype == PI_TYPE_Q4_0) PI_CUDA(cudaMemsetAsync(h, 0, (size_t)T * F * 4, st));
+    if ((rc = launch_convert_act(wtype, x, ncols, ncols, T, act, st))) return rc;
+    // the kernels below are chained with programmatic dependent launch: each may start while its predecessor drains
+    CompactArgs c;
+    c.pdl = true;
+    c.idx = idx; c.idx_stride = idx_stride; c.T = T; c.threshold = threshold; c.n_local = n_w_rows; c.bucket = bucket;
+    c.list = ss.list; c.count = ss.count; c.masks = ss.masks; c.ticket = ss.ticket;
+    if (wtype == PI_TYPE_Q4_0) { c.zero_dst = h; c.zero_stride = F; c.fill_bias = up_bias; c.fill_relu = 1; }
+    if ((rc = launch_compact(c, st))) return rc;
+    GemvArgs g;
+    g.pdl = true;
+    g.wtype = wtype; g.W = up; g.W2 = gate; g.nrows = n_w_rows; g.ncols = ncols; g.x = act.view(); g.T = T;
+    g.list = ss.list; g.count = ss.count; g.bucket = bucket; g.idx = idx; g.idx_stride = idx_stride; g.threshold = threshold;
+    g.bias = up_bias; g.relu = gate ? 0 : 1;
+    g.dst = h; g.dst_stride = F; g.status = ss.status;
+    if ((rc = launch_gemv(g, st))) return rc;
+    if (wtype == PI_TYPE_Q4_0 && T > 1 && (rc = launch_neuron_q8(h, F, F, T, cq, cd, st))) return rc;
+    AxpyArgs a;
+    a.pdl = !(wtype == PI_TYPE_Q4_0 && T > 1);
+    a.wtype = wtype; a.Wt = down_t; a.nrows = n_w_rows; a.ncols = ncols; a.h = h; a.h_stride = F; a.T = T;
+    a.list = ss.list; a.count = ss.count; a.bucket = bucket; a.idx = idx; a.idx_stride = idx_stride; a.threshold = threshold;
+    a.cq = cq; a.cd = cd; a.c_stride = F; a.partial = partial; a.n_groups = G; a.status = ss.status;
+    int used = G;
+    if ((rc = launch_axpy(a, st, &used))) return rc;
+    return launch_reduce_partials(partial, used, T, ncols, nullptr, nullptr, dst, st, T == 1);
 }
 
 int pi_norm(const float * x, int T, int64_t n, int rms, float eps, const float * w, const float * b, float * y, void * stream) {

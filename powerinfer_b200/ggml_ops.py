@@ -138,6 +138,22 @@ def ggml_axpy(a: Weight, b: torch.Tensor, sparse_idx: torch.Tensor, hybrid_aux: 
     return dst
 
 
+def sparse_ffn(up: Weight, gate: Weight | None, down_t: Weight, x: torch.Tensor, sparse_idx: torch.Tensor,
+               gpu_bucket: torch.Tensor | None = None, up_bias: torch.Tensor | None = None) -> torch.Tensor:
+    """llm_build_ffn_sparse (llama.cpp:4652-4757) after the predictor, as one call: the two ggml_mul_mat_idx nodes, the
+    relu / mul / bias nodes and ggml_axpy.  x F32 [T, d], sparse_idx F32 [T, F] -> F32 [T, d]."""
+    x = x.contiguous().float().reshape(-1, up.ncols)
+    T = x.shape[0]
+    sparse_idx = sparse_idx.contiguous().float().reshape(T, -1)
+    F = sparse_idx.shape[1]
+    dst = torch.empty(T, up.ncols, dtype=torch.float32, device="cuda")
+    ws, wsn = _ws.get(up.ncols, max(up.nrows, F), T)
+    check(lib.pi_sparse_ffn(up.wtype, up.ptr, gate.ptr if gate is not None else None, down_t.ptr, up.nrows, up.ncols,
+                            x.data_ptr(), T, sparse_idx.data_ptr(), F, _p(gpu_bucket), sparse_pred_threshold, _p(up_bias),
+                            dst.data_ptr(), ws, wsn, _stream()))
+    return dst
+
+
 def predictor(fc1: Weight, fc2: Weight, p: torch.Tensor) -> torch.Tensor:
     """idx = mul_mat(fc2, relu(mul_mat(fc1, p))) (llama.cpp:4688-4695); p F32 [T, d] -> F32 [T, F]."""
     p = p.contiguous().float().reshape(-1, fc1.ncols)

@@ -108,6 +108,48 @@ def test_sparse_ops_vs_oracle_batches_and_buckets(ops, oracle, wtype, T):
     assert np.abs(down_b - ref_down_b).max() <= ATOL
 
 
+@pytest.mark.parametrize("wtype", [synth.F16, synth.Q4_0])
+@pytest.mark.parametrize("T", [1, 4, 16])
+@pytest.mark.parametrize("gated", [True, False])
+def test_sparse_ffn_one_call_vs_oracle_nodes(ops, oracle, wtype, T, gated):
+    """pi_sparse_ffn against the reference's node sequence on the CPU: mul_mat_idx (up, gate), relu / mul (or bias add +
+    relu), axpy; full and bucketed (hot rows only) forms."""
+    rng = np.random.default_rng(7 + 10 * wtype + T + (100 if gated else 0))
+    d, F = 512, 2048
+    x = rng.standard_normal((T, d), dtype=np.float32)
+    mats = [rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.05) for _ in range(3)]
+    q = [synth.quantize_q4_0(m) if wtype == synth.Q4_0 else m.astype(np.float16) for m in mats]
+    bias = None if gated else (rng.standard_normal(F).astype(np.float32) * np.float32(0.1))
+    idx = (rng.random((T, F)) - 0.8).astype(np.float32)
+    zeros = np.zeros(F, np.int32)
+
+    def ref_ffn(gpu_idx):
+        up = oracle.mul_mat_idx(wtype, q[0], F, d, x, idx, gpu_idx)
+        if gated:
+            gate = oracle.mul_mat_idx(wtype, q[1], F, d, x, idx, gpu_idx)
+            h = np.maximum(gate, 0) * up
+        else:
+            h = np.maximum(up + bias[None, :], 0)                       # the bias add is dense, as the graph's ggml_add
+        return oracle.axpy(wtype, q[2], F, d, h, idx, gpu_idx)
+
+    W = [ops.upload_weight(m, wtype, F, d) for m in q]
+    got = ops.sparse_ffn(W[0], W[1] if gated else None, W[2], dev(x), dev(idx), up_bias=dev(bias) if bias is not None else None)
+    ref = ref_ffn(zeros)
+    assert np.abs(got.cpu().numpy() - ref).max() <= 5 * ATOL, np.abs(got.cpu().numpy() - ref).max()
+    again = ops.sparse_ffn(W[0], W[1] if gated else None, W[2], dev(x), dev(idx), up_bias=dev(bias) if bias is not None else None)
+    assert torch.equal(got, again)
+    # hot rows only (whole 32-neuron blocks 1, 3, 5, ...)
+    blocks = np.arange(1, F // 32, 2)
+    bucket = (blocks[:, None] * 32 + np.arange(32)[None, :]).reshape(-1).astype(np.int32)
+    gpu_idx = np.ones(F, np.int32)
+    gpu_idx[bucket] = 0
+    Wb = [ops.upload_weight(m[bucket], wtype, len(bucket), d) for m in q]
+    got_b = ops.sparse_ffn(Wb[0], Wb[1] if gated else None, Wb[2], dev(x), dev(idx), gpu_bucket=dev(bucket),
+                           up_bias=dev(bias) if bias is not None else None)
+    ref_b = ref_ffn(gpu_idx)
+    assert np.abs(got_b.cpu().numpy() - ref_b).max() <= 5 * ATOL, np.abs(got_b.cpu().numpy() - ref_b).max()
+
+
 def test_predictor_and_active_list(ops, oracle):
     spec = synth.ModelSpec(n_layer=1, d=512, n_ff=4096, rank=128, firing=0.1, seed=5)
     t = synth.build_model(spec)
