@@ -300,6 +300,10 @@ static int launch_wt(const GemvP & p, int tt, bool sparse, bool gated, size_t sm
 
 int launch_gemv(const GemvArgs & a, cudaStream_t st) {
     if (a.T <= 0 || a.nrows <= 0) return PI_OK;
+    if (a.wtype == PI_TYPE_F16 && a.status) {                      // FP16 rows, up to 32 tokens: tensor-core ring kernel
+        const int rc = launch_gemv_mma(a, st);
+        if (rc != PI_ERR_UNSUPPORTED) return rc;
+    }
     if (a.T == 1 && a.status) {
         const int rc = launch_gemv_ring(a, a.status, a.pdl, st);
         if (rc != PI_ERR_UNSUPPORTED) return rc;

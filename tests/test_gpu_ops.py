@@ -150,6 +150,36 @@ def test_sparse_ffn_one_call_vs_oracle_nodes(ops, oracle, wtype, T, gated):
     assert np.abs(got_b.cpu().numpy() - ref_b).max() <= 5 * ATOL, np.abs(got_b.cpu().numpy() - ref_b).max()
 
 
+@pytest.mark.parametrize("wtype", [synth.F16, synth.Q4_0])
+def test_hot_rows_from_placement_match_the_cpu_split(ops, oracle, wtype):
+    """The placement module's gpu_idx / gpu_bucket drive both halves of the reference's hybrid split: the device computes
+    the hot rows (bucket form), the CPU operator the cold ones (gpu_idx form); their sum is the full result
+    (llama.cpp:4581-4594)."""
+    from powerinfer_b200 import placement
+    rng = np.random.default_rng(3 + wtype)
+    d, F, T = 512, 2048, 2
+    prof = synth.zipf_profile(F, 0.15)[rng.permutation(F)]
+    gpu_idx, bucket = placement.bucket_of_whole_blocks(prof, 768)
+    x = rng.standard_normal((T, d), dtype=np.float32)
+    mats = [rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.05) for _ in range(3)]
+    q = [synth.quantize_q4_0(m) if wtype == synth.Q4_0 else m.astype(np.float16) for m in mats]
+    idx = np.where(rng.random((T, F)) < prof[None, :], 1.0, -1.0).astype(np.float32)
+    zeros = np.zeros(F, np.int32)
+
+    def cpu_ffn(gi):
+        up = oracle.mul_mat_idx(wtype, q[0], F, d, x, idx, gi)
+        gate = oracle.mul_mat_idx(wtype, q[1], F, d, x, idx, gi)
+        return oracle.axpy(wtype, q[2], F, d, np.maximum(gate, 0) * up, idx, gi)
+
+    Wb = [ops.upload_weight(m[bucket], wtype, len(bucket), d) for m in q]
+    hot = ops.sparse_ffn(Wb[0], Wb[1], Wb[2], dev(x), dev(idx), gpu_bucket=dev(bucket)).cpu().numpy()
+    ref_hot = cpu_ffn(gpu_idx)                                    # the CPU op run with the COMPLEMENT skipped = the hot part
+    assert np.abs(hot - ref_hot).max() <= 5 * ATOL
+    cold = cpu_ffn(1 - gpu_idx)
+    full = cpu_ffn(zeros)
+    assert np.abs((hot + cold) - full).max() <= 2e-3              # Q4_0 coefficients are per 32-neuron block: whole blocks keep them equal
+
+
 def test_predictor_and_active_list(ops, oracle):
     spec = synth.ModelSpec(n_layer=1, d=512, n_ff=4096, rank=128, firing=0.1, seed=5)
     t = synth.build_model(spec)
