@@ -173,9 +173,9 @@ def test_hot_rows_from_placement_match_the_cpu_split(ops, oracle, wtype):
 
     Wb = [ops.upload_weight(m[bucket], wtype, len(bucket), d) for m in q]
     hot = ops.sparse_ffn(Wb[0], Wb[1], Wb[2], dev(x), dev(idx), gpu_bucket=dev(bucket)).cpu().numpy()
-    ref_hot = cpu_ffn(gpu_idx)                                    # the CPU op run with the COMPLEMENT skipped = the hot part
+    ref_hot = cpu_ffn(1 - gpu_idx)                                # the CPU op skips rows flagged 1: flag the cold ones -> hot part
     assert np.abs(hot - ref_hot).max() <= 5 * ATOL
-    cold = cpu_ffn(1 - gpu_idx)
+    cold = cpu_ffn(gpu_idx)                                       # what the reference's CPU half computes
     full = cpu_ffn(zeros)
     assert np.abs((hot + cold) - full).max() <= 2e-3              # Q4_0 coefficients are per 32-neuron block: whole blocks keep them equal
 
