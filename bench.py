@@ -259,12 +259,34 @@ def sparse_ffn_microbench(args):
             "cpu_baseline": ({"value": head_cpu["sparse_ffn"]["GBps"], "unit": "GB/s", "cores": head_cpu["threads"], "kind": "reference",
                               "sample": "reference ggml mul_mat_idx x2 + axpy on the same shape and sparsity, batch 1, best of 3"} if head_cpu else None),
             "table": table, "cpu_table": cpu}
-    print(json.dumps(line))
+    _emit(line)
 
 
 # ------------------------------------------------------------------------------------------------ main
 
+def _emit(line: dict):
+    """The JSON line is the only thing this program writes to its stdout: see _guard_stdout."""
+    sys.stdout.flush()
+    if _REAL_STDOUT is not None:
+        os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+    else:
+        print(json.dumps(line), flush=True)
+
+
+_REAL_STDOUT = None
+
+
+def _guard_stdout():
+    """Libraries loaded below (NCCL prints its version banner on stdout) must not get between the caller and the one JSON
+    line: file descriptor 1 is pointed at stderr for the rest of the run and the line is written to the saved descriptor."""
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
+
+
 def main():
+    _guard_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -316,7 +338,7 @@ def main():
                 "dtype": "q4_0xq8_0 int8 dot, f32 accumulate" if spec.wtype == 2 else "f16 weights, f32 accumulate",
                 "data": "synthetic", "config": config, "cpu_baseline": best,
                 "e2e": {"value": best["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        _emit(line)
         return
 
     import numpy as np
@@ -439,7 +461,7 @@ def main():
                 line["cpu_baseline"] = cpu_reference(spec)
             except Exception as ex:                     # the checker is optional at run time; say so rather than fail the bench
                 line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "reference", "sample": f"unavailable: {ex}"}
-        print(json.dumps(line))
+        _emit(line)
     eng.close()
     if world > 1:
         dist.barrier()

@@ -231,7 +231,7 @@ int launch_attention(const AttnArgs & a, cudaStream_t st);
 // v = sum_g partial[g, t, :] (+ extra[t, :]) is written into slot rank_id of every rank's mailbox, then the flags are
 // raised to the next epoch (see pi_exchange in the public header)
 int launch_exchange_push(const pi_exchange & x, const float * partial, int n_groups, int T, int64_t n, const float * extra,
-                         unsigned int * status, cudaStream_t st);
+                         unsigned int * status, cudaStream_t st, bool pdl = false);
 
 // ------------------------------------------------------------------------------------ device primitives
 #ifdef __CUDACC__

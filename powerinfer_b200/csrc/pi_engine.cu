@@ -508,7 +508,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
         if (!falcon) {
             Pending pa;
             if (multi) {
-                STAGE(PI_STAGE_EXCHANGE, 1, launch_exchange_push(e->xch, e->attn_out, 1, T, d, nullptr, e->status, st));
+                STAGE(PI_STAGE_EXCHANGE, 1, launch_exchange_push(e->xch, e->attn_out, 1, T, d, nullptr, e->status, st, pdl));
                 pa.mailbox = true;
             } else {
                 pa.vec = e->attn_out;
@@ -596,7 +596,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
         pend.bias = L->down_b;
         if (multi) {
             // falcon sums its two branches locally first: one exchange per layer (llama.cpp:5443-5447)
-            STAGE(PI_STAGE_EXCHANGE, 1, launch_exchange_push(e->xch, e->partial, used, T, d, falcon ? e->attn_out : nullptr, e->status, st));
+            STAGE(PI_STAGE_EXCHANGE, 1, launch_exchange_push(e->xch, e->partial, used, T, d, falcon ? e->attn_out : nullptr, e->status, st, pdl && T == 1));
             pend.mailbox = true;
         } else {
             STAGE(PI_STAGE_DOWN, 1, launch_reduce_partials(e->partial, used, T, d, nullptr, nullptr, e->ffn_vec, st, pdl));

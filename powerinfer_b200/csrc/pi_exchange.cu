@@ -13,7 +13,7 @@
 
 namespace pi {
 
-static constexpr int PUSH_THREADS = 128;
+static constexpr int PUSH_WARPS = 32;
 
 struct PushP {
     const float * partial; int n_groups; int64_t group_stride; int64_t total; const float * extra;
@@ -21,25 +21,45 @@ struct PushP {
     int n_ranks, rank_id; int64_t slot_floats; unsigned int * epoch; unsigned int * ticket;
 };
 
-__global__ void __launch_bounds__(PUSH_THREADS) k_exchange_push(const PushP p) {
+// A CTA owns 128 consecutive values.  Warp w adds groups w, w+32, ... (all its loads in flight at once: the partials
+// were just written, so this is one L2 round trip, not n_groups of them); the 32 warp sums are added in warp order, then
+// warp 0 stores the result into every rank's mailbox.  The order is fixed, so every launch gives the same bits.
+__global__ void __launch_bounds__(PUSH_WARPS * 32) k_exchange_push(const PushP p) {
+    __shared__ float4 s_part[PUSH_WARPS][32];
     __shared__ int s_last;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    pdl_launch();
+    pdl_wait();
     // every CTA reads the epoch before it takes a ticket; only the last ticket holder advances it
     const unsigned int e = *reinterpret_cast<volatile unsigned int *>(p.epoch) + 1u;
     const size_t slot = ((size_t)(e & 1u) * p.n_ranks + p.rank_id) * (size_t)p.slot_floats;
-    const int64_t n4 = p.total / 4;
-    for (int64_t i = (int64_t)blockIdx.x * PUSH_THREADS + threadIdx.x; i < n4; i += (int64_t)gridDim.x * PUSH_THREADS) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int g = 0; g < p.n_groups; g++) {
-            const float4 a = __ldcg(reinterpret_cast<const float4 *>(p.partial + (size_t)g * p.group_stride) + i);
-            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+    const int64_t i4 = (int64_t)blockIdx.x * 32 + lane;                // float4 index
+    const bool ok = i4 * 4 < p.total;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ok) {
+        for (int j0 = w; j0 < p.n_groups; j0 += PUSH_WARPS * 8) {
+            float4 a[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int j = j0 + u * PUSH_WARPS;
+                a[u] = j < p.n_groups ? __ldcg(reinterpret_cast<const float4 *>(p.partial + (size_t)j * p.group_stride) + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) { v.x += a[u].x; v.y += a[u].y; v.z += a[u].z; v.w += a[u].w; }
         }
-        if (p.extra) {
-            const float4 a = reinterpret_cast<const float4 *>(p.extra)[i];
-            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
-        }
-        for (int q = 0; q < p.n_ranks; q++) reinterpret_cast<float4 *>(p.mbox[q] + slot)[i] = v;
     }
-    __threadfence_system();
+    s_part[w][lane] = v;
+    __syncthreads();
+    if (w == 0 && ok) {
+#pragma unroll
+        for (int k = 1; k < PUSH_WARPS; k++) { const float4 a = s_part[k][lane]; v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w; }
+        if (p.extra) {
+            const float4 a = reinterpret_cast<const float4 *>(p.extra)[i4];
+            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+        }
+        for (int q = 0; q < p.n_ranks; q++) reinterpret_cast<float4 *>(p.mbox[q] + slot)[i4] = v;
+        __threadfence_system();
+    }
     __syncthreads();
     if (threadIdx.x == 0) s_last = atomicAdd(p.ticket, 1u) == gridDim.x - 1;
     __syncthreads();
@@ -53,7 +73,7 @@ __global__ void __launch_bounds__(PUSH_THREADS) k_exchange_push(const PushP p) {
 }
 
 int launch_exchange_push(const pi_exchange & x, const float * partial, int n_groups, int T, int64_t n, const float * extra,
-                         unsigned int * status, cudaStream_t st) {
+                         unsigned int * status, cudaStream_t st, bool pdl) {
     (void)status;
     PI_REQUIRE(x.n_ranks >= 1 && x.n_ranks <= PI_MAX_RANKS && x.mailbox_local && x.epoch && x.ticket, "exchange: not configured");
     PI_REQUIRE((int64_t)T * n <= x.slot_floats && (T * n) % 4 == 0, "exchange: vector of %lld floats does not fit a slot", (long long)T * n);
@@ -61,10 +81,8 @@ int launch_exchange_push(const pi_exchange & x, const float * partial, int n_gro
     p.partial = partial; p.n_groups = n_groups; p.group_stride = (int64_t)T * n; p.total = (int64_t)T * n; p.extra = extra;
     for (int q = 0; q < PI_MAX_RANKS; q++) { p.mbox[q] = q < x.n_ranks ? x.mailbox_peer[q] : nullptr; p.flags[q] = q < x.n_ranks ? x.flags_peer[q] : nullptr; }
     p.n_ranks = x.n_ranks; p.rank_id = x.rank_id; p.slot_floats = x.slot_floats; p.epoch = x.epoch; p.ticket = x.ticket;
-    const int64_t n4 = p.total / 4;
-    const int grid = (int)imin64((n4 + PUSH_THREADS - 1) / PUSH_THREADS, sm_count());
-    k_exchange_push<<<grid, PUSH_THREADS, 0, st>>>(p);
-    PI_LAUNCH_CHECK("k_exchange_push");
+    const int grid = (int)((p.total / 4 + 31) / 32);
+    PI_CUDA(launch_k(k_exchange_push, dim3(grid), dim3(PUSH_WARPS * 32), 0, st, pdl, p));
     return PI_OK;
 }
 
