@@ -240,8 +240,36 @@ int launch_exchange_push(const pi_exchange & x, const float * partial, int n_gro
 // stream is still running; it must call pdl_wait() before it reads anything the predecessor wrote and before it writes
 // anything the predecessor may still read (weights are immutable, so prefetching them before the wait is safe).
 // pdl_launch() lets the NEXT kernel be scheduled early.  Both are no-ops for a normally launched kernel.
+#ifndef PI_TIMELINE
 __device__ __forceinline__ void pdl_wait()   { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#define PI_TL_MARK(i) do { } while (0)
+#else
+// Timeline builds (-DPI_TIMELINE -rdc=true, never the shipped library): thread 0 of CTA 0 of every kernel stamps the
+// global timer when the kernel starts, when its dependency wait begins and when it returns (= its producer is complete).
+extern __device__ unsigned long long g_tl[65536 * 16];
+extern __device__ unsigned int g_tl_n;
+static __shared__ unsigned int s_tl_slot;
+__device__ __forceinline__ unsigned long long tl_time() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ bool tl_me() { return blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0; }
+__device__ __forceinline__ void pdl_launch() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tl_me()) {
+        const unsigned int s = atomicAdd(&g_tl_n, 1u) & 65535u;
+        s_tl_slot = s;
+        unsigned int smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_tl[s * 16 + 0] = tl_time(); g_tl[s * 16 + 1] = (unsigned long long)clock64();
+        g_tl[s * 16 + 2] = ((unsigned long long)gridDim.x << 32) | blockDim.x; g_tl[s * 16 + 3] = smid;
+        for (int k = 8; k < 16; k++) g_tl[s * 16 + k] = 0;
+    }
+}
+__device__ __forceinline__ void pdl_wait() {
+    if (tl_me()) { g_tl[s_tl_slot * 16 + 4] = tl_time(); }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tl_me()) { g_tl[s_tl_slot * 16 + 5] = tl_time(); g_tl[s_tl_slot * 16 + 6] = (unsigned long long)clock64(); }
+}
+#define PI_TL_MARK(i) do { if (tl_me()) g_tl[s_tl_slot * 16 + 8 + (i)] = tl_time(); } while (0)
+#endif
 
 // Up to two byte ranges (weights of kernels that run later in the step) to pull into L2.  Every participating thread
 // issues bulk L2 prefetches for 8 KB pieces, pieces interleaved over all participating threads so the range arrives

@@ -70,7 +70,9 @@ __device__ __forceinline__ void emit_act8(int type, const ActBuf & a, int t, int
     }
 }
 
-__global__ void __launch_bounds__(1024) k_norm(const NormP p) {
+// MAXT = the launch bound: 512 threads cover n <= 8192 with registers to spare for the weights, 1024 cover n <= 16384
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT) k_norm(const NormP p) {
     __shared__ double s_red[32];
     const int t = blockIdx.x;
     const int64_t n = p.n;
@@ -108,45 +110,79 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
         __syncthreads();
         partial += (size_t)par * p.n_groups * tn;
     }
+    // ---- all loads of all chunks first (x_out may alias the inputs, so the compiler cannot move a load across a store
+    //      itself): one round trip instead of one per chunk
     float v[NORM_CHUNKS][8];
     bool ok[NORM_CHUNKS];
+    float4 in[NORM_CHUNKS][2][2];                                   // [chunk][x | residual][half]
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int k = 0; k < NORM_CHUNKS; k++) {
         const int64_t c = ((int64_t)k * blockDim.x + threadIdx.x) * 8;
         ok[k] = c < n;
+        const size_t o = (size_t)t * n + c;
+#pragma unroll
+        for (int q = 0; q < 2; q++) { in[k][q][0] = z4; in[k][q][1] = z4; }
+        if (ok[k]) {
+            if (!p.partial) { in[k][0][0] = *reinterpret_cast<const float4 *>(p.x + o); in[k][0][1] = *reinterpret_cast<const float4 *>(p.x + o + 4); }
+            if (p.residual)  { in[k][1][0] = *reinterpret_cast<const float4 *>(p.residual + o); in[k][1][1] = *reinterpret_cast<const float4 *>(p.residual + o + 4); }
+        }
+    }
+    auto add8 = [](float (&d)[8], const float4 a, const float4 b) {
+        d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w; d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
+    };
+#pragma unroll
+    for (int k = 0; k < NORM_CHUNKS; k++) {
+        const int64_t c = ((int64_t)k * blockDim.x + threadIdx.x) * 8;
+        const size_t o = (size_t)t * n + c;
 #pragma unroll
         for (int j = 0; j < 8; j++) v[k][j] = 0.f;
-        const size_t o = (size_t)t * n + c;
         if (ok[k]) {
-        if (p.partial) {
-            for (int g = 0; g < p.n_groups; g++) {
-                const float4 a = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)g * tn + o));
-                const float4 b = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)g * tn + o + 4));
-                v[k][0] += a.x; v[k][1] += a.y; v[k][2] += a.z; v[k][3] += a.w;
-                v[k][4] += b.x; v[k][5] += b.y; v[k][6] += b.z; v[k][7] += b.w;
+            if (p.partial) {
+                for (int g = 0; g < p.n_groups; g++) {
+                    const float4 a = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)g * tn + o));
+                    const float4 b = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)g * tn + o + 4));
+                    add8(v[k], a, b);
+                }
+            } else {
+                add8(v[k], in[k][0][0], in[k][0][1]);
             }
-        } else {
-            const float4 a = *reinterpret_cast<const float4 *>(p.x + o);
-            const float4 b = *reinterpret_cast<const float4 *>(p.x + o + 4);
-            v[k][0] = a.x; v[k][1] = a.y; v[k][2] = a.z; v[k][3] = a.w;
-            v[k][4] = b.x; v[k][5] = b.y; v[k][6] = b.z; v[k][7] = b.w;
+            // same order of additions as the graph: bias, residual, second residual (the rarer two cost their own round trip)
+            if (p.in_bias) add8(v[k], *reinterpret_cast<const float4 *>(p.in_bias + c), *reinterpret_cast<const float4 *>(p.in_bias + c + 4));
+            if (p.residual) add8(v[k], in[k][1][0], in[k][1][1]);
+            if (p.residual2) add8(v[k], *reinterpret_cast<const float4 *>(p.residual2 + o), *reinterpret_cast<const float4 *>(p.residual2 + o + 4));
         }
-        auto add8 = [&](const float * src) {
-            const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
-            v[k][0] += a.x; v[k][1] += a.y; v[k][2] += a.z; v[k][3] += a.w;
-            v[k][4] += b.x; v[k][5] += b.y; v[k][6] += b.z; v[k][7] += b.w;
-        };
-        if (p.in_bias) add8(p.in_bias + c);
-        if (p.residual) add8(p.residual + o);
-        if (p.residual2) add8(p.residual2 + o);
-        if (p.x_out) {
+    }
+    // weights (made L2-resident by the hints above): issued before the stores and the reductions so that their latency hides there
+    float wv[NORM_CHUNKS][8], bv[NORM_CHUNKS][8];
+#pragma unroll
+    for (int k = 0; k < NORM_CHUNKS; k++) {
+        const int64_t c = ((int64_t)k * blockDim.x + threadIdx.x) * 8;
+#pragma unroll
+        for (int j = 0; j < 8; j++) { wv[k][j] = 1.f; bv[k][j] = 0.f; }
+        if (MAXT <= 512) {
+            if (ok[k] && p.w) {
+                const float4 a = *reinterpret_cast<const float4 *>(p.w + c), b = *reinterpret_cast<const float4 *>(p.w + c + 4);
+                wv[k][0] = a.x; wv[k][1] = a.y; wv[k][2] = a.z; wv[k][3] = a.w; wv[k][4] = b.x; wv[k][5] = b.y; wv[k][6] = b.z; wv[k][7] = b.w;
+            }
+            if (ok[k] && p.b) {
+                const float4 a = *reinterpret_cast<const float4 *>(p.b + c), b = *reinterpret_cast<const float4 *>(p.b + c + 4);
+                bv[k][0] = a.x; bv[k][1] = a.y; bv[k][2] = a.z; bv[k][3] = a.w; bv[k][4] = b.x; bv[k][5] = b.y; bv[k][6] = b.z; bv[k][7] = b.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NORM_CHUNKS; k++) {
+        const int64_t c = ((int64_t)k * blockDim.x + threadIdx.x) * 8;
+        const size_t o = (size_t)t * n + c;
+        if (ok[k] && p.x_out) {
             *reinterpret_cast<float4 *>(p.x_out + o)     = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
             *reinterpret_cast<float4 *>(p.x_out + o + 4) = make_float4(v[k][4], v[k][5], v[k][6], v[k][7]);
-        }
         }
         if (p.act2_type && p.act2_src == 0) emit_act8(p.act2_type, p.act2, t, n, (int)(c / 8), v[k], ok[k]);
     }
 
+    PI_TL_MARK(0);
     float scale, mean = 0.f;
     if (p.rms) {
         double s = 0.0;
@@ -176,25 +212,26 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
         const float var = (float)(s2 / (double)n);
         scale = 1.0f / sqrtf(var + p.eps);
     }
+    PI_TL_MARK(1);
 #pragma unroll
     for (int k = 0; k < NORM_CHUNKS; k++) {
         const int64_t c = ((int64_t)k * blockDim.x + threadIdx.x) * 8;
-        float y[8], wv[8], bv[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) { wv[j] = 1.f; bv[j] = 0.f; }
-        if (ok[k] && p.w) {
-            const float4 a = *reinterpret_cast<const float4 *>(p.w + c), b = *reinterpret_cast<const float4 *>(p.w + c + 4);
-            wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
-        }
-        if (ok[k] && p.b) {
-            const float4 a = *reinterpret_cast<const float4 *>(p.b + c), b = *reinterpret_cast<const float4 *>(p.b + c + 4);
-            bv[0] = a.x; bv[1] = a.y; bv[2] = a.z; bv[3] = a.w; bv[4] = b.x; bv[5] = b.y; bv[6] = b.z; bv[7] = b.w;
+        float y[8];
+        if (MAXT > 512) {                                              // no registers to hold them across the reductions
+            if (ok[k] && p.w) {
+                const float4 a = *reinterpret_cast<const float4 *>(p.w + c), b = *reinterpret_cast<const float4 *>(p.w + c + 4);
+                wv[k][0] = a.x; wv[k][1] = a.y; wv[k][2] = a.z; wv[k][3] = a.w; wv[k][4] = b.x; wv[k][5] = b.y; wv[k][6] = b.z; wv[k][7] = b.w;
+            }
+            if (ok[k] && p.b) {
+                const float4 a = *reinterpret_cast<const float4 *>(p.b + c), b = *reinterpret_cast<const float4 *>(p.b + c + 4);
+                bv[k][0] = a.x; bv[k][1] = a.y; bv[k][2] = a.z; bv[k][3] = a.w; bv[k][4] = b.x; bv[k][5] = b.y; bv[k][6] = b.z; bv[k][7] = b.w;
+            }
         }
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             float r = __fmul_rn(v[k][j], scale);                       // separate roundings, as separate graph nodes give
-            if (ok[k] && p.w) r = __fmul_rn(r, wv[j]);
-            if (ok[k] && p.b) r = __fadd_rn(r, bv[j]);
+            if (ok[k] && p.w) r = __fmul_rn(r, wv[k][j]);
+            if (ok[k] && p.b) r = __fadd_rn(r, bv[k][j]);
             y[j] = r;
         }
         if (ok[k] && p.y) {
@@ -205,6 +242,7 @@ __global__ void __launch_bounds__(1024) k_norm(const NormP p) {
         if (p.act_type) emit_act8(p.act_type, p.act, t, n, (int)(c / 8), y, ok[k]);
         if (p.act2_type && p.act2_src == 1) emit_act8(p.act2_type, p.act2, t, n, (int)(c / 8), y, ok[k]);
     }
+    PI_TL_MARK(2);
 }
 
 // One CTA per SM, every thread issues bulk L2 prefetches for its pieces: no shared memory and few registers, so the
@@ -230,7 +268,8 @@ int launch_norm(const NormArgs & a, cudaStream_t st) {
     p.y = a.y; p.act_type = a.act_type; p.act = a.act; p.act2_type = a.act2_type; p.act2 = a.act2; p.act2_src = a.act2_src;
     int threads = (int)((a.n / 8 + NORM_CHUNKS - 1) / NORM_CHUNKS);
     threads = min(1024, max(32, (threads + 31) / 32 * 32));
-    PI_CUDA(launch_k(k_norm, dim3(a.T), dim3(threads), 0, st, a.pdl, p));
+    if (threads <= 512) PI_CUDA(launch_k(k_norm<512>, dim3(a.T), dim3(threads), 0, st, a.pdl, p));
+    else                PI_CUDA(launch_k(k_norm<1024>, dim3(a.T), dim3(threads), 0, st, a.pdl, p));
     return PI_OK;
 }
 
@@ -355,6 +394,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
         }
     }
 
+    PI_TL_MARK(0);
     // ---- scores: one thread per position; the new token's K comes from shared memory
     const float scale = 1.0f / sqrtf((float)hd);
     float mx = -INFINITY;
@@ -385,6 +425,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
 #pragma unroll
     for (int i = 1; i < ATTN_THREADS / 32; i++) mx = fmaxf(mx, s_max[i]);
 
+    PI_TL_MARK(1);
     // ---- softmax (ggml.c:10708-10777)
     double part = 0.0;
     for (int j = tid; j <= pos; j += ATTN_THREADS) {
@@ -404,6 +445,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     }
     __syncthreads();
 
+    PI_TL_MARK(2);
     // ---- out[e] = sum_j p_j V[j, e]: thread = (chunk of 8 columns, slice of positions); slices reduced through smem
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     auto fma8 = [&](float pj, const uint4 vv) {
@@ -430,6 +472,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
             for (int u = 0; u < 4; u++) fma8(pj[u], vv[u]);
         }
     }
+    PI_TL_MARK(3);
     float * red = sc;                                              // exp values are dead: reuse as [slices][hd]
     if (sl < slices) {
 #pragma unroll
@@ -460,6 +503,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
             emit_act8(p.out_act_type, p.out_act, t, n, h * (hd / 8) + lane, y, valid);
         }
     }
+    PI_TL_MARK(4);
 }
 
 int launch_attention(const AttnArgs & a, cudaStream_t st) {

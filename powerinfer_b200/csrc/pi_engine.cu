@@ -86,6 +86,18 @@ __global__ void k_advance(int32_t * __restrict__ tokens, int32_t * __restrict__ 
 
 using namespace pi;
 
+#ifdef PI_TIMELINE
+__device__ unsigned long long pi::g_tl[65536 * 16];
+__device__ unsigned int pi::g_tl_n;
+extern "C" __attribute__((visibility("default"))) int pi_timeline_read(unsigned long long * host, unsigned int * n, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(n, pi::g_tl_n, 4);
+    cudaMemcpyFromSymbol(host, pi::g_tl, sizeof(unsigned long long) * 65536 * 16);
+    if (reset) { unsigned int z = 0; cudaMemcpyToSymbol(pi::g_tl_n, &z, 4); }
+    return 0;
+}
+#endif
+
 // ------------------------------------------------------------------------------------------------ engine state
 
 struct pi_engine {

@@ -371,12 +371,16 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
             bulk_g2s(ring + s * stage_bytes + lane * row_stride, p.Wt + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
         }
     };
+    PI_TL_MARK(0);
     if (wid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
-    for (int i0 = wid; i0 < n_mine; i0 += nwarp * 4) {             // 4 rows per warp per pass: their loads overlap
+    PI_TL_MARK(1);
+    // warp 0 is busy issuing the copies (~80 ns each): the coefficients are the other warps' work
+    const int cw = nwarp > 1 ? nwarp - 1 : 1, cw0 = nwarp > 1 ? wid - 1 : 0;
+    for (int i0 = cw0; i0 >= 0 && i0 < n_mine; i0 += cw * 4) {     // 4 rows per warp per pass: their loads overlap
         float hv[4], pv[4]; int64_t g[4]; bool ok[4];
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-            const int i = i0 + u * nwarp;
+            const int i = i0 + u * cw;
             ok[u] = i < n_mine && rows[i] >= 0;
             const int r = ok[u] ? rows[i] : 0;
             g[u] = p.bucket ? p.bucket[r] : r;
@@ -385,7 +389,7 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
         }
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-            const int i = i0 + u * nwarp;
+            const int i = i0 + u * cw;
             float c;
             if (WT == PI_TYPE_F16) {
                 c = round_f16(hv[u]);
@@ -402,6 +406,7 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
     }
     __syncthreads();
 
+    PI_TL_MARK(2);
     constexpr int NACC = WT == PI_TYPE_F16 ? CPT * 8 : 8;
     float acc[NACC];
 #pragma unroll
@@ -409,6 +414,7 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
     const int n_chunks = p.ncols / 8;
     const int n_words = p.nb * 4;
     bool dead = false;                                               // warp-uniform
+    float corr = 0.f;                                                // Q4_0: sum of the row scales (see the dequantisation below)
 
     for (int st = 0; st < n_stages; st++) {
         const int s = st % S;
@@ -422,6 +428,7 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
             dead = __any_sync(0xffffffffu, gave_up) != 0;
             if (dead && lane == 0) atomicOr(p.status, 2u);
         }
+        if (st == 0) PI_TL_MARK(3);
         const int cnt = min(PIPE_RS, n_mine - st * PIPE_RS);
         if (!dead) {
 #pragma unroll
@@ -445,12 +452,16 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
                     }
                 } else if (tid < n_words) {
                     const uint32_t word = reinterpret_cast<const uint32_t *>(row)[tid];
-                    const float sc = c * __half2float(reinterpret_cast<const __half *>(row + (size_t)p.nb * 16)[tid >> 2]);
+                    // nibble q -> the float 0.5 + q/256 with one byte permute (q lands in mantissa bits 16..19 under the
+                    // exponent of 0.5); (q - 8) * sc = (0.5 + q/256) * 256 sc - 0.53125 * 256 sc, and the second term is
+                    // summed once per row instead of once per weight.  Costs ~4 bits of the FP32 accumulator.
+                    const float sc = 256.0f * c * __half2float(reinterpret_cast<const __half *>(row + (size_t)p.nb * 16)[tid >> 2]);
                     const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu;
+                    corr += sc;
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        acc[j]     = fmaf(nib_to_float(lo, j), sc, acc[j]);
-                        acc[4 + j] = fmaf(nib_to_float(hi, j), sc, acc[4 + j]);
+                        acc[j]     = fmaf(__uint_as_float(__byte_perm(lo, 0x3F000000u, 0x7044u | (uint32_t)(j << 8))), sc, acc[j]);
+                        acc[4 + j] = fmaf(__uint_as_float(__byte_perm(hi, 0x3F000000u, 0x7044u | (uint32_t)(j << 8))), sc, acc[4 + j]);
                     }
                 }
             }
@@ -465,6 +476,7 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
         for (int s = 0; s < S; s++) { int spins = 0; while (!mbar_try_wait(full + s, 0) && !mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
     }
 
+    PI_TL_MARK(4);
     float * out = p.partial + (size_t)cta * p.ncols;
     if (WT == PI_TYPE_F16) {
 #pragma unroll
@@ -477,6 +489,8 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
         }
     } else if (tid < n_words) {
         const int b = tid >> 2, i = tid & 3;
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j] = fmaf(-0.53125f, corr, acc[j]);
         *reinterpret_cast<float4 *>(out + (size_t)b * QK + 4 * i)      = make_float4(acc[0], acc[1], acc[2], acc[3]);
         *reinterpret_cast<float4 *>(out + (size_t)b * QK + 16 + 4 * i) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
