@@ -395,28 +395,58 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     }
 
     PI_TL_MARK(0);
-    // ---- scores: one thread per position; the new token's K comes from shared memory
+    // ---- scores.  head_dim/8 a power of two <= 32 (head_dim 32, 64, 128, 256): a group of head_dim/8 lanes reads one
+    //      cached row as ONE coalesced request (a lane per 16-byte chunk, its 8 query values in registers), U rows in flight
+    //      per group, the dot finished by a shuffle tree.  (One thread per row, the other branch, makes every request touch
+    //      32 different rows and needs head_dim/32 dependent batches.)  The new token's K comes from shared memory.
     const float scale = 1.0f / sqrtf((float)hd);
     float mx = -INFINITY;
-    for (int j = tid; j <= pos; j += ATTN_THREADS) {
-        float a = 0.f;
-        if (j < pos) {
-            const uint4 * kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * dkv);
-            float part[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int c = 0; c < chunks; c += 4) {
-                uint4 kv[4];
+    if ((chunks & (chunks - 1)) == 0 && chunks <= 32) {
+        constexpr int U = 4;
+        const int LP = chunks, NG = ATTN_THREADS / LP, gi = tid / LP, c = tid % LP;
+        float qr[8];
 #pragma unroll
-                for (int u = 0; u < 4; u++) kv[u] = __ldg(kr + c + u);               // chunks % 4 == 0 (head_dim % 32 == 0)
+        for (int j = 0; j < 8; j++) qr[j] = q32[c * 8 + j];
+        const int n_iter = (pos + NG) / NG;                          // ceil((pos + 1) / NG): the same for every lane
+        for (int it = 0; it < n_iter; it += U) {
+            uint4 kv[U];
 #pragma unroll
-                for (int u = 0; u < 4; u++) part[u] += dot8(kv[u], q32 + (c + u) * 8);
+            for (int u = 0; u < U; u++) {
+                const int j = gi + (it + u) * NG;
+                kv[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (j < pos) kv[u] = __ldg(reinterpret_cast<const uint4 *>(kc + (size_t)j * dkv) + c);
+                else if (j == pos) kv[u] = reinterpret_cast<const uint4 *>(k16)[c];
             }
-            a = (part[0] + part[1]) + (part[2] + part[3]);
-        } else {
-            for (int c = 0; c < chunks; c++) a += dot8(reinterpret_cast<const uint4 *>(k16)[c], q32 + c * 8);
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int j = gi + (it + u) * NG;
+                float a = dot8(kv[u], qr);
+                for (int o = LP >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                a *= scale;
+                if (c == 0 && j <= pos) { sc[j] = a; mx = fmaxf(mx, a); }
+            }
         }
-        a *= scale;
-        sc[j] = a;
-        mx = fmaxf(mx, a);
+    } else {
+        for (int j = tid; j <= pos; j += ATTN_THREADS) {
+            float a = 0.f;
+            if (j < pos) {
+                const uint4 * kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * dkv);
+                float part[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int c = 0; c < chunks; c += 4) {
+                    uint4 kv[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) kv[u] = __ldg(kr + c + u);               // chunks % 4 == 0 (head_dim % 32 == 0)
+#pragma unroll
+                    for (int u = 0; u < 4; u++) part[u] += dot8(kv[u], q32 + (c + u) * 8);
+                }
+                a = (part[0] + part[1]) + (part[2] + part[3]);
+            } else {
+                for (int c = 0; c < chunks; c++) a += dot8(reinterpret_cast<const uint4 *>(k16)[c], q32 + c * 8);
+            }
+            a *= scale;
+            sc[j] = a;
+            mx = fmaxf(mx, a);
+        }
     }
     mx = warp_max(mx);
     if (lane == 0) s_max[wid] = mx;
