@@ -150,6 +150,27 @@ def test_batched_sequences_match_single(engine_mod, name, T):
     eng.close()
 
 
+def test_model_loaded_from_powerinfer_gguf_matches_reference(engine_mod, tmp_path):
+    """The file the reference's llama.cpp loads, read by the repo's own loader and run by the engine: the logits of the
+    first decode steps match the reference's (golden) logits."""
+    pytest.importorskip("gguf")
+    from powerinfer_b200 import gguf_loader
+    name = "llama_q4_0"
+    spec0 = mg.MODEL_CASES[name]
+    g = np.load(os.path.join(GOLD, f"model_{name}.npz"))
+    path = str(tmp_path / "m.powerinfer.gguf")
+    mg.write_gguf(spec0, synth.build_model(spec0), path)
+    spec, tensors = gguf_loader.load_model(path)
+    eng = engine_mod.DecodeEngine(spec, {k: np.asarray(v) for k, v in tensors.items()}, max_batch=1)
+    toks = [int(v) for v in g["prompt"]]
+    for pos, tk in enumerate(toks[:-1]):
+        eng.decode([tk], [pos])
+    logits, amax = eng.decode([toks[-1]], [len(toks) - 1])
+    assert np.abs(logits[0] - g["logits"][0]).max() <= tol(spec0)
+    assert int(amax[0]) == int(g["greedy"][0])
+    eng.close()
+
+
 def test_device_resident_step_and_graph_replay_are_deterministic(engine_mod):
     spec = mg.MODEL_CASES["llama_q4_0"]
     t = synth.build_model(spec)
