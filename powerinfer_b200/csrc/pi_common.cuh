@@ -170,6 +170,7 @@ struct AxpyArgs {
 };
 int axpy_groups(int wtype, int64_t ncols, int T);                     // row groups the launcher will use
 int launch_axpy(const AxpyArgs & a, cudaStream_t st, int * groups_used = nullptr);   // groups_used: partial vectors written
+int launch_axpy_mma(const AxpyArgs & a, cudaStream_t st, int * groups_used);         // FP16, 2..32 tokens; PI_ERR_UNSUPPORTED: not eligible
 // h F32 [T, stride] -> Q8_0 over 32-neuron blocks: cq int8 [T, stride], cd float [T, stride/32]
 int launch_neuron_q8(const float * h, int64_t stride, int64_t n, int T, int8_t * cq, float * cd, cudaStream_t st);
 

@@ -556,6 +556,11 @@ int launch_axpy(const AxpyArgs & a, cudaStream_t st, int * groups_used) {
     if (a.T <= 0) return PI_OK;
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
     if (groups_used) *groups_used = a.n_groups;
+    if (a.T > 1 && !q4 && a.status) {                               // FP16 rows, 2..32 tokens: tensor-core kernel
+        const int rc = launch_axpy_mma(a, st, groups_used);
+        if (rc != PI_ERR_UNSUPPORTED) return rc;
+        if (groups_used) *groups_used = a.n_groups;
+    }
     if (a.T == 1 && a.status) {
         const PipePlan pl = pipe_plan(a.wtype, a.nrows, a.ncols);
         if (pl.ok && pl.groups <= a.n_groups) {
