@@ -266,6 +266,11 @@ int  pi_engine_decode_host(pi_engine * e, const int32_t * host_tokens, const int
 #define PI_STAGE_OTHER    10
 #define PI_N_STAGES       11
 int  pi_engine_profile_step(pi_engine * e, int T, float * host_ms, int * host_launches, void * stream);
+/* Measurement helper: the kernels of ONE stage for every layer, back to back in a CUDA graph exactly as they are launched
+ * inside a step (programmatic dependent launch included), `reps` replays between two events.  host_ms_per_rep = time of
+ * one replay, host_launches = kernels in it.  The stage's outputs are overwritten with values computed from stale
+ * inputs: run a real step afterwards before using results.  Synchronises `stream`. */
+int  pi_engine_time_stage(pi_engine * e, int T, int stage, int reps, float * host_ms_per_rep, int * host_launches, void * stream);
 
 /* Device status word: 0, or PI_ERR_TIMEOUT after an exchange wait ran out.  Synchronises `stream`. */
 int  pi_engine_status(pi_engine * e, void * stream);

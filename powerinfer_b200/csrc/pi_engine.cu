@@ -416,7 +416,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
     e->pf_used = 0; e->pf_forked = false;
     int rc_pf = PI_OK;
 
-    {
+    if (!(e->skip_mask & (1u << PI_STAGE_OTHER))) {
         const dim3 grid((unsigned)((d + 255) / 256), T);
         if (tm.begin()) return PI_ERR_CUDA;
         k_embed<<<grid, 256, 0, st>>>((const __half *)e->g.tok_embd, (const __half *)e->g.pos_embd, e->tokens, e->pos,
@@ -447,11 +447,13 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             g.wtype = out_t; g.W = e->g.output ? e->g.output : e->g.tok_embd; g.nrows = c.n_vocab; g.ncols = d;
             g.x = n1.act.view(); g.T = T; g.dst = e->logits; g.dst_stride = c.n_vocab;
             STAGE(PI_STAGE_LM_HEAD, (T + 7) / 8, launch_gemv(g, st));
-            if (tm.begin()) return PI_ERR_CUDA;
-            k_argmax<<<T, 1024, 0, st>>>(e->logits, c.n_vocab, e->argmax);
-            PI_LAUNCH_CHECK("k_argmax");
-            if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA;
-            e->launches++;
+            if (!(e->skip_mask & (1u << PI_STAGE_OTHER))) {
+                if (tm.begin()) return PI_ERR_CUDA;
+                k_argmax<<<T, 1024, 0, st>>>(e->logits, c.n_vocab, e->argmax);
+                PI_LAUNCH_CHECK("k_argmax");
+                if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA;
+                e->launches++;
+            }
             break;
         }
         ActBuf qkv_in = e->act_q;
@@ -839,6 +841,43 @@ int pi_engine_profile_step(pi_engine * e, int T, float * host_ms, int * host_lau
     if (rc) { cudaStreamSynchronize(st); return rc; }
     if (host_launches) *host_launches = e->launches;
     return tm.collect(host_ms);
+}
+
+int pi_engine_time_stage(pi_engine * e, int T, int stage, int reps, float * host_ms_per_rep, int * host_launches, void * stream) {
+    int rc = check_T(e, T);
+    if (rc) return rc;
+    PI_REQUIRE(host_ms_per_rep && stage >= 0 && stage < PI_N_STAGES && reps > 0, "engine_time_stage: bad arguments");
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned saved = e->skip_mask;
+    e->skip_mask = ~(1u << stage) & ((1u << PI_N_STAGES) - 1u);
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    StageTimer tm;
+    cudaError_t ce = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+    if (ce == cudaSuccess) {
+        rc = enqueue_step(e, T, st, tm);
+        ce = cudaStreamEndCapture(st, &graph);
+    }
+    e->skip_mask = saved;
+    if (host_launches) *host_launches = e->launches;
+    if (rc == PI_OK && ce == cudaSuccess) ce = cudaGraphInstantiate(&exec, graph, 0);
+    if (rc == PI_OK && ce == cudaSuccess) ce = cudaEventCreate(&ev0);
+    if (rc == PI_OK && ce == cudaSuccess) ce = cudaEventCreate(&ev1);
+    if (rc == PI_OK && ce == cudaSuccess) ce = cudaGraphLaunch(exec, st);                    // warm
+    if (rc == PI_OK && ce == cudaSuccess) ce = cudaEventRecord(ev0, st);
+    for (int i = 0; i < reps && rc == PI_OK && ce == cudaSuccess; i++) ce = cudaGraphLaunch(exec, st);
+    if (rc == PI_OK && ce == cudaSuccess) ce = cudaEventRecord(ev1, st);
+    if (rc == PI_OK && ce == cudaSuccess) ce = cudaStreamSynchronize(st);
+    float ms = 0.f;
+    if (rc == PI_OK && ce == cudaSuccess) ce = cudaEventElapsedTime(&ms, ev0, ev1);
+    *host_ms_per_rep = ms / (float)reps;
+    if (ev0) cudaEventDestroy(ev0);
+    if (ev1) cudaEventDestroy(ev1);
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+    if (rc) return rc;
+    return ce == cudaSuccess ? PI_OK : cuda_fail(ce, "engine_time_stage");
 }
 
 int pi_engine_status(pi_engine * e, void * stream) {

@@ -68,13 +68,14 @@ for _name, _res, _args in [
     ("pi_ipc_export", C.c_int, [_vp, _vp]),
     ("pi_ipc_import", C.c_int, [_vp, C.POINTER(_vp)]),
     ("pi_ipc_close", C.c_int, [_vp]),
+    ("pi_engine_time_stage", C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int), _vp]),
 ]:
     _fn = getattr(lib, _name)
     _fn.restype, _fn.argtypes = _res, _args
 
 ENGINE_EXPORTS = ["pi_engine_workspace_bytes", "pi_engine_kv_bytes", "pi_engine_create", "pi_engine_destroy",
                   "pi_engine_set_exchange", "pi_engine_io", "pi_engine_decode", "pi_engine_advance", "pi_engine_decode_host",
-                  "pi_engine_profile_step", "pi_engine_status", "pi_engine_debug", "pi_engine_launches", "pi_engine_set_trace", "pi_engine_active_total",
+                  "pi_engine_profile_step", "pi_engine_time_stage", "pi_engine_status", "pi_engine_debug", "pi_engine_launches", "pi_engine_set_trace", "pi_engine_active_total",
                   "pi_device_malloc", "pi_device_free", "pi_ipc_export", "pi_ipc_import", "pi_ipc_close"]
 
 
@@ -217,6 +218,12 @@ class DecodeEngine:
         launches = C.c_int(0)
         check(lib.pi_engine_profile_step(self.handle, T, ms, C.byref(launches), self.st))
         return {STAGE_NAMES[i]: ms[i] for i in range(N_STAGES)}, launches.value
+
+    def time_stage(self, T: int, stage: str, reps: int = 5):
+        """(ms per launch, launches per replay) of one stage's kernels over all layers, back to back in a graph."""
+        ms, launches = C.c_float(0), C.c_int(0)
+        check(lib.pi_engine_time_stage(self.handle, T, STAGE_NAMES.index(stage), reps, C.byref(ms), C.byref(launches), self.st))
+        return ms.value / max(1, launches.value), launches.value
 
     def active_total(self, reset: bool = True) -> int:
         v = C.c_uint64(0)
