@@ -3,6 +3,8 @@
 // keep the residual stream on the device and to hand the next mat-vec its input already in FP16 / Q8_0 form.
 #include "pi_common.cuh"
 
+#include <cstdlib>
+
 namespace pi {
 
 static constexpr int QK = 32;
@@ -245,6 +247,111 @@ __global__ void __launch_bounds__(MAXT) k_norm(const NormP p) {
     PI_TL_MARK(2);
 }
 
+// The same norm spread over a thread-block cluster: one SM moves the ~170 KB a norm of 8192 values touches (input,
+// residual, weights, new residual stream, activation planes) in ~3 us, eight SMs in a fraction of that.  CTA `rank` of the
+// cluster owns a contiguous slice of n / cluster_size values (a multiple of 256: whole Q8_0 blocks, whole warps); the
+// partial sums are exchanged through distributed shared memory and added in rank order, so the result does not depend on
+// timing.  Same order of additions and roundings per element as k_norm.
+__device__ __forceinline__ unsigned cluster_rank()  { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned cluster_size()  { unsigned r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ double cluster_read_f64(const double * local, unsigned rank) {
+    unsigned la = (unsigned)__cvta_generic_to_shared(local), ra;
+    double v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(rank));
+    asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(ra) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
+    __shared__ double s_red[32];
+    __shared__ double s_part[2];
+    const unsigned rank = cluster_rank(), CS = cluster_size();
+    const int t = blockIdx.x / CS;
+    const int64_t n = p.n;
+    const int64_t c = (int64_t)rank * (n / CS) + (int64_t)threadIdx.x * 8;      // every thread owns 8 values: blockDim = n / CS / 8
+    const size_t o = (size_t)t * n + c;
+    pdl_launch();
+    if ((threadIdx.x & 3) == 0) {
+        if (p.w) asm volatile("prefetch.global.L2 [%0];" :: "l"(p.w + c));
+        if (p.b) asm volatile("prefetch.global.L2 [%0];" :: "l"(p.b + c));
+        if (p.in_bias) asm volatile("prefetch.global.L2 [%0];" :: "l"(p.in_bias + c));
+    }
+    pdl_wait();
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 x0 = *reinterpret_cast<const float4 *>(p.x + o), x1 = *reinterpret_cast<const float4 *>(p.x + o + 4);
+    float4 r0 = z4, r1 = z4;
+    if (p.residual) { r0 = *reinterpret_cast<const float4 *>(p.residual + o); r1 = *reinterpret_cast<const float4 *>(p.residual + o + 4); }
+    float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    auto add8 = [&](const float4 a, const float4 b) {
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+    };
+    if (p.in_bias) add8(*reinterpret_cast<const float4 *>(p.in_bias + c), *reinterpret_cast<const float4 *>(p.in_bias + c + 4));
+    if (p.residual) add8(r0, r1);
+    if (p.residual2) add8(*reinterpret_cast<const float4 *>(p.residual2 + o), *reinterpret_cast<const float4 *>(p.residual2 + o + 4));
+    float wv[8], bv[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) { wv[j] = 1.f; bv[j] = 0.f; }
+    if (p.w) {
+        const float4 a = *reinterpret_cast<const float4 *>(p.w + c), b = *reinterpret_cast<const float4 *>(p.w + c + 4);
+        wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+    }
+    if (p.b) {
+        const float4 a = *reinterpret_cast<const float4 *>(p.b + c), b = *reinterpret_cast<const float4 *>(p.b + c + 4);
+        bv[0] = a.x; bv[1] = a.y; bv[2] = a.z; bv[3] = a.w; bv[4] = b.x; bv[5] = b.y; bv[6] = b.z; bv[7] = b.w;
+    }
+    if (p.x_out) {
+        *reinterpret_cast<float4 *>(p.x_out + o)     = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(p.x_out + o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    if (p.act2_type && p.act2_src == 0) emit_act8(p.act2_type, p.act2, t, n, (int)(c / 8), v, true);
+
+    auto cluster_total = [&](double mine, int slot) {               // every CTA gets the sum over the cluster, ranks in order
+        mine = block_sum_d(mine, s_red);
+        if (threadIdx.x == 0) s_part[slot] = mine;
+        cluster_sync();
+        double tot = 0.0;
+        for (unsigned r = 0; r < CS; r++) tot += cluster_read_f64(&s_part[slot], r);
+        return tot;
+    };
+    float scale;
+    if (p.rms) {
+        double s = 0.0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) s += (double)(v[j] * v[j]);
+        const float ms = (float)(cluster_total(s, 0) / (double)n);
+        scale = 1.0f / sqrtf(ms + p.eps);
+    } else {
+        double s = 0.0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) s += (double)v[j];
+        const float mean = (float)(cluster_total(s, 0) / (double)n);
+        double s2 = 0.0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) { v[j] = v[j] - mean; s2 += (double)(v[j] * v[j]); }
+        const float var = (float)(cluster_total(s2, 1) / (double)n);
+        scale = 1.0f / sqrtf(var + p.eps);
+    }
+    float y[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        float r = __fmul_rn(v[j], scale);                              // separate roundings, as separate graph nodes give
+        if (p.w) r = __fmul_rn(r, wv[j]);
+        if (p.b) r = __fadd_rn(r, bv[j]);
+        y[j] = r;
+    }
+    if (p.y) {
+        float * out = p.y + (size_t)t * n + c;
+        *reinterpret_cast<float4 *>(out)     = make_float4(y[0], y[1], y[2], y[3]);
+        *reinterpret_cast<float4 *>(out + 4) = make_float4(y[4], y[5], y[6], y[7]);
+    }
+    if (p.act_type) emit_act8(p.act_type, p.act, t, n, (int)(c / 8), y, true);
+    if (p.act2_type && p.act2_src == 1) emit_act8(p.act2_type, p.act2, t, n, (int)(c / 8), y, true);
+    cluster_sync();                                                  // nobody leaves while a peer may still read its partial sums
+}
+
 // One CTA per SM, every thread issues bulk L2 prefetches for its pieces: no shared memory and few registers, so the
 // CTAs fit beside whatever the main chain has resident.
 __global__ void __launch_bounds__(128) k_prefetch(const Prefetch pf) {
@@ -266,6 +373,24 @@ int launch_norm(const NormArgs & a, cudaStream_t st) {
     p.partial = a.partial; p.n_groups = a.n_groups; p.T = a.T; p.residual = a.residual; p.residual2 = a.residual2; p.in_bias = a.in_bias; p.x_out = a.x_out;
     p.partial_stride = a.partial_stride; p.wait_flags = a.wait_flags; p.wait_epoch = a.wait_epoch; p.status = a.status;
     p.y = a.y; p.act_type = a.act_type; p.act = a.act; p.act2_type = a.act2_type; p.act2 = a.act2; p.act2_src = a.act2_src;
+    static int use_cluster = -1;
+    if (use_cluster < 0) { const char * v = getenv("PI_NORM_CLUSTER"); use_cluster = !(v && v[0] == '0'); }
+    if (use_cluster && !a.partial && !a.wait_flags && a.x) {
+        int cs = 0;
+        for (int k = 8; k >= 2; k /= 2) if (a.n % (k * 256) == 0 && a.n / k / 8 <= 256) { cs = k; break; }
+        if (cs) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(a.T * cs); cfg.blockDim = dim3((unsigned)(a.n / cs / 8)); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+            cudaLaunchAttribute attr[2];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = cs; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr; cfg.numAttrs = a.pdl ? 2 : 1;
+            PI_CUDA(cudaLaunchKernelEx(&cfg, k_norm_cluster, p));
+            return PI_OK;
+        }
+    }
     int threads = (int)((a.n / 8 + NORM_CHUNKS - 1) / NORM_CHUNKS);
     threads = min(1024, max(32, (threads + 31) / 32 * 32));
     if (threads <= 512) PI_CUDA(launch_k(k_norm<512>, dim3(a.T), dim3(threads), 0, st, a.pdl, p));
