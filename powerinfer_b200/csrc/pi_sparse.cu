@@ -556,7 +556,7 @@ int launch_axpy(const AxpyArgs & a, cudaStream_t st, int * groups_used) {
     if (a.T <= 0) return PI_OK;
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
     if (groups_used) *groups_used = a.n_groups;
-    if (a.T > 1 && !q4 && a.status) {                               // FP16 rows, 2..32 tokens: tensor-core kernel
+    if (a.T > 1 && a.status) {                                      // 2..32 tokens: tensor-core kernels
         const int rc = launch_axpy_mma(a, st, groups_used);
         if (rc != PI_ERR_UNSUPPORTED) return rc;
         if (groups_used) *groups_used = a.n_groups;

@@ -180,38 +180,41 @@ def test_hot_rows_from_placement_match_the_cpu_split(ops, oracle, wtype):
     assert np.abs((hot + cold) - full).max() <= 2e-3              # Q4_0 coefficients are per 32-neuron block: whole blocks keep them equal
 
 
+@pytest.mark.parametrize("wtype", [synth.F16, synth.Q4_0])
 @pytest.mark.parametrize("T", [2, 8, 13, 32])
-def test_fp16_small_batch_tensor_core_kernels_vs_oracle(ops, oracle, T):
-    """Shapes that take the tensor-core paths (FP16 rows, 2..32 tokens, 1024-column slices): ggml_mul_mat_idx, ggml_axpy and
-    the one-call FFN against the CPU operators, full and bucketed."""
-    rng = np.random.default_rng(900 + T)
+def test_small_batch_tensor_core_kernels_vs_oracle(ops, oracle, wtype, T):
+    """Shapes that take the tensor-core paths (2..32 tokens, 1024-column slices): ggml_mul_mat_idx (FP16 rows), ggml_axpy
+    (FP16 and Q4_0 rows) and the one-call FFN against the CPU operators, full and bucketed.  The Q4_0 axpy rounds the
+    dequantised weight and the coefficient to FP16 once each (the CPU multiplies (q-8)*b8 as integers): 1e-3 there."""
+    rng = np.random.default_rng(900 + T + wtype)
     d, F = 2048, 1536
+    q4 = wtype == synth.Q4_0
+    atol_axpy = 1e-3 if q4 else ATOL
     x = rng.standard_normal((T, d), dtype=np.float32)
-    W = (rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.02)).astype(np.float16)
-    Wg = (rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.02)).astype(np.float16)
-    Wt = (rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.02)).astype(np.float16)
+    mk = lambda: rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.02)
+    W, Wg, Wt = ((synth.quantize_q4_0(m) if q4 else m.astype(np.float16)) for m in (mk(), mk(), mk()))
     idx = (rng.random((T, F)) - 0.8).astype(np.float32)
     zeros = np.zeros(F, np.int32)
-    Wd, Wgd, Wtd = (ops.upload_weight(m, synth.F16, F, d) for m in (W, Wg, Wt))
-    ref_up = oracle.mul_mat_idx(synth.F16, W, F, d, x, idx, zeros)
+    Wd, Wgd, Wtd = (ops.upload_weight(m, wtype, F, d) for m in (W, Wg, Wt))
+    ref_up = oracle.mul_mat_idx(wtype, W, F, d, x, idx, zeros)
     up = ops.ggml_mul_mat_idx(Wd, dev(x), dev(idx)).cpu().numpy()
     assert np.abs(up - ref_up).max() <= ATOL
     h = np.maximum(ref_up, 0)
-    ref_down = oracle.axpy(synth.F16, Wt, F, d, h, idx, zeros)
+    ref_down = oracle.axpy(wtype, Wt, F, d, h, idx, zeros)
     down = ops.ggml_axpy(Wtd, dev(h), dev(idx)).cpu().numpy()
-    assert np.abs(down - ref_down).max() <= ATOL, np.abs(down - ref_down).max()
+    assert np.abs(down - ref_down).max() <= atol_axpy, np.abs(down - ref_down).max()
     assert np.array_equal(down, ops.ggml_axpy(Wtd, dev(h), dev(idx)).cpu().numpy())
-    ref_gate = oracle.mul_mat_idx(synth.F16, Wg, F, d, x, idx, zeros)
-    ref_ffn = oracle.axpy(synth.F16, Wt, F, d, np.maximum(ref_gate, 0) * ref_up, idx, zeros)
+    ref_gate = oracle.mul_mat_idx(wtype, Wg, F, d, x, idx, zeros)
+    ref_ffn = oracle.axpy(wtype, Wt, F, d, np.maximum(ref_gate, 0) * ref_up, idx, zeros)
     ffn = ops.sparse_ffn(Wd, Wgd, Wtd, dev(x), dev(idx)).cpu().numpy()
-    assert np.abs(ffn - ref_ffn).max() <= 5 * ATOL
+    assert np.abs(ffn - ref_ffn).max() <= 5 * atol_axpy
     blocks = np.arange(0, F // 32, 3)
     bucket = (blocks[:, None] * 32 + np.arange(32)[None, :]).reshape(-1).astype(np.int32)
     gpu_idx = np.ones(F, np.int32)
     gpu_idx[bucket] = 0
-    Wtb = ops.upload_weight(Wt[bucket], synth.F16, len(bucket), d)
+    Wtb = ops.upload_weight(Wt[bucket], wtype, len(bucket), d)
     down_b = ops.ggml_axpy(Wtb, dev(h), dev(idx), dev(bucket)).cpu().numpy()
-    assert np.abs(down_b - oracle.axpy(synth.F16, Wt, F, d, h, idx, gpu_idx)).max() <= ATOL
+    assert np.abs(down_b - oracle.axpy(wtype, Wt, F, d, h, idx, gpu_idx)).max() <= atol_axpy
 
 
 def test_predictor_and_active_list(ops, oracle):
