@@ -281,13 +281,52 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
     }
     pdl_wait();
     const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 x0 = *reinterpret_cast<const float4 *>(p.x + o), x1 = *reinterpret_cast<const float4 *>(p.x + o + 4);
     float4 r0 = z4, r1 = z4;
     if (p.residual) { r0 = *reinterpret_cast<const float4 *>(p.residual + o); r1 = *reinterpret_cast<const float4 *>(p.residual + o + 4); }
-    float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     auto add8 = [&](const float4 a, const float4 b) {
         v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
     };
+    if (p.partial) {
+        // the vector is the sum of n_groups slots (the ranks' mailbox slots when wait_flags is given: every CTA of the
+        // cluster waits, bounded, for all flags, then adds its slice of the slots in rank order)
+        const size_t tn = p.partial_stride ? (size_t)p.partial_stride : (size_t)p.T * n;
+        const float * partial = p.partial;
+        if (p.wait_flags) {
+            const unsigned int epoch = *p.wait_epoch;
+            const unsigned int par = epoch & 1u;
+            if (threadIdx.x < (unsigned)p.n_groups) {
+                const volatile unsigned int * f = p.wait_flags + par * p.n_groups + threadIdx.x;
+                const long long t0 = clock64();
+                bool ok_flag = false;
+                for (;;) {
+                    unsigned int seen;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f));
+                    if ((int)(seen - epoch) >= 0) { ok_flag = true; break; }
+                    if (clock64() - t0 > 2000000000LL) break;          // about a second
+                    __nanosleep(64);
+                }
+                if (!ok_flag) atomicOr(p.status, 1u);
+            }
+            __syncthreads();
+            partial += (size_t)par * p.n_groups * tn;
+        }
+        float4 a[8], b[8];                                             // all slots in flight at once (n_groups <= 8 per pass)
+        for (int g0 = 0; g0 < p.n_groups; g0 += 8) {
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                a[u] = z4; b[u] = z4;
+                if (g0 + u < p.n_groups) {
+                    a[u] = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)(g0 + u) * tn + o));
+                    b[u] = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)(g0 + u) * tn + o + 4));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) add8(a[u], b[u]);
+        }
+    } else {
+        add8(*reinterpret_cast<const float4 *>(p.x + o), *reinterpret_cast<const float4 *>(p.x + o + 4));
+    }
     if (p.in_bias) add8(*reinterpret_cast<const float4 *>(p.in_bias + c), *reinterpret_cast<const float4 *>(p.in_bias + c + 4));
     if (p.residual) add8(r0, r1);
     if (p.residual2) add8(*reinterpret_cast<const float4 *>(p.residual2 + o), *reinterpret_cast<const float4 *>(p.residual2 + o + 4));
@@ -375,7 +414,7 @@ int launch_norm(const NormArgs & a, cudaStream_t st) {
     p.y = a.y; p.act_type = a.act_type; p.act = a.act; p.act2_type = a.act2_type; p.act2 = a.act2; p.act2_src = a.act2_src;
     static int use_cluster = -1;
     if (use_cluster < 0) { const char * v = getenv("PI_NORM_CLUSTER"); use_cluster = !(v && v[0] == '0'); }
-    if (use_cluster && !a.partial && !a.wait_flags && a.x) {
+    if (use_cluster && (a.x || a.partial)) {
         int cs = 0;
         for (int k = 8; k >= 2; k /= 2) if (a.n % (k * 256) == 0 && a.n / k / 8 <= 256) { cs = k; break; }
         if (cs) {
