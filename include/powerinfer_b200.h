@@ -74,7 +74,8 @@ int pi_quantize_q8_0(const float * x, void * q8_ggml, int64_t nrows, int64_t nco
  *   x      F32 [T, ncols]
  *   idx    F32 [T, idx_stride]  predictor logits, indexed by GLOBAL neuron id
  *   bucket NULL, or int32 [n_w_rows] sorted global ids of the local rows (gpu_bucket, llama.cpp:2943-2967)
- *   dst    F32 [T, n_dst_rows]  dst[t, g] = idx[t, g] >= threshold ? W[r,:] . x[t,:] : 0 with g = bucket ? bucket[r] : r;
+ *   dst    F32 [T, n_dst_rows]  dst[t, g] = idx[t, g] < threshold ? 0 : W[r,:] . x[t,:] with g = bucket ? bucket[r] : r (the reference's
+ *          test, ggml.c:14256: a NaN logit therefore counts as active);
  *          rows no local row maps to are written 0.
  * Activations are rounded as the CPU path does before the dot product: to FP16 for F16 weights, to Q8_0 for Q4_0. */
 int pi_mul_mat_idx(int wtype, const void * W, int64_t n_w_rows, int64_t ncols,
@@ -87,7 +88,7 @@ int pi_mul_mat_idx(int wtype, const void * W, int64_t n_w_rows, int64_t ncols,
  * dispatch 8805-8814).
  *   Wt     [n_w_rows, ncols] : rows of ffn_down_t held on this device (one row per neuron)
  *   h      F32 [T, h_stride]   FFN hidden activations, indexed by global neuron id
- *   dst    F32 [T, ncols]      dst[t,:] = sum over local rows r with idx[t,g] >= threshold of coef(h[t,g]) * Wt[r,:]
+ *   dst    F32 [T, ncols]      dst[t,:] = sum over local rows r with !(idx[t,g] < threshold) of coef(h[t,g]) * Wt[r,:]
  * coef() is the CPU path's: h rounded to FP16 (F16 weights), or Q8_0 over blocks of 32 consecutive neurons (Q4_0
  * weights; then h_stride % 32 == 0 and a bucket must hold whole 32-neuron blocks).  The sum runs in a fixed order
  * (no atomics): two calls give identical bits. */

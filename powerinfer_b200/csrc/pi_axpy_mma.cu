@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(AM_THREADS) k_axpy_mma(const AxpyMmaP p) {
         float c = 0.f;
         if (i < n_mine && t < p.T) {
             const int64_t g = p.bucket ? p.bucket[rows[i]] : rows[i];
-            if (p.idx[(size_t)t * p.idx_stride + g] >= p.threshold) c = p.h[(size_t)t * p.h_stride + g];
+            if (!(p.idx[(size_t)t * p.idx_stride + g] < p.threshold)) c = p.h[(size_t)t * p.h_stride + g];
         }
         coef[e] = __float2half_rn(c);
     }
@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(AM_THREADS) k_axpy_mma_q4(const AxpyMmaQ4P p) 
         float c = 0.f;
         if (i < n_mine && t < p.T) {
             const int64_t g = p.bucket ? p.bucket[rows[i]] : rows[i];
-            if (p.idx[(size_t)t * p.idx_stride + g] >= p.threshold)
+            if (!(p.idx[(size_t)t * p.idx_stride + g] < p.threshold))
                 c = (float)p.cq[(size_t)t * p.c_stride + g] * p.cd[(size_t)t * (p.c_stride / 32) + g / 32];
         }
         coef[e] = __float2half_rn(c);

@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_gemv(const GemvP p) {
                     for (int t = 0; t < TT; t++) if (lane == t) { v = acc[k][t]; if (GATED) v2 = acc[PAIR + k][t]; }
                     const int t = lane;
                     bool active = true;
-                    if (SPARSE) active = p.idx[(size_t)t * p.idx_stride + g] >= p.threshold;
+                    if (SPARSE) active = !(p.idx[(size_t)t * p.idx_stride + g] < p.threshold);
                     float o = active ? v : 0.f;
                     if (GATED) o = active ? fmaxf(v2, 0.f) * v : 0.f;
                     if (p.bias) o += p.bias[g];

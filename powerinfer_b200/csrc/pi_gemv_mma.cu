@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(MMA_THREADS) k_gemv_mma(const MmaP p) {
                 const int r = SPARSE ? rows[i * 16 + mrow] : (cta + i * G) * 16 + mrow;
                 const int64_t g = SPARSE && p.bucket ? p.bucket[r] : r;
                 bool active = true;
-                if (SPARSE) active = p.idx[(size_t)t * p.idx_stride + g] >= p.threshold;
+                if (SPARSE) active = !(p.idx[(size_t)t * p.idx_stride + g] < p.threshold);
                 float o = active ? v : 0.f;
                 if (GATED) {
                     const float v2 = sum[((1 * NT + nt) * 4 + reg) * 32 + fl];

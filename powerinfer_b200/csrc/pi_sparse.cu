@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(COMPACT_THREADS) k_compact(const CompactP p) {
             float fill = 0.f;
             if (p.zero_dst && p.fill_bias) { fill = p.fill_bias[g]; if (p.fill_relu) fill = fmaxf(fill, 0.f); }
             for (int t = 0; t < p.T; t++) {
-                const bool a = p.idx[(size_t)t * p.idx_stride + g] >= p.threshold;
+                const bool a = !(p.idx[(size_t)t * p.idx_stride + g] < p.threshold);   // the reference skips on `<`: a NaN logit counts as active
                 any |= a;
                 if (p.zero_dst && !a) p.zero_dst[(size_t)t * p.zero_stride + g] = fill;
             }
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(AXPY_F16_THREADS) k_axpy_f16(const AxpyP p) {
                     for (int t = 0; t < TT; t++) {
                         // the CPU path rounds h to FP16 and skips rows below the threshold (ggml.c:14422-14428)
                         const float hv = round_f16(p.h[(size_t)t * p.h_stride + g]);
-                        const bool on = p.idx[(size_t)t * p.idx_stride + g] >= p.threshold;
+                        const bool on = !(p.idx[(size_t)t * p.idx_stride + g] < p.threshold);
                         a[u][t] = on ? hv : 0.f;
                     }
                 }
@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(AXPY_Q4_THREADS) k_axpy_q4(const AxpyP p) {
                     const float d4 = __half2float(__ldg(reinterpret_cast<const __half *>(row + (size_t)p.nb * 16) + b));
 #pragma unroll
                     for (int t = 0; t < TT; t++) {
-                        const bool on = p.idx[(size_t)t * p.idx_stride + g] >= p.threshold;
+                        const bool on = !(p.idx[(size_t)t * p.idx_stride + g] < p.threshold);
                         const int b8 = p.cq[(size_t)t * p.c_stride + g];
                         const float d8 = p.cd[(size_t)t * (p.c_stride / QK) + g / QK];
                         s[u][t] = on ? (float)b8 * (d4 * d8) : 0.f;
@@ -400,7 +400,7 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
                 const int b8 = __shfl_sync(0xffffffffu, q, (int)(g[u] & 31));
                 c = (float)b8 * round_f16(amax / 127.0f);
             }
-            if (!ok[u] || !(pv[u] >= p.threshold)) c = 0.f;
+            if (!ok[u] || pv[u] < p.threshold) c = 0.f;
             if (lane == 0 && i < n_mine) coef[i] = c;
         }
     }

@@ -255,6 +255,55 @@ def test_active_list_edges(ops):
             assert np.array_equal(lst[:len(want)].cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("wtype", [synth.F16, synth.Q4_0])
+@pytest.mark.parametrize("T", [1, 5])
+def test_sparse_ops_edge_masks_and_threshold(ops, oracle, wtype, T):
+    """No neuron active, every neuron active, logits exactly at a non-zero threshold, NaN logits (active: the reference
+    skips a row when `logit < threshold`, which is false for NaN) and bad arguments rejected before any launch."""
+    rng = np.random.default_rng(40 + wtype + T)
+    d, F = 512, 1024
+    x = rng.standard_normal((T, d), dtype=np.float32)
+    mats = [rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.03) for _ in range(2)]
+    q = [synth.quantize_q4_0(m) if wtype == synth.Q4_0 else m.astype(np.float16) for m in mats]
+    W, Wt = (ops.upload_weight(m, wtype, F, d) for m in q)
+    zeros = np.zeros(F, np.int32)
+    base = rng.standard_normal((T, F)).astype(np.float32)
+    cases = {"none": np.full((T, F), -1.0, np.float32), "all": np.full((T, F), 2.0, np.float32)}
+    at = base.copy(); at[:, ::3] = 0.25                                   # exactly at the threshold: active (>=)
+    cases["at_threshold"] = at
+    nan = base.copy(); nan[:, ::5] = np.nan
+    cases["nan"] = nan
+    saved = ops.sparse_pred_threshold
+    try:
+        for name, idx in cases.items():
+            thr = 0.25 if name == "at_threshold" else 0.0
+            ops.sparse_pred_threshold = thr
+            ref_up = oracle.mul_mat_idx(wtype, q[0], F, d, x, idx, zeros, thr)
+            up = ops.ggml_mul_mat_idx(W, dev(x), dev(idx)).cpu().numpy()
+            assert np.abs(up - ref_up).max() <= ATOL, name
+            h = np.maximum(ref_up, 0)
+            ref_down = oracle.axpy(wtype, q[1], F, d, h, idx, zeros, thr)
+            down = ops.ggml_axpy(Wt, dev(h), dev(idx)).cpu().numpy()
+            assert np.abs(down - ref_down).max() <= ATOL, name
+            if name == "none":
+                assert not up.any() and not down.any()
+            if name == "nan":
+                assert up[:, ::5].any()                                   # computed, as on the CPU
+    finally:
+        ops.sparse_pred_threshold = saved
+    from powerinfer_b200 import _lib
+    xd, id_ = dev(x), dev(cases["all"])
+    out = torch.empty(T, F, dtype=torch.float32, device="cuda")
+    ws = torch.empty(1 << 22, dtype=torch.uint8, device="cuda")
+    # fewer destination rows than weight rows: rejected with a message, nothing launched
+    rc = _lib.lib.pi_mul_mat_idx(wtype, W.ptr, F, d, xd.data_ptr(), T, id_.data_ptr(), F, None, 0.0, out.data_ptr(), F - 32,
+                                 ws.data_ptr(), ws.numel(), None)
+    assert rc == 1 and b"n_w_rows" in _lib.lib.pi_last_error()
+    rc = _lib.lib.pi_mul_mat_idx(wtype, W.ptr, F, d, xd.data_ptr(), T, id_.data_ptr(), F, None, 0.0, out.data_ptr(), F,
+                                 ws.data_ptr(), 1024, None)
+    assert rc != 0 and b"workspace" in _lib.lib.pi_last_error()           # too small a workspace is an error, not a fault
+
+
 def test_norms_rope_bit_exact(ops, golden_ops):
     xs = np.random.default_rng(7).standard_normal((3, 512), dtype=np.float32)
     assert np.array_equal(ops.ggml_rms_norm(dev(xs), 1e-5).cpu().numpy(), golden_ops["rms_norm"])
