@@ -488,6 +488,113 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
     }
 }
 
+// Dense matrices whose stage holds at least one row per warp (R >= 8): every warp owns whole rows of the stage, so nothing
+// is exchanged between warps, and the stage is handed back through a second ("empty") mbarrier on which each warp arrives
+// when it is done: only warp 0, which refills the stage, waits for the others; the rest go straight on to the next stage.
+// Halving the stage size in the kernel above costs 1.7 ms per 70B-shape token: its per-stage block barrier, shared-memory
+// exchange of partial sums and result hand-off are a fixed cost comparable to the stage's streaming time.
+__device__ __forceinline__ void r_mbar_arrive(uint64_t * bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(r_smem_u32(bar)) : "memory");
+}
+
+template <int WT>
+__global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const int S = p.stages, R = p.R;
+    uint64_t * full = reinterpret_cast<uint64_t *>(smem);           // [S] at byte 0, [S] "empty" at byte 128 (S <= 8)
+    uint64_t * empty = reinterpret_cast<uint64_t *>(smem + 128);
+    const size_t x_bytes = WT == PI_TYPE_F16 ? (size_t)p.ncols * 2 : (size_t)p.nb * 40;
+    unsigned char * xs = smem + 256;
+    unsigned char * ring = xs + ((x_bytes + 127) & ~(size_t)127);
+
+    pdl_launch();
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) { r_mbar_init(full + s, 1); r_mbar_init(empty + s, RING_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    const int n_items = p.nrows;
+    const int total_stages = (n_items + R - 1) / R;
+    const int n_stages = cta < total_stages ? (total_stages - cta + G - 1) / G : 0;
+    auto stage_first = [&](int st) { return (cta + st * G) * R; };
+    auto issue = [&](int st) {                                       // lane 0 of warp 0
+        const int s = st % S, first = stage_first(st), n = min(R, n_items - first);
+        r_mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
+        r_bulk_g2s(ring + (size_t)s * p.stage_bytes, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
+    };
+    if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);   // weights need no producer: before the wait
+    pdl_wait();
+    if (WT == PI_TYPE_F16) {
+        const uint4 * src = reinterpret_cast<const uint4 *>(p.x.h16);
+        uint4 * dstx = reinterpret_cast<uint4 *>(xs);
+        for (int i = tid; i < p.ncols / 8; i += RING_THREADS) dstx[i] = src[i];
+    } else {
+        uint4 * lo = reinterpret_cast<uint4 *>(xs);
+        uint4 * hi = lo + p.nb;
+        uint2 * ds = reinterpret_cast<uint2 *>(hi + p.nb);
+        for (int i = tid; i < p.nb; i += RING_THREADS) {
+            lo[i] = p.x.lo[i]; hi[i] = p.x.hi[i];
+            ds[i] = make_uint2(__float_as_uint(p.x.d[i]), (unsigned)p.x.s[i]);
+        }
+    }
+    __syncthreads();
+
+    const int units = WT == PI_TYPE_F16 ? p.ncols / 8 : p.nb;
+    const int rpw = R / RING_WARPS;                                 // rows of a stage per warp (1, 2, 4 or 8), consecutive
+    bool dead = false;                                              // warp-uniform
+    auto store = [&](int r, float o) {
+        if (p.bias) o += p.bias[r];
+        if (p.relu) o = fmaxf(o, 0.f);
+        if (p.dst)   p.dst[r] = o;
+        if (p.dst16) p.dst16[r] = __float2half_rn(o);
+    };
+    for (int st = 0; st < n_stages; st++) {
+        const int s = st % S;
+        const unsigned parity = (unsigned)(st / S) & 1u;
+        if (!dead) {
+            int spins = 0;
+            bool gave_up = false;
+            while (!r_mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            dead = __any_sync(0xffffffffu, gave_up) != 0;
+            if (dead && lane == 0) atomicOr(p.status, 4u);
+        }
+        const unsigned char * base = ring + (size_t)s * p.stage_bytes;
+        const int first = stage_first(st);
+        const int n = min(R, n_items - first);
+        if (!dead) {
+            int k = warp * rpw;
+            const int k_end = min(k + rpw, n);
+            for (; k + 2 <= k_end; k += 2) {
+                float acc[2];
+                ring_dot_rows<WT, 2>(base + (size_t)k * p.row_bytes, (size_t)p.row_bytes, 0, units, p.nb, xs, lane, acc);
+                const float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
+                if (lane == 0) { store(first + k, v0); store(first + k + 1, v1); }
+            }
+            if (k < k_end) {
+                float acc[1];
+                ring_dot_rows<WT, 1>(base + (size_t)k * p.row_bytes, (size_t)p.row_bytes, 0, units, p.nb, xs, lane, acc);
+                const float v0 = warp_sum(acc[0]);
+                if (lane == 0) store(first + k, v0);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) r_mbar_arrive(empty + s);                     // this warp is done with stage s (also when it gave up)
+        if (warp == 0 && st + S < n_stages) {                        // refill: wait (bounded) until every warp has arrived
+            int spins = 0;
+            bool gave_up = false;
+            while (!r_mbar_try_wait(empty + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            if (gave_up) { if (lane == 0) atomicOr(p.status, 4u); }
+            else if (lane == 0 && !dead) issue(st + S);
+        }
+    }
+    if (__syncthreads_or(dead) && tid == 0) {                       // do not exit with copies still landing in shared memory
+        for (int s = 0; s < S; s++) { int spins = 0; while (!r_mbar_try_wait(full + s, 0) && !r_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+    }
+}
+
 struct RingPlan { bool ok; int R, split, rw, stages, ctas_per_sm; size_t stage_bytes, smem; int max_items; };
 
 // Two 100 KB rings per SM rather than one big one (PI_RING_CPS / PI_RING_KB override): with a single 8-warp CTA the
@@ -566,6 +673,24 @@ int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaSt
     p.bias = a.bias; p.relu = a.relu; p.dst = a.dst; p.dst16 = a.dst16; p.status = status; p.fin = a.fin; p.res_add = a.res_add; p.stats_out = a.stats_out;
     p.R = pl.R; p.split = pl.split; p.stages = pl.stages; p.max_items = pl.max_items; p.stage_bytes = pl.stage_bytes;
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
+    {
+        static int warp_rows = -1;
+        if (warp_rows < 0) { const char * v = getenv("PI_RING_W"); warp_rows = !(v && v[0] == '0'); }
+        if (warp_rows && !sparse && !a.fin.on && !a.res_add && !a.stats_out && pl.R >= RING_WARPS && pl.stages <= 8) {
+            static bool attr_w[2][16] = {{false}};
+            int dev = 0;
+            PI_CUDA(cudaGetDevice(&dev));
+            if (dev >= 0 && dev < 16 && !attr_w[q4][dev]) {
+                if (q4) PI_CUDA(cudaFuncSetAttribute(k_gemv_ring_w<PI_TYPE_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
+                else    PI_CUDA(cudaFuncSetAttribute(k_gemv_ring_w<PI_TYPE_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
+                attr_w[q4][dev] = true;
+            }
+            const dim3 grid(sm_count() * pl.ctas_per_sm);
+            if (q4) PI_CUDA(launch_k(k_gemv_ring_w<PI_TYPE_Q4_0>, grid, dim3(RING_THREADS), pl.smem, st, pdl, p));
+            else    PI_CUDA(launch_k(k_gemv_ring_w<PI_TYPE_F16>, grid, dim3(RING_THREADS), pl.smem, st, pdl, p));
+            return PI_OK;
+        }
+    }
 #define PI_RING_DISPATCH_RW(FUSED, RW)                                                                                                     \
     do {                                                                                                                                   \
         if (!sparse) return q4 ? launch_ring_inst<PI_TYPE_Q4_0, false, false, FUSED, RW>(p, pl, pdl, st)                                   \
