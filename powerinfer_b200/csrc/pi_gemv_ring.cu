@@ -595,7 +595,161 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
     }
 }
 
+// The same hand-off for stages of fewer than 8 vectors (the gather mat-vec with the gate rows riding along, matrices with
+// long rows): 8 / NV warps share a vector, each a column part, and only the warps working on ONE output row (its up and gate
+// vectors, all parts) meet, at a named barrier of their own, before one of them combines the sums; the stage goes back
+// through the "empty" mbarrier as above.
+template <int WT, bool SPARSE, bool GATED>
+__global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_g(const RingP p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ float s_grp[2][RING_WARPS][RING_WARPS];              // [stage parity][vector][column part]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const int S = p.stages, R = p.R;
+    constexpr int NM = GATED ? 2 : 1;
+    uint64_t * full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t * empty = reinterpret_cast<uint64_t *>(smem + 128);
+    int * items = reinterpret_cast<int *>(smem + 8 * 32);
+    const size_t x_bytes = WT == PI_TYPE_F16 ? (size_t)p.ncols * 2 : (size_t)p.nb * 40;
+    unsigned char * xs = smem + (((size_t)8 * 32 + (size_t)4 * p.max_items + 127) & ~(size_t)127);
+    unsigned char * ring = xs + ((x_bytes + 127) & ~(size_t)127);
+
+    pdl_launch();
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) { r_mbar_init(full + s, 1); r_mbar_init(empty + s, RING_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    int n_items, n_stages;
+    auto stage_first = [&](int st) { return (cta + st * G) * R; };
+    auto issue = [&](int st) {                                       // all lanes of warp 0
+        const int s = st % S, first = stage_first(st), n = min(R, n_items - first);
+        unsigned char * dstp = ring + (size_t)s * p.stage_bytes;
+        if (!SPARSE) {
+            if (lane == 0) {
+                r_mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
+                r_bulk_g2s(dstp, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
+            }
+        } else {
+            if (lane == 0) r_mbar_expect_tx(full + s, (unsigned)(n * NM * p.row_bytes));
+            for (int k = lane; k < n; k += 32) {
+                const int r = items[st * R + k];
+                r_bulk_g2s(dstp + (size_t)k * p.row_bytes, p.W + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
+                if (GATED) r_bulk_g2s(dstp + (size_t)(R + k) * p.row_bytes, p.W2 + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
+            }
+        }
+    };
+    if (!SPARSE) {
+        n_items = p.nrows;
+        const int total_stages = (n_items + R - 1) / R;
+        n_stages = cta < total_stages ? (total_stages - cta + G - 1) / G : 0;
+        if (warp == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
+    }
+    pdl_wait();
+    if (SPARSE) {
+        n_items = min(*p.count, p.nrows);
+        const int total_stages = (n_items + R - 1) / R;
+        n_stages = cta < total_stages ? (total_stages - cta + G - 1) / G : 0;
+        n_stages = min(n_stages, p.max_items / R);
+        for (int i = tid; i < n_stages * R; i += RING_THREADS) {
+            const int it = stage_first(i / R) + (i % R);
+            int r = it < n_items ? p.list[it] : 0;
+            items[i] = (unsigned)r < (unsigned)p.nrows ? r : 0;
+        }
+        __syncthreads();
+        if (warp == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
+    }
+    if (WT == PI_TYPE_F16) {
+        const uint4 * src = reinterpret_cast<const uint4 *>(p.x.h16);
+        uint4 * dstx = reinterpret_cast<uint4 *>(xs);
+        for (int i = tid; i < p.ncols / 8; i += RING_THREADS) dstx[i] = src[i];
+    } else {
+        uint4 * lo = reinterpret_cast<uint4 *>(xs);
+        uint4 * hi = lo + p.nb;
+        uint2 * ds = reinterpret_cast<uint2 *>(hi + p.nb);
+        for (int i = tid; i < p.nb; i += RING_THREADS) {
+            lo[i] = p.x.lo[i]; hi[i] = p.x.hi[i];
+            ds[i] = make_uint2(__float_as_uint(p.x.d[i]), (unsigned)p.x.s[i]);
+        }
+    }
+    __syncthreads();
+
+    const int units = WT == PI_TYPE_F16 ? p.ncols / 8 : p.nb;
+    const int NV = R * NM, wpv = RING_WARPS / NV;                   // warps per vector
+    const int vec = warp / wpv, part = warp % wpv, k = vec % R;     // my vector of the stage, my column part, its output row
+    const int per = units / wpv, gw = NM * wpv;                     // units per part, warps working on one output row
+    bool dead = false;                                              // warp-uniform
+    for (int st = 0; st < n_stages; st++) {
+        const int s = st % S;
+        const unsigned parity = (unsigned)(st / S) & 1u;
+        if (!dead) {
+            int spins = 0;
+            bool gave_up = false;
+            while (!r_mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            dead = __any_sync(0xffffffffu, gave_up) != 0;
+            if (dead && lane == 0) atomicOr(p.status, 4u);
+        }
+        const unsigned char * base = ring + (size_t)s * p.stage_bytes;
+        const int first = stage_first(st);
+        const int n = min(R, n_items - first);
+        float v = 0.f;
+        if (!dead && k < n) {
+            float acc[1];
+            ring_dot_rows<WT, 1>(base + (size_t)vec * p.row_bytes, (size_t)p.row_bytes, part * per, (part + 1) * per, p.nb, xs, lane, acc);
+            v = warp_sum(acc[0]);
+        }
+        if (gw > 1) {                                                // the warps of output row k meet; nobody else waits
+            if (lane == 0) s_grp[st & 1][vec][part] = v;
+            asm volatile("bar.sync %0, %1;" :: "r"(1 + k), "r"(gw * 32) : "memory");
+        }
+        if (vec < R && part == 0 && lane == 0 && k < n && !dead) {
+            float v2 = 0.f;
+            if (gw > 1) {
+                v = s_grp[st & 1][k][0];
+                for (int q = 1; q < wpv; q++) v += s_grp[st & 1][k][q];
+                if (GATED) { v2 = s_grp[st & 1][R + k][0]; for (int q = 1; q < wpv; q++) v2 += s_grp[st & 1][R + k][q]; }
+            }
+            const int r = SPARSE ? items[st * R + k] : first + k;
+            const int64_t g = SPARSE && p.bucket ? p.bucket[r] : r;
+            float o = v;                                             // batch 1: a listed row is an active row
+            if (GATED) o = fmaxf(v2, 0.f) * v;
+            if (p.bias) o += p.bias[g];
+            if (p.relu) o = fmaxf(o, 0.f);
+            if (p.dst)   p.dst[g] = o;
+            if (p.dst16) p.dst16[g] = __float2half_rn(o);
+        }
+        __syncwarp();
+        if (lane == 0) r_mbar_arrive(empty + s);
+        if (warp == 0 && st + S < n_stages) {
+            int spins = 0;
+            bool gave_up = false;
+            while (!r_mbar_try_wait(empty + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            if (gave_up) { if (lane == 0) atomicOr(p.status, 4u); }
+            else if (!dead) issue(st + S);
+        }
+    }
+    if (__syncthreads_or(dead) && tid == 0) {
+        for (int s = 0; s < S; s++) { int spins = 0; while (!r_mbar_try_wait(full + s, 0) && !r_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+    }
+}
+
 struct RingPlan { bool ok; int R, split, rw, stages, ctas_per_sm; size_t stage_bytes, smem; int max_items; };
+
+template <int WT, bool SPARSE, bool GATED>
+static int launch_ring_g(const RingP & p, const RingPlan & pl, bool pdl, cudaStream_t st) {
+    static bool attr_done[16] = {false};
+    int dev = 0;
+    PI_CUDA(cudaGetDevice(&dev));
+    auto kern = k_gemv_ring_g<WT, SPARSE, GATED>;
+    if (dev >= 0 && dev < 16 && !attr_done[dev]) {
+        PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
+        attr_done[dev] = true;
+    }
+    PI_CUDA(launch_k(kern, dim3(sm_count() * pl.ctas_per_sm), dim3(RING_THREADS), pl.smem, st, pdl, p));
+    return PI_OK;
+}
+
 
 // Two 100 KB rings per SM rather than one big one (PI_RING_CPS / PI_RING_KB override): with a single 8-warp CTA the
 // consumers are issue-latency bound, and what matters for bandwidth is ~200 KB of copies in flight per SM; four 54 KB rings
@@ -689,6 +843,18 @@ int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaSt
             if (q4) PI_CUDA(launch_k(k_gemv_ring_w<PI_TYPE_Q4_0>, grid, dim3(RING_THREADS), pl.smem, st, pdl, p));
             else    PI_CUDA(launch_k(k_gemv_ring_w<PI_TYPE_F16>, grid, dim3(RING_THREADS), pl.smem, st, pdl, p));
             return PI_OK;
+        }
+    }
+    {
+        static int grp = -1;
+        if (grp < 0) { const char * v = getenv("PI_RING_G"); grp = !(v && v[0] == '0'); }
+        const int nv = pl.R * (gated ? 2 : 1);
+        const int units = q4 ? (int)(a.ncols / QK) : (int)(a.ncols / 8);
+        if (grp && !a.fin.on && !a.res_add && !a.stats_out && pl.stages <= 8 && nv <= RING_WARPS && RING_WARPS % nv == 0 &&
+            units % (RING_WARPS / nv) == 0 && (sparse || pl.R < RING_WARPS)) {
+            if (!sparse) return q4 ? launch_ring_g<PI_TYPE_Q4_0, false, false>(p, pl, pdl, st) : launch_ring_g<PI_TYPE_F16, false, false>(p, pl, pdl, st);
+            if (gated)   return q4 ? launch_ring_g<PI_TYPE_Q4_0, true, true>(p, pl, pdl, st) : launch_ring_g<PI_TYPE_F16, true, true>(p, pl, pdl, st);
+            return q4 ? launch_ring_g<PI_TYPE_Q4_0, true, false>(p, pl, pdl, st) : launch_ring_g<PI_TYPE_F16, true, false>(p, pl, pdl, st);
         }
     }
 #define PI_RING_DISPATCH_RW(FUSED, RW)                                                                                                     \
