@@ -48,7 +48,7 @@ def measured_peaks():
 # `ncu --set full` capture of the 4-layer case of the same layer shape (profiles/step_kernels_*_ncu_full.md); traffic per
 # launch does not depend on the layer count.  Stages with two kernels give the mean over their launches.
 NCU_TRAFFIC = {
-    "relu-llama-70b-q4_0": {"predictor": (16.82e6 + 58.81e6) / 2, "qkv": 47.22e6, "out_proj": 37.78e6, "up_gate": 30.50e6,
+    "relu-llama-70b-q4_0": {"predictor": (16.82e6 + 58.78e6) / 2, "qkv": 47.22e6, "out_proj": 37.78e6, "up_gate": 30.50e6,
                             "down": (15.49e6 + 4.86e6) / 2},
 }
 
@@ -445,9 +445,9 @@ def main():
                        "GBps": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 3),
                        "serialised_ms_per_step": round(stage_ms[st], 4)}
         dom = max(ops, key=lambda k: ops[k]["ms_per_step"])
-        roofline = {"bound": "hbm", "kernel": {"qkv": "k_gemv_ring (dense, QKV rows)", "out_proj": "k_gemv_ring (dense, out-proj)",
-                                               "predictor": "k_gemv_ring (dense F16, fc1+fc2)", "up_gate": "k_gemv_ring (gather, up+gate)",
-                                               "down": "k_axpy_pipe + k_reduce_partials", "lm_head": "k_gemv_ring (dense, lm head)"}[dom],
+        roofline = {"bound": "hbm", "kernel": {"qkv": "k_gemv_ring_w (dense, QKV rows)", "out_proj": "k_gemv_ring_w (dense, out-proj)",
+                                               "predictor": "k_gemv_ring_g + k_gemv_ring_w (dense F16, fc1 + fc2)", "up_gate": "k_gemv_ring_g (gather, up+gate)",
+                                               "down": "k_axpy_pipe + k_reduce_partials", "lm_head": "k_gemv_ring_w (dense, lm head)"}[dom],
                     "achieved": ops[dom]["GBps"], "peak": peak, "unit": "GB/s", "frac": round(ops[dom]["GBps"] / peak, 3),
                     "peak_source": f"of {peak_kind}", "launches_per_step": ops[dom]["launches_per_step"],
                     "bytes_per_launch": bytes_tok[dom] / world / ops[dom]["launches_per_step"],
