@@ -648,13 +648,20 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_g(const RingP p) {
     }
     pdl_wait();
     if (SPARSE) {
+        // the list entry this thread would own is read together with the count, not after it (the list buffer has nrows
+        // entries whatever the count; entries beyond the count are stale and dropped below): one round trip, not two
+        int spec = 0;
+        {
+            const int it = stage_first(tid / R) + (tid % R);
+            if (tid < p.max_items && it < p.nrows) spec = p.list[it];
+        }
         n_items = min(*p.count, p.nrows);
         const int total_stages = (n_items + R - 1) / R;
         n_stages = cta < total_stages ? (total_stages - cta + G - 1) / G : 0;
         n_stages = min(n_stages, p.max_items / R);
         for (int i = tid; i < n_stages * R; i += RING_THREADS) {
             const int it = stage_first(i / R) + (i % R);
-            int r = it < n_items ? p.list[it] : 0;
+            int r = it < n_items ? (i == tid ? spec : p.list[it]) : 0;
             items[i] = (unsigned)r < (unsigned)p.nrows ? r : 0;
         }
         __syncthreads();

@@ -350,14 +350,18 @@ __global__ void __launch_bounds__(1024) k_axpy_pipe(const AxpyPipeP p) {
     }
     pdl_launch();
     pdl_wait();
+    // the list entry this thread would own is read together with the count, not after it (the list buffer has nrows
+    // entries whatever the count; what lies beyond the count is stale and is dropped below): one round trip, not two
+    int spec = -1;
+    if (tid < p.max_rows && cta + tid * G < p.nrows) spec = p.list[cta + tid * G];
     const int n = min(*p.count, p.nrows);
     int n_mine = cta < n ? (n - cta + G - 1) / G : 0;
     n_mine = min(n_mine, p.max_rows);
     const int n_stages = (n_mine + PIPE_RS - 1) / PIPE_RS;
 
-    // ---- prologue: my rows first (one round trip), start the copies, then the coefficients while the rows fly in
+    // ---- prologue: my rows first, start the copies, then the coefficients while the rows fly in
     for (int i = tid; i < n_mine; i += blockDim.x) {
-        const int r = p.list[cta + i * G];
+        const int r = i == tid ? spec : p.list[cta + i * G];
         rows[i] = (unsigned)r < (unsigned)p.nrows ? r : -1;
     }
     __syncthreads();
