@@ -116,6 +116,10 @@ int pi_mul_mat(int wtype, const void * W, int64_t nrows, int64_t ncols, const fl
     GemvArgs g;
     g.wtype = wtype; g.W = W; g.nrows = nrows; g.ncols = ncols; g.x = act.view(); g.T = T;
     g.bias = bias; g.dst = dst; g.dst_stride = nrows;
+    if (workspace_bytes >= act_bytes(wtype, ncols, T) + 256) {       // room for a status word: the bulk-copy ring kernels are eligible
+        g.status = (unsigned int *)p;
+        PI_CUDA(cudaMemsetAsync(g.status, 0, 4, st));
+    }
     return launch_gemv(g, st);
 }
 

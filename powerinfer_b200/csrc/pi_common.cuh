@@ -134,6 +134,7 @@ struct GemvArgs {
 int launch_gemv(const GemvArgs & a, cudaStream_t st);
 int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaStream_t st);   // PI_ERR_UNSUPPORTED: not eligible
 int launch_gemv_mma(const GemvArgs & a, cudaStream_t st);                                     // FP16 rows, T <= 32; PI_ERR_UNSUPPORTED: not eligible
+int launch_gemv_mma_q4(const GemvArgs & a, cudaStream_t st);                                  // Q4_0 rows, T >= 2; PI_ERR_UNSUPPORTED: not eligible
 
 // predictor logits -> compacted list of LOCAL rows active for >= 1 token; also writes zeros (or relu(bias)) into
 // h_init [T, h_stride] for rows that are inactive for a token when h_init != nullptr

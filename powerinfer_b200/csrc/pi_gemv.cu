@@ -304,6 +304,10 @@ int launch_gemv(const GemvArgs & a, cudaStream_t st) {
         const int rc = launch_gemv_mma(a, st);
         if (rc != PI_ERR_UNSUPPORTED) return rc;
     }
+    if (a.wtype == PI_TYPE_Q4_0 && a.status && a.T > 1) {          // Q4_0 rows, 2+ tokens: integer tensor-core ring kernel
+        const int rc = launch_gemv_mma_q4(a, st);
+        if (rc != PI_ERR_UNSUPPORTED) return rc;
+    }
     if (a.T == 1 && a.status) {
         const int rc = launch_gemv_ring(a, a.status, a.pdl, st);
         if (rc != PI_ERR_UNSUPPORTED) return rc;

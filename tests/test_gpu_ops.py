@@ -217,6 +217,48 @@ def test_small_batch_tensor_core_kernels_vs_oracle(ops, oracle, wtype, T):
     assert np.abs(down_b - oracle.axpy(wtype, Wt, F, d, h, idx, gpu_idx)).max() <= atol_axpy
 
 
+@pytest.mark.parametrize("T", [2, 5, 8, 11, 16])
+@pytest.mark.parametrize("d", [256, 1024, 2560])
+def test_q4_0_small_batch_integer_tensor_core_kernel_vs_oracle(ops, oracle, T, d):
+    """Q4_0 rows with 2+ tokens take the integer tensor-core kernel (tiles of 8 row vectors, launches of 8 tokens): dense
+    with a ragged last tile, ggml_mul_mat_idx over a ragged list, bucketed rows, and the gated pair inside the one-call
+    FFN, against the CPU operators.  The integer block dots are exact; only the FP32 order over the blocks differs."""
+    rng = np.random.default_rng(1300 + T + d)
+    F = 1190 + 8 * 3 + 5                                          # >= 148 tiles of 8, last tile ragged
+    x = rng.standard_normal((T, d), dtype=np.float32)
+    mk = lambda n: synth.quantize_q4_0(rng.standard_normal((n, d), dtype=np.float32) * np.float32(0.02))
+    W, Wg = mk(F), mk(F)
+    Wd, Wgd = ops.upload_weight(W, synth.Q4_0, F, d), ops.upload_weight(Wg, synth.Q4_0, F, d)
+    ref = oracle.mul_mat(synth.Q4_0, W, F, d, x)
+    out = ops.ggml_mul_mat(Wd, dev(x)).cpu().numpy()
+    assert np.abs(out - ref).max() <= ATOL, np.abs(out - ref).max()
+    idx = (rng.random((T, F)) - 0.7).astype(np.float32)
+    zeros = np.zeros(F, np.int32)
+    ref_up = oracle.mul_mat_idx(synth.Q4_0, W, F, d, x, idx, zeros)
+    up = ops.ggml_mul_mat_idx(Wd, dev(x), dev(idx)).cpu().numpy()
+    assert np.abs(up - ref_up).max() <= ATOL
+    assert np.array_equal(up == 0, ref_up == 0) or np.abs(up - ref_up).max() <= ATOL
+    bucket = np.sort(rng.choice(F, 333, replace=False)).astype(np.int32)
+    gpu_idx = np.ones(F, np.int32)
+    gpu_idx[bucket] = 0
+    Wb = ops.upload_weight(W[bucket], synth.Q4_0, len(bucket), d)
+    up_b = ops.ggml_mul_mat_idx(Wb, dev(x), dev(idx), dev(bucket), result_ne0=F).cpu().numpy()
+    assert np.abs(up_b - oracle.mul_mat_idx(synth.Q4_0, W, F, d, x, idx, gpu_idx)).max() <= ATOL
+    if d % 1024 == 0 or d == 256:
+        Fd = F // 32 * 32
+        Wt = mk(d)[:, :0]                                         # placeholder keeps the generator sequence simple
+        Wt = synth.quantize_q4_0(rng.standard_normal((Fd, d), dtype=np.float32) * np.float32(0.02))
+        Wtd = ops.upload_weight(Wt, synth.Q4_0, Fd, d)
+        Wd2, Wgd2 = ops.upload_weight(W[:Fd], synth.Q4_0, Fd, d), ops.upload_weight(Wg[:Fd], synth.Q4_0, Fd, d)
+        idx2 = np.ascontiguousarray(idx[:, :Fd])
+        z2 = np.zeros(Fd, np.int32)
+        r_up = oracle.mul_mat_idx(synth.Q4_0, W[:Fd], Fd, d, x, idx2, z2)
+        r_gate = oracle.mul_mat_idx(synth.Q4_0, Wg[:Fd], Fd, d, x, idx2, z2)
+        r_ffn = oracle.axpy(synth.Q4_0, Wt, Fd, d, np.maximum(r_gate, 0) * r_up, idx2, z2)
+        ffn = ops.sparse_ffn(Wd2, Wgd2, Wtd, dev(x), dev(idx2)).cpu().numpy()
+        assert np.abs(ffn - r_ffn).max() <= 5e-3, np.abs(ffn - r_ffn).max()
+
+
 def test_predictor_and_active_list(ops, oracle):
     spec = synth.ModelSpec(n_layer=1, d=512, n_ff=4096, rank=128, firing=0.1, seed=5)
     t = synth.build_model(spec)
