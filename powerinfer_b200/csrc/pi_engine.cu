@@ -766,6 +766,21 @@ int check_T(pi_engine * e, int T) {
     return PI_OK;
 }
 
+// kernel nodes of a captured step: the exact number of kernel launches one replay makes (the per-call estimates added
+// up in `launches` do not know which kernel a launcher picked for a batch)
+int count_kernel_nodes(cudaGraph_t graph) {
+    size_t n = 0;
+    if (cudaGraphGetNodes(graph, nullptr, &n) != cudaSuccess || n == 0) return 0;
+    std::vector<cudaGraphNode_t> nodes(n);
+    if (cudaGraphGetNodes(graph, nodes.data(), &n) != cudaSuccess) return 0;
+    int k = 0;
+    for (size_t i = 0; i < n; i++) {
+        cudaGraphNodeType ty;
+        if (cudaGraphNodeGetType(nodes[i], &ty) == cudaSuccess && ty == cudaGraphNodeTypeKernel) k++;
+    }
+    return k;
+}
+
 // first call for a batch size: one plain run (fills every per-kernel attribute cache), then capture
 int run_step(pi_engine * e, int T, cudaStream_t st) {
     StageTimer tm;
@@ -780,6 +795,7 @@ int run_step(pi_engine * e, int T, cudaStream_t st) {
     const cudaError_t ce = cudaStreamEndCapture(st, &graph);
     if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
     if (ce != cudaSuccess) return cuda_fail(ce, "cudaStreamEndCapture");
+    { const int k = count_kernel_nodes(graph); if (k > 0) e->launches = k; }
     cudaGraphExec_t exec = nullptr;
     const cudaError_t ci = cudaGraphInstantiate(&exec, graph, 0);
     cudaGraphDestroy(graph);
@@ -849,6 +865,7 @@ int pi_engine_time_stage(pi_engine * e, int T, int stage, int reps, float * host
     PI_REQUIRE(host_ms_per_rep && stage >= 0 && stage < PI_N_STAGES && reps > 0, "engine_time_stage: bad arguments");
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned saved = e->skip_mask;
+    const int saved_launches = e->launches;                          // stays the count of the whole step
     e->skip_mask = ~(1u << stage) & ((1u << PI_N_STAGES) - 1u);
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
@@ -860,7 +877,8 @@ int pi_engine_time_stage(pi_engine * e, int T, int stage, int reps, float * host
         ce = cudaStreamEndCapture(st, &graph);
     }
     e->skip_mask = saved;
-    if (host_launches) *host_launches = e->launches;
+    if (host_launches) { const int k = graph ? count_kernel_nodes(graph) : 0; *host_launches = k > 0 ? k : e->launches; }
+    e->launches = saved_launches;
     if (rc == PI_OK && ce == cudaSuccess) ce = cudaGraphInstantiate(&exec, graph, 0);
     if (rc == PI_OK && ce == cudaSuccess) ce = cudaEventCreate(&ev0);
     if (rc == PI_OK && ce == cudaSuccess) ce = cudaEventCreate(&ev1);
