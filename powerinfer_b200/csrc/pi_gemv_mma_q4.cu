@@ -44,12 +44,12 @@ __device__ __forceinline__ void q_bulk_g2s(void * dst, const void * src, unsigne
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  :: "r"(q_smem_u32(dst)), "l"(src), "r"(bytes), "r"(q_smem_u32(bar)) : "memory");
 }
-// rows 8..15 of the A tile are not used: their registers are zero.  {k0, k1} are the C operand of fragment row g.
-__device__ __forceinline__ void mma_u8s8_8rows(int & c0, int & c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1, int k0, int k1) {
-    const uint32_t z = 0u;
-    asm volatile("{\n .reg .s32 c2, c3;\n"
-                 " mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,c2,c3}, {%2,%3,%4,%3}, {%5,%6}, {%7,%8,%3,%3};\n}"
-                 : "=r"(c0), "=r"(c1) : "r"(a0), "r"(z), "r"(a2), "r"(b0), "r"(b1), "r"(k0), "r"(k1));
+// D = A x B + C for a 16 x 32 u8 tile, a 32 x 8 s8 tile and s32 accumulators (fragment rows g and g+8, columns 2q, 2q+1)
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
+                                         int k0, int k1, int k2, int k3) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(k0), "r"(k1), "r"(k2), "r"(k3));
 }
 
 // a packed {FP16 scale | 0x8000 - 8*s} word -> the mma's C operand, and the scale
@@ -71,34 +71,38 @@ struct Q4mP {
 __device__ __forceinline__ void q_bar_sync(int id, int n)   { asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(n) : "memory"); }
 __device__ __forceinline__ void q_bar_arrive(int id, int n) { asm volatile("bar.arrive %0, %1;" :: "r"(id), "r"(n) : "memory"); }
 // arrive only once v0 and v1 exist, i.e. once the shared-memory loads they were summed from have returned
-__device__ __forceinline__ void q_bar_arrive_after(int id, int n, float v0, float v1) {
-    asm volatile("bar.arrive %0, %1;" :: "r"(id), "r"(n), "f"(v0), "f"(v1) : "memory");
+__device__ __forceinline__ void q_bar_arrive_after(int id, int n, float v0, float v1, float v2, float v3) {
+    asm volatile("bar.arrive %0, %1;" :: "r"(id), "r"(n), "f"(v0), "f"(v1), "f"(v2), "f"(v3) : "memory");
 }
 
 // Warp roles: warps 0..15 compute (each owns every 16th pair of blocks of the tile's rows), warp 16 serves: it issues the
 // copies, adds the 16 partial fragments in warp order and runs the epilogue, so the compute warps never stop at a
-// block-wide barrier.  Hand-offs per tile i (parity = i & 1): the compute warps write their partial sums to red[parity] and
-// arrive at named barrier 1+parity, where the serving warp waits; it then refills the tile's ring stage (all compute warps
-// are past it), reduces, stores, and arrives at named barrier 3+parity, which the compute warps pass before they write
-// red[parity] again two tiles later.  All warps run the same number of tiles, so every barrier completes; a warp whose
-// bounded wait for the copies ran out contributes zeros and sets bit 3 of *status.
-// GATED: a second matrix shares the rows (tile = 4 up rows + 4 gate rows)
-template <bool SPARSE, bool GATED>
+// block-wide barrier.  Hand-offs per tile: the compute warps write their partial sums to `red` and arrive at named
+// barrier 1, where the serving warp waits; it then refills the tile's ring stage (all compute warps are past it), reads
+// `red`, arrives at named barrier 2, which the compute warps pass before they write `red` for the next tile (the serving
+// warp is long there by then), and stores.  All warps run the same number of tiles, so every barrier completes; a warp
+// whose bounded wait for the copies ran out contributes zeros and sets bit 3 of *status.
+// M16: tiles of 16 row vectors (all rows of the mma tile carry data) instead of 8; GATED: a second matrix shares the rows
+// (tile = NV/2 up rows + the NV/2 gate rows of the same neurons).
+template <bool SPARSE, bool GATED, bool M16>
 __global__ void __launch_bounds__(Q4M_THREADS, 1) k_gemv_mma_q4(const Q4mP p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    constexpr int IT = GATED ? 4 : 8;                                // items (rows / neurons) of a tile
+    constexpr int NV = M16 ? 16 : 8;                                 // row vectors of a tile
+    constexpr int IT = GATED ? NV / 2 : NV;                          // items (rows / neurons) of a tile
+    constexpr int NR = M16 ? 4 : 2;                                  // accumulators of a lane
+    constexpr int RW = NR * 32;                                      // floats of one warp's partial fragment
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q4 = lane & 3;                          // fragment coordinates: row / token g, word q4
     const int G = gridDim.x, cta = blockIdx.x;
     const int S = p.stages, pitch = p.pitch, nb = p.nb;
     const bool server = warp == Q4M_CWARPS;
 
-    // shared-memory map: [S] mbarriers | row numbers of my tiles | partial sums [2][16 warps][64] |
+    // shared-memory map: [S] mbarriers | row numbers of my tiles | partial sums [16 warps][RW] |
     //                    activation planes: words {lo0,hi0,..,lo3,hi3} [nb][8 tokens] 32 B, {half d | 0x8000 - 8s} [nb][8 tokens] 4 B | ring
     uint64_t * full = reinterpret_cast<uint64_t *>(smem);
     int * rows = reinterpret_cast<int *>(smem + 8 * 32);                                   // [max_tiles * IT] (sparse only)
     float * red = reinterpret_cast<float *>(smem + (((size_t)8 * 32 + (size_t)4 * IT * (SPARSE ? p.max_tiles : 0) + 127) & ~(size_t)127));
-    uint4 * xw = reinterpret_cast<uint4 *>(red + 2 * Q4M_CWARPS * 64);
+    uint4 * xw = reinterpret_cast<uint4 *>(red + Q4M_CWARPS * RW);
     uint32_t * xds = reinterpret_cast<uint32_t *>(xw + (size_t)nb * Q4M_TOK * 2);
     unsigned char * ring = reinterpret_cast<unsigned char *>(xds + (size_t)nb * Q4M_TOK);
 
@@ -181,8 +185,9 @@ __global__ void __launch_bounds__(Q4M_THREADS, 1) k_gemv_mma_q4(const Q4mP p) {
         }
     }
     __syncthreads();
-    constexpr int NB_A = 1, NB_B = 3;                                // named barriers: partial sums ready / red[] free (+ parity)
+    constexpr int NB_A = 1, NB_B = 2;                                // named barriers: partial sums ready / `red` free
     constexpr int NB_COUNT = Q4M_THREADS;
+    constexpr uint32_t NIB = 0x0F0F0F0Fu;
 
     if (!server) {
         // ------------------------------------------------------------------------------------ compute warps
@@ -190,7 +195,7 @@ __global__ void __launch_bounds__(Q4M_THREADS, 1) k_gemv_mma_q4(const Q4mP p) {
         const uint2 * xds_q = reinterpret_cast<const uint2 *>(xds) + q4;                   // + b*4: tokens 2*q4, 2*q4+1
         const int n_pairs = nb >> 1;
         for (int i = 0; i < my_tiles; i++) {
-            const int s = i % S, par = i & 1;
+            const int s = i % S;
             bool dead = false;                                       // warp-uniform
             {
                 int spins = 0;
@@ -199,76 +204,107 @@ __global__ void __launch_bounds__(Q4M_THREADS, 1) k_gemv_mma_q4(const Q4mP p) {
                 dead = __any_sync(0xffffffffu, gave_up) != 0;
                 if (dead && lane == 0) atomicOr(p.status, 8u);
             }
-            float acc0 = 0.f, acc1 = 0.f;                            // vector g x tokens 2*q4, 2*q4+1
+            float acc[NR];                                           // vectors g (and g+8) x tokens 2*q4, 2*q4+1
+#pragma unroll
+            for (int j = 0; j < NR; j++) acc[j] = 0.f;
             if (!dead) {
                 const unsigned char * vrow = ring + (size_t)s * p.stage_bytes + (size_t)g * pitch;
                 const uint32_t * aw = reinterpret_cast<const uint32_t *>(vrow) + q4;        // + b*4: word q4 of block b
                 const __half2 * dw = reinterpret_cast<const __half2 *>(vrow + (size_t)nb * 16);   // + b/2: scales of blocks b, b+1
-#pragma unroll 4
+                const uint32_t * aw8 = reinterpret_cast<const uint32_t *>(vrow + (size_t)8 * pitch) + q4;          // vector g+8
+                const __half2 * dw8 = reinterpret_cast<const __half2 *>(vrow + (size_t)8 * pitch + (size_t)nb * 16);
+#pragma unroll 2
                 for (int pj = warp; pj < n_pairs; pj += Q4M_CWARPS) {
                     const int b = pj * 2;
                     const uint32_t w0 = aw[b * 4], w1 = aw[b * 4 + 4];
                     const uint2 x0 = xb[b * 32], x1 = xb[b * 32 + 32];
                     const uint2 ds0 = xds_q[b * 4], ds1 = xds_q[b * 4 + 4];
                     const float2 d4 = __half22float2(dw[pj]);
-                    int c0, c1, e0, e1;
-                    mma_u8s8_8rows(c0, c1, w0 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu, x0.x, x0.y, q_magic(ds0.x), q_magic(ds0.y));
-                    mma_u8s8_8rows(e0, e1, w1 & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, x1.x, x1.y, q_magic(ds1.x), q_magic(ds1.y));
-                    acc0 = fmaf(__int_as_float(c0) - Q4M_BIAS, d4.x * q_scale(ds0.x), acc0);
-                    acc1 = fmaf(__int_as_float(c1) - Q4M_BIAS, d4.x * q_scale(ds0.y), acc1);
-                    acc0 = fmaf(__int_as_float(e0) - Q4M_BIAS, d4.y * q_scale(ds1.x), acc0);
-                    acc1 = fmaf(__int_as_float(e1) - Q4M_BIAS, d4.y * q_scale(ds1.y), acc1);
+                    const int k00 = q_magic(ds0.x), k01 = q_magic(ds0.y), k10 = q_magic(ds1.x), k11 = q_magic(ds1.y);
+                    const float s00 = q_scale(ds0.x), s01 = q_scale(ds0.y), s10 = q_scale(ds1.x), s11 = q_scale(ds1.y);
+                    int c[4], e[4];
+                    if (M16) {
+                        const uint32_t v0 = aw8[b * 4], v1 = aw8[b * 4 + 4];
+                        const float2 e4 = __half22float2(dw8[pj]);
+                        mma_u8s8(c, w0 & NIB, v0 & NIB, (w0 >> 4) & NIB, (v0 >> 4) & NIB, x0.x, x0.y, k00, k01, k00, k01);
+                        mma_u8s8(e, w1 & NIB, v1 & NIB, (w1 >> 4) & NIB, (v1 >> 4) & NIB, x1.x, x1.y, k10, k11, k10, k11);
+                        acc[NR - 2] = fmaf(__int_as_float(c[2]) - Q4M_BIAS, e4.x * s00, acc[NR - 2]);
+                        acc[NR - 1] = fmaf(__int_as_float(c[3]) - Q4M_BIAS, e4.x * s01, acc[NR - 1]);
+                        acc[NR - 2] = fmaf(__int_as_float(e[2]) - Q4M_BIAS, e4.y * s10, acc[NR - 2]);
+                        acc[NR - 1] = fmaf(__int_as_float(e[3]) - Q4M_BIAS, e4.y * s11, acc[NR - 1]);
+                    } else {
+                        mma_u8s8(c, w0 & NIB, 0u, (w0 >> 4) & NIB, 0u, x0.x, x0.y, k00, k01, 0, 0);
+                        mma_u8s8(e, w1 & NIB, 0u, (w1 >> 4) & NIB, 0u, x1.x, x1.y, k10, k11, 0, 0);
+                    }
+                    acc[0] = fmaf(__int_as_float(c[0]) - Q4M_BIAS, d4.x * s00, acc[0]);
+                    acc[1] = fmaf(__int_as_float(c[1]) - Q4M_BIAS, d4.x * s01, acc[1]);
+                    acc[0] = fmaf(__int_as_float(e[0]) - Q4M_BIAS, d4.y * s10, acc[0]);
+                    acc[1] = fmaf(__int_as_float(e[1]) - Q4M_BIAS, d4.y * s11, acc[1]);
                 }
             }
-            if (i >= 2) q_bar_sync(NB_B + par, NB_COUNT);            // the serving warp is done with red[par] of tile i-2
-            float * r = red + (size_t)(par * Q4M_CWARPS + warp) * 64;
-            r[lane] = acc0;
-            r[32 + lane] = acc1;
+            if (i >= 1) q_bar_sync(NB_B, NB_COUNT);                  // the serving warp has read `red` of tile i-1
+            float * r = red + (size_t)warp * RW;
+#pragma unroll
+            for (int j = 0; j < NR; j++) r[j * 32 + lane] = acc[j];
             __threadfence_block();
-            q_bar_arrive(NB_A + par, NB_COUNT);
+            q_bar_arrive(NB_A, NB_COUNT);
         }
     } else {
         // ------------------------------------------------------------------------------------ serving warp
-        const int m = g, k = GATED ? (m & 3) : m;                    // my fragment row = vector m of the tile = item k
+        // What a lane's fragment rows are: M16 dense: items g and g+8; M16 gated: item g (up in rows g, gate in rows g+8);
+        // 8 vectors dense: item g; 8 vectors gated: item g & 3 (up in lanes with g < 4, its gate sums 16 lanes up).
+        constexpr int NH = (M16 && !GATED) ? 2 : 1;
         for (int i = 0; i < my_tiles; i++) {
-            const int par = i & 1, n = tile_rows(i);
+            const int n = tile_rows(i);
             // the epilogue's global operands (row -> neuron id -> logits, bias) are fetched while the tile is computed
-            const bool mine = k < n && (!GATED || m < 4);
             const int t0 = 2 * q4, t1 = t0 + 1;
-            int64_t gid = 0;
-            bool act0 = true, act1 = true;
-            float biasv = 0.f;
-            if (mine) {
-                const int r = SPARSE ? rows[i * IT + k] : (cta + i * G) * IT + k;
-                gid = SPARSE && p.bucket ? p.bucket[r] : r;
-                if (SPARSE) {
-                    if (t0 < p.T) act0 = !(p.idx[(size_t)t0 * p.idx_stride + gid] < p.threshold);
-                    if (t1 < p.T) act1 = !(p.idx[(size_t)t1 * p.idx_stride + gid] < p.threshold);
-                }
-                if (p.bias) biasv = p.bias[gid];
-            }
-            q_bar_sync(NB_A + par, NB_COUNT);                        // all compute warps are past tile i: its stage is free
-            if (i + S < my_tiles) issue(i + S);
-            const float * r = red + (size_t)par * Q4M_CWARPS * 64;
-            float v0 = r[lane], v1 = r[32 + lane];
+            int64_t gid[NH];
+            bool mine[NH], act0[NH], act1[NH];
+            float biasv[NH];
 #pragma unroll
-            for (int w = 1; w < Q4M_CWARPS; w++) { v0 += r[w * 64 + lane]; v1 += r[w * 64 + 32 + lane]; }
-            if (i + 2 < my_tiles) q_bar_arrive_after(NB_B + par, NB_COUNT, v0, v1);
-            float o0 = v0, o1 = v1;
-            if (GATED) {                                             // the gate sums of item k sit 4 fragment rows (16 lanes) up
-                const float g0 = __shfl_down_sync(0xffffffffu, v0, 16), g1 = __shfl_down_sync(0xffffffffu, v1, 16);
-                o0 = fmaxf(g0, 0.f) * v0; o1 = fmaxf(g1, 0.f) * v1;
-            }
-            if (mine) {
-                o0 = (act0 ? o0 : 0.f) + biasv; o1 = (act1 ? o1 : 0.f) + biasv;
-                if (p.relu) { o0 = fmaxf(o0, 0.f); o1 = fmaxf(o1, 0.f); }
-                if (t0 < p.T) {
-                    if (p.dst)   p.dst[(size_t)t0 * p.dst_stride + gid] = o0;
-                    if (p.dst16) p.dst16[(size_t)t0 * p.dst_stride + gid] = __float2half_rn(o0);
+            for (int h = 0; h < NH; h++) {
+                const int k = M16 ? g + 8 * h : (GATED ? (g & 3) : g);
+                mine[h] = k < n && (M16 || !GATED || g < 4);
+                gid[h] = 0; act0[h] = true; act1[h] = true; biasv[h] = 0.f;
+                if (mine[h]) {
+                    const int r = SPARSE ? rows[i * IT + k] : (cta + i * G) * IT + k;
+                    gid[h] = SPARSE && p.bucket ? p.bucket[r] : r;
+                    if (SPARSE) {
+                        if (t0 < p.T) act0[h] = !(p.idx[(size_t)t0 * p.idx_stride + gid[h]] < p.threshold);
+                        if (t1 < p.T) act1[h] = !(p.idx[(size_t)t1 * p.idx_stride + gid[h]] < p.threshold);
+                    }
+                    if (p.bias) biasv[h] = p.bias[gid[h]];
                 }
-                if (t1 < p.T) {
-                    if (p.dst)   p.dst[(size_t)t1 * p.dst_stride + gid] = o1;
-                    if (p.dst16) p.dst16[(size_t)t1 * p.dst_stride + gid] = __float2half_rn(o1);
+            }
+            q_bar_sync(NB_A, NB_COUNT);                              // all compute warps are past tile i: its stage is free
+            if (i + S < my_tiles) issue(i + S);
+            float v[NR];
+#pragma unroll
+            for (int j = 0; j < NR; j++) v[j] = red[j * 32 + lane];
+#pragma unroll
+            for (int w = 1; w < Q4M_CWARPS; w++)
+#pragma unroll
+                for (int j = 0; j < NR; j++) v[j] += red[w * RW + j * 32 + lane];
+            if (i + 1 < my_tiles) q_bar_arrive_after(NB_B, NB_COUNT, v[0], v[1], v[NR - 2], v[NR - 1]);
+#pragma unroll
+            for (int h = 0; h < NH; h++) {
+                float o0 = v[2 * h], o1 = v[2 * h + 1];
+                if (GATED) {
+                    const float g0 = M16 ? v[NR - 2] : __shfl_down_sync(0xffffffffu, v[0], 16);
+                    const float g1 = M16 ? v[NR - 1] : __shfl_down_sync(0xffffffffu, v[1], 16);
+                    o0 = fmaxf(g0, 0.f) * v[0]; o1 = fmaxf(g1, 0.f) * v[1];
+                }
+                if (mine[h]) {
+                    o0 = (act0[h] ? o0 : 0.f) + biasv[h]; o1 = (act1[h] ? o1 : 0.f) + biasv[h];
+                    if (p.relu) { o0 = fmaxf(o0, 0.f); o1 = fmaxf(o1, 0.f); }
+                    if (t0 < p.T) {
+                        if (p.dst)   p.dst[(size_t)t0 * p.dst_stride + gid[h]] = o0;
+                        if (p.dst16) p.dst16[(size_t)t0 * p.dst_stride + gid[h]] = __float2half_rn(o0);
+                    }
+                    if (t1 < p.T) {
+                        if (p.dst)   p.dst[(size_t)t1 * p.dst_stride + gid[h]] = o1;
+                        if (p.dst16) p.dst16[(size_t)t1 * p.dst_stride + gid[h]] = __float2half_rn(o1);
+                    }
                 }
             }
         }
@@ -279,15 +315,17 @@ __global__ void __launch_bounds__(Q4M_THREADS, 1) k_gemv_mma_q4(const Q4mP p) {
     }
 }
 
+struct Q4mPlan { bool ok; bool m16; int stages, pitch, max_tiles; size_t stage_bytes, smem; };
 
-struct Q4mPlan { bool ok; int stages, pitch, max_tiles; size_t stage_bytes, smem; };
+static constexpr size_t Q4M_SMEM_MAX = 232448;          // 227 KB: the most dynamic shared memory a CTA can opt into
 
-static Q4mPlan q4m_plan(int64_t nrows, int nb, bool sparse, bool gated) {
+static Q4mPlan q4m_plan(int64_t nrows, int nb, bool sparse, bool gated, bool m16) {
     Q4mPlan pl{};
     if (nb <= 0 || nb % 8 != 0) return pl;                           // rows must be copyable in 16-byte units
-    const int it = gated ? 4 : 8;
+    const int nv = m16 ? 16 : 8;
+    const int it = gated ? nv / 2 : nv;
     const int G = sm_count();
-    const size_t budget = (size_t)224 * 1024;
+    if (!sparse && nrows / it < G) return pl;                        // too few row tiles to fill the GPU
     const int max_tiles = sparse ? (int)(((nrows + it - 1) / it + G - 1) / G) : 0;
     if (max_tiles > 2048) return pl;
     const size_t row_bytes = (size_t)nb * 18;
@@ -300,47 +338,62 @@ static Q4mPlan q4m_plan(int64_t nrows, int nb, bool sparse, bool gated) {
         if (seen == 0xffffffffu) pitch = (int)row_bytes + pad;
     }
     if (!pitch) return pl;
-    const size_t head = (((size_t)8 * 32 + (size_t)4 * it * max_tiles + 127) & ~size_t(127)) + (size_t)2 * Q4M_CWARPS * 64 * 4 + (size_t)nb * Q4M_TOK * 36;
-    const size_t stage_bytes = ((size_t)8 * pitch + 127) & ~size_t(127);
-    if (head + 2 * stage_bytes > budget) return pl;
-    int S = (int)((budget - head) / stage_bytes);
+    const size_t head = (((size_t)8 * 32 + (size_t)4 * it * max_tiles + 127) & ~size_t(127))
+                      + (size_t)Q4M_CWARPS * (m16 ? 128 : 64) * 4 + (size_t)nb * Q4M_TOK * 36;
+    const size_t stage_bytes = ((size_t)nv * pitch + 127) & ~size_t(127);
+    if (head + 2 * stage_bytes > Q4M_SMEM_MAX) return pl;
+    int S = (int)((Q4M_SMEM_MAX - head) / stage_bytes);
     static int s_env = -1;
     if (s_env < 0) { const char * v = getenv("PI_MMA_Q4_STAGES"); s_env = v ? atoi(v) : 0; }
     if (s_env >= 2 && s_env < S) S = s_env;
-    pl.ok = true; pl.stages = S > 8 ? 8 : S; pl.pitch = pitch; pl.max_tiles = max_tiles;
+    pl.ok = true; pl.m16 = m16; pl.stages = S > 8 ? 8 : S; pl.pitch = pitch; pl.max_tiles = max_tiles;
     pl.stage_bytes = stage_bytes; pl.smem = head + (size_t)pl.stages * stage_bytes;
     return pl;
 }
 
-template <bool SPARSE, bool GATED>
+template <bool SPARSE, bool GATED, bool M16>
 static int launch_q4m_inst(const Q4mP & p, const Q4mPlan & pl, bool pdl, cudaStream_t st) {
     static bool attr_done[16] = {false};
     int dev = 0;
     PI_CUDA(cudaGetDevice(&dev));
-    auto kern = k_gemv_mma_q4<SPARSE, GATED>;
+    auto kern = k_gemv_mma_q4<SPARSE, GATED, M16>;
     if (dev >= 0 && dev < 16 && !attr_done[dev]) {
-        PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
+        PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Q4M_SMEM_MAX));
         attr_done[dev] = true;
     }
     PI_CUDA(launch_k(kern, dim3(sm_count()), dim3(Q4M_THREADS), pl.smem, st, pdl, p));
     return PI_OK;
 }
 
+template <bool M16>
+static int launch_q4m_shape(const Q4mP & p, const Q4mPlan & pl, bool sparse, bool gated, bool pdl, cudaStream_t st) {
+    if (!sparse) return launch_q4m_inst<false, false, M16>(p, pl, pdl, st);
+    if (gated)   return launch_q4m_inst<true, true, M16>(p, pl, pdl, st);
+    return launch_q4m_inst<true, false, M16>(p, pl, pdl, st);
+}
+
 // PI_ERR_UNSUPPORTED: shape not eligible, the caller uses another kernel.  Tokens go in launches of at most 8.
 int launch_gemv_mma_q4(const GemvArgs & a, cudaStream_t st) {
     static int enabled = -1;
-    static int min_T = 0;
-    if (enabled < 0) { const char * v = getenv("PI_MMA_Q4"); enabled = !(v && v[0] == '0'); const char * m = getenv("PI_MMA_Q4_MIN_T"); if (m) min_T = atoi(m); }
+    static int min_T = 0, rows_env = 0;
+    if (enabled < 0) {
+        const char * m = getenv("PI_MMA_Q4_MIN_T"); if (m) min_T = atoi(m);
+        const char * r = getenv("PI_MMA_Q4_ROWS"); if (r) rows_env = atoi(r);
+        const char * v = getenv("PI_MMA_Q4"); enabled = !(v && v[0] == '0');
+    }
     const bool sparse = a.list != nullptr, gated = a.W2 != nullptr;
-    // measured on the 70B shape: from 2 tokens on this kernel is level with or ahead of the CUDA-core one, for the gated pair
-    // (tiles of 4 neurons) from 4 tokens on
-    const int need_T = min_T > 0 ? min_T : (gated ? 4 : 2);
-    if (!enabled || a.T < need_T || a.wtype != PI_TYPE_Q4_0 || !a.status || !a.x.lo || a.fin.on || a.res_add || a.stats_out) return PI_ERR_UNSUPPORTED;
+    if (!enabled || a.wtype != PI_TYPE_Q4_0 || !a.status || !a.x.lo || a.fin.on || a.res_add || a.stats_out) return PI_ERR_UNSUPPORTED;
     if (a.ncols % QK != 0) return PI_ERR_UNSUPPORTED;
-    if (!sparse && a.nrows / 8 < sm_count()) return PI_ERR_UNSUPPORTED;       // too few row tiles to fill the GPU
     const int nb = (int)(a.ncols / QK);
-    const Q4mPlan pl = q4m_plan(a.nrows, nb, sparse, gated);
+    // tiles of 16 vectors when their ring fits next to the activation planes (rows up to 8192 columns), else of 8
+    Q4mPlan pl{};
+    if (rows_env != 8) pl = q4m_plan(a.nrows, nb, sparse, gated, true);
+    if (!pl.ok && rows_env != 16) pl = q4m_plan(a.nrows, nb, sparse, gated, false);
     if (!pl.ok) return PI_ERR_UNSUPPORTED;
+    // measured on the 70B shape: from 2 tokens on this kernel is level with or ahead of the CUDA-core one, for the gated
+    // pair from 4 tokens on
+    const int need_T = min_T > 0 ? min_T : (gated ? 4 : 2);
+    if (a.T < need_T) return PI_ERR_UNSUPPORTED;
     for (int t0 = 0; t0 < a.T; t0 += Q4M_TOK) {
         Q4mP p;
         p.W = (const uint8_t *)a.W; p.W2 = (const uint8_t *)a.W2;
@@ -355,10 +408,7 @@ int launch_gemv_mma_q4(const GemvArgs & a, cudaStream_t st) {
         p.dst16 = a.dst16 ? a.dst16 + (size_t)t0 * a.dst_stride : nullptr;
         p.dst_stride = a.dst_stride; p.status = a.status;
         p.stages = pl.stages; p.pitch = pl.pitch; p.max_tiles = pl.max_tiles; p.stage_bytes = pl.stage_bytes;
-        int rc;
-        if (!sparse)     rc = launch_q4m_inst<false, false>(p, pl, a.pdl, st);
-        else if (gated)  rc = launch_q4m_inst<true, true>(p, pl, a.pdl, st);
-        else             rc = launch_q4m_inst<true, false>(p, pl, a.pdl, st);
+        const int rc = pl.m16 ? launch_q4m_shape<true>(p, pl, sparse, gated, a.pdl, st) : launch_q4m_shape<false>(p, pl, sparse, gated, a.pdl, st);
         if (rc != PI_OK) return rc;
     }
     return PI_OK;

@@ -220,11 +220,11 @@ def test_small_batch_tensor_core_kernels_vs_oracle(ops, oracle, wtype, T):
 @pytest.mark.parametrize("T", [2, 5, 8, 11, 16])
 @pytest.mark.parametrize("d", [256, 1024, 2560])
 def test_q4_0_small_batch_integer_tensor_core_kernel_vs_oracle(ops, oracle, T, d):
-    """Q4_0 rows with 2+ tokens take the integer tensor-core kernel (tiles of 8 row vectors, launches of 8 tokens): dense
+    """Q4_0 rows with 2+ tokens take the integer tensor-core kernel (tiles of 16 or 8 row vectors, launches of 8 tokens): dense
     with a ragged last tile, ggml_mul_mat_idx over a ragged list, bucketed rows, and the gated pair inside the one-call
     FFN, against the CPU operators.  The integer block dots are exact; only the FP32 order over the blocks differs."""
     rng = np.random.default_rng(1300 + T + d)
-    F = 1190 + 8 * 3 + 5                                          # >= 148 tiles of 8, last tile ragged
+    F = 2400 + 16 + 5                                             # >= 148 tiles of 16 rows, last tile ragged
     x = rng.standard_normal((T, d), dtype=np.float32)
     mk = lambda n: synth.quantize_q4_0(rng.standard_normal((n, d), dtype=np.float32) * np.float32(0.02))
     W, Wg = mk(F), mk(F)
