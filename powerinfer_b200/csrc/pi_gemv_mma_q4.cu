@@ -4,18 +4,20 @@
 // int8 values, minus 8 x (sum of the int8 values), times the two block scales, accumulated in FP32 (ggml.c:2494-2560).
 // On the CUDA cores every (row, block, token) costs eight dp4a plus two 128-bit shared-memory reads of the activation
 // block; at 8 tokens that kernel is bound by shared-memory bandwidth at about an eighth of the HBM rate.  Here one
-// mma.sync.m16n8k32 (u8 x s8 -> s32) does the 32-value dots of 8 weight rows with 8 tokens at once: the nibbles are the
+// mma.sync.m16n8k32 (u8 x s8 -> s32) does the 32-value dots of 16 weight rows with 8 tokens at once: the nibbles are the
 // A operand (low nibbles = values 0..15 of the block, high nibbles = values 16..31, which is exactly the k order of the
 // fragment), the two int8 planes of the activations the B operand.  The integer results are the same numbers dp4a gives;
 // the scales are applied per block in FP32 as before, so only the order of the FP32 additions over the blocks differs.
 //
-// Work unit: a tile of 8 row vectors (dense / ggml_mul_mat_idx: 8 rows; with a gate matrix: 4 up rows + the 4 gate rows of
-// the same neurons), each whole row placed by one cp.async.bulk (plain, non-tensor, no multicast; 16-byte aligned) at a
-// pitch that keeps the fragment reads bank-conflict free.  The activation planes of the launch's tokens are staged once
-// per CTA, interleaved by token.  16 compute warps split the blocks of a row; a 17th warp issues the copies, adds the
-// partial sums in warp order through shared memory and runs the epilogue (predicate, gate, bias, relu) while the compute
-// warps go on with the next tile.  Tiles are dealt round-robin to one CTA per SM.  Dense weights do not depend on the previous kernel: their copies are issued before griddepcontrol.wait.  Every
-// mbarrier wait is bounded: on expiry the CTA sets bit 3 of *status and stops.
+// Work unit: a tile of 16 row vectors (dense / ggml_mul_mat_idx: 16 rows; with a gate matrix: 8 up rows + the 8 gate rows
+// of the same neurons), each whole row placed by one cp.async.bulk (plain, non-tensor, no multicast; 16-byte aligned) at a
+// pitch that keeps the fragment reads bank-conflict free; two such stages (74 KB each at 8192 columns) fit next to the
+// activation planes of the launch's tokens, which are staged once per CTA, interleaved by token.  Rows too long for that
+// go in tiles of 8 vectors (rows 8..15 of the mma tile then stay zero).  16 compute warps split the blocks of a row; a
+// 17th warp issues the copies, adds the partial sums in warp order through shared memory and runs the epilogue
+// (predicate, gate, bias, relu) while the compute warps go on with the next tile.  Tiles are dealt round-robin to one CTA
+// per SM.  Dense weights do not depend on the previous kernel: their copies are issued before griddepcontrol.wait.
+// Every mbarrier wait is bounded: on expiry the warp sets bit 3 of *status and contributes zeros.
 #include "pi_common.cuh"
 
 #include <cstdlib>
