@@ -47,3 +47,44 @@ def test_rope_table_matches_reference_recurrence():
     for pos in (0, 1, 17, 39):
         y = o.rope(x, hd, 1, pos, 10000.0, False)
         assert np.array_equal(y[0, 0::2], cs[pos, :, 0]) and np.array_equal(y[0, 1::2], cs[pos, :, 1])
+
+
+C_CONSUMER = r"""
+#include <stdio.h>
+#include <string.h>
+#include "powerinfer_b200.h"
+int main(void) {
+    float cs[4 * 8 * 2];
+    if (pi_version() < 1) return 2;
+    if (pi_row_bytes(PI_TYPE_Q4_0, 4096) != 2304 || pi_row_bytes(PI_TYPE_F16, 4096) != 8192) return 3;
+    if (pi_workspace_bytes(4096, 11008, 4) == 0) return 4;
+    pi_rope_table_host(cs, 4, 16, 10000.0f);
+    if (cs[0] != 1.0f || cs[1] != 0.0f) return 5;                      /* position 0: cos 1, sin 0 */
+    /* argument validation comes before any CUDA call: no device needed */
+    if (pi_mul_mat(PI_TYPE_Q4_0, (const void *)16, 8, 100, (const float *)16, 1, NULL, (float *)16, (void *)256, 1u << 20, NULL) != PI_ERR_INVALID) return 6;
+    if (strlen(pi_last_error()) == 0) return 7;
+    puts("c consumer ok");
+    return 0;
+}
+"""
+
+
+def test_plain_c99_consumer_compiles_links_and_runs(tmp_path):
+    """The header is C (not only C++): a C99 translation unit with -pedantic -Werror includes it, links the library and
+    calls the entry points that need no device."""
+    import shutil
+    import subprocess
+    import pytest
+    from powerinfer_b200 import build
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    lib = build.build()
+    src = tmp_path / "consumer.c"
+    src.write_text(C_CONSUMER)
+    exe = tmp_path / "consumer"
+    libdir = os.path.dirname(lib)
+    r = subprocess.run(["gcc", "-std=c99", "-pedantic", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                        "-L", libdir, "-lpowerinfer_b200", f"-Wl,-rpath,{libdir}"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and "c consumer ok" in r.stdout, (r.returncode, r.stdout, r.stderr[-2000:])
