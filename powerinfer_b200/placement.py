@@ -111,3 +111,59 @@ def deal_across_gpus(counts: np.ndarray, n_gpus: int, block: int = 32) -> list:
 def vram_bytes(neurons_per_layer: list, row_bytes: int, n_mats: int) -> int:
     """Bytes of FFN rows the placement keeps on the GPU: n_mats rows (gate, up, down_t) of row_bytes per hot neuron."""
     return int(sum(neurons_per_layer)) * row_bytes * n_mats
+
+
+def load_activation_counts(directory: str) -> list:
+    """`activation_<i>.pt` files of a profiling run (one 1-D tensor of per-neuron activation counts per layer), in layer
+    order, as float64 arrays.  The reference sorts the file names as strings (export_split.py:16-22), which puts
+    activation_10 before activation_2; here they are ordered by layer number, which is what the solver's
+    `activation_{i}.pt` loop (solver.py:20-22) reads."""
+    import os
+    import re
+    import torch
+    found = {}
+    for f in os.listdir(directory):
+        m = re.fullmatch(r"activation_(\d+)\.pt", f)
+        if m:
+            found[int(m.group(1))] = os.path.join(directory, f)
+    if not found or sorted(found) != list(range(len(found))):
+        raise ValueError(f"{directory}: expected activation_0.pt .. activation_<n-1>.pt, found layers {sorted(found)}")
+    return [torch.load(found[i], map_location="cpu").to(torch.float64).reshape(-1).numpy() for i in range(len(found))]
+
+
+def main(argv=None) -> int:
+    """`python -m powerinfer_b200.placement`: the command line of powerinfer-py (`python -m powerinfer`, __main__.py:10-46)
+    with the same flags: profile directory -> per-layer neuron counts under the capacity -> `.generated.gpuidx` file."""
+    import argparse
+    from . import gguf_loader
+    ap = argparse.ArgumentParser(prog="python -m powerinfer_b200.placement",
+                                 description="Choose the GPU-resident FFN neurons of every layer under a capacity and write the GPU index file.")
+    ap.add_argument("--activation", required=True, help="directory with activation_<layer>.pt count tensors")
+    ap.add_argument("--neuron", type=int, default=8192 * 4, help="neurons per layer")
+    ap.add_argument("--capacity", type=int, default=int(8192 * 4 * 32 * 0.1), help="neurons that fit on the GPU in total")
+    ap.add_argument("--layer", type=int, default=None, help="layers to place (default: every activation file)")
+    ap.add_argument("--vram-capacity", type=int, default=0, help="bytes of VRAM the split was made for (recorded in the file)")
+    ap.add_argument("--batch", type=int, default=256, help="neurons per placement slice")
+    ap.add_argument("--threshold", type=int, default=0, help="a layer gets no neurons or at least this many")
+    ap.add_argument("--whole-blocks", action="store_true", help="place whole blocks of 32 consecutive neurons (needed for a Q4_0 down_t bucket)")
+    ap.add_argument("--output", required=True, help="path of the GPU index file to write")
+    a = ap.parse_args(argv)
+    counts = load_activation_counts(a.activation)
+    if a.layer is not None:
+        if a.layer > len(counts):
+            raise SystemExit(f"--layer {a.layer} but only {len(counts)} activation files")
+        counts = counts[: a.layer]
+    for i, c in enumerate(counts):
+        if c.size != a.neuron:
+            raise SystemExit(f"layer {i}: {c.size} counts, --neuron says {a.neuron}")
+    solved = solve_gpu_split(counts, a.capacity, a.batch, a.threshold)
+    pick = bucket_of_whole_blocks if a.whole_blocks else gpu_idx_and_bucket
+    idx, bucket = zip(*(pick(c, k) for c, k in zip(counts, solved)))
+    gguf_loader.write_gpu_split(a.output, list(idx), list(bucket), a.vram_capacity)
+    print(f"solved: {solved}, total neurons: {sum(solved)}")
+    print(f"exported GPU index to {a.output}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

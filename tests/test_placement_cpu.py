@@ -1,6 +1,7 @@
 """Hot / cold placement (the gpu_idx / gpu_bucket contract) on CPU: exactness of the split solver against brute force, the
 export rule of the reference (top-k by activation count, bucket sorted), whole-block buckets and multi-GPU dealing."""
 import itertools
+import os
 
 import numpy as np
 import pytest
@@ -72,3 +73,37 @@ def test_whole_block_bucket_and_dealing():
 
 def test_vram_bytes():
     assert placement.vram_bytes([256, 512], 4608, 3) == 768 * 4608 * 3
+
+
+def test_command_line_writes_the_gpu_index_file(tmp_path):
+    """`python -m powerinfer_b200.placement` with powerinfer-py's flags: activation_<i>.pt files in, a PWRI GPU index file
+    out whose tensors follow the export rule for the solver's per-layer counts (layer 10 must not sort before layer 2)."""
+    import subprocess
+    import sys
+    import torch
+    from powerinfer_b200 import gguf_loader, placement
+    rng = np.random.default_rng(5)
+    n_layer, F, batch = 12, 1024, 64
+    counts = [np.floor(rng.pareto(1.2, F) * (1 + i)).astype(np.float32) for i in range(n_layer)]
+    act = tmp_path / "act"
+    act.mkdir()
+    for i, c in enumerate(counts):
+        torch.save(torch.from_numpy(c), act / f"activation_{i}.pt")
+    out = tmp_path / "model.generated.gpuidx"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "powerinfer_b200.placement", "--activation", str(act), "--neuron", str(F),
+                        "--capacity", str(3 * F), "--batch", str(batch), "--threshold", str(2 * batch),
+                        "--vram-capacity", str(123456789), "--output", str(out)], capture_output=True, text=True, cwd=root)
+    assert r.returncode == 0, r.stderr[-2000:]
+    idx, bucket, vram = gguf_loader.load_gpu_split(str(out))
+    assert vram == 123456789 and len(idx) == n_layer
+    solved = placement.solve_gpu_split(counts, 3 * F, batch, 2 * batch)
+    assert sum(solved) <= 3 * F and all(k == 0 or k >= 2 * batch for k in solved)
+    for i in range(n_layer):
+        want_idx, want_bucket = placement.gpu_idx_and_bucket(counts[i], solved[i])
+        assert np.array_equal(idx[i], want_idx) and np.array_equal(bucket[i], want_bucket)
+        assert len(bucket[i]) == solved[i] and np.all(np.diff(bucket[i]) > 0)
+    # a wrong --neuron is refused
+    r = subprocess.run([sys.executable, "-m", "powerinfer_b200.placement", "--activation", str(act), "--neuron", str(F + 64),
+                        "--output", str(out)], capture_output=True, text=True, cwd=root)
+    assert r.returncode != 0 and "counts" in r.stderr
