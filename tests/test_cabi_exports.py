@@ -88,3 +88,22 @@ def test_plain_c99_consumer_compiles_links_and_runs(tmp_path):
     assert r.returncode == 0, r.stderr[-3000:]
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0 and "c consumer ok" in r.stdout, (r.returncode, r.stdout, r.stderr[-2000:])
+
+
+def test_no_device_means_an_error_status_not_a_fallback():
+    """On a box without a GPU the compute entry points return PI_ERR_CUDA and a message naming the failed launch: there is
+    no CPU path behind the C ABI."""
+    import ctypes as C
+    import pytest
+    torch = pytest.importorskip("torch")
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    from powerinfer_b200 import _lib
+    lib = _lib.lib
+    buf = (C.c_char * (1 << 20))()
+    addr = (C.addressof(buf) + 255) & ~255
+    rc = lib.pi_mul_mat(_lib.PI_TYPE_F16, addr, 8, 256, addr, 1, None, addr, addr, 1 << 19, None)
+    assert rc == 2 and b"CUDA error" in lib.pi_last_error()
+    rc = lib.pi_norm(addr, 1, 256, 1, C.c_float(1e-5), None, None, addr, None)
+    assert rc == 2 and b"CUDA error" in lib.pi_last_error()
+    assert not bytes(buf[:4096]).strip(b"\0")                      # nothing was computed on the host
