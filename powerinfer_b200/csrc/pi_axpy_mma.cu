@@ -24,23 +24,6 @@ static constexpr int AM_WARPS = 16;
 static constexpr int AM_CW = 1024;                     // columns per CTA
 static constexpr int AM_PITCH = AM_CW * 2 + 16;
 
-__device__ __forceinline__ uint32_t am_smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void am_mbar_init(uint64_t * bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(am_smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void am_mbar_expect_tx(uint64_t * bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(am_smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool am_mbar_try_wait(uint64_t * bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(am_smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void am_bulk_g2s(void * dst, const void * src, unsigned bytes, uint64_t * bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(am_smem_u32(dst)), "l"(src), "r"(bytes), "r"(am_smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void am_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
@@ -77,7 +60,7 @@ __global__ void __launch_bounds__(AM_THREADS) k_axpy_mma(const AxpyMmaP p) {
 
     pdl_launch();
     if (tid == 0) {
-        for (int s = 0; s < S; s++) am_mbar_init(full + s, 1);
+        for (int s = 0; s < S; s++) mbar_init(full + s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -95,9 +78,9 @@ __global__ void __launch_bounds__(AM_THREADS) k_axpy_mma(const AxpyMmaP p) {
     __syncthreads();
     auto issue = [&](int k) {                                        // all lanes of warp 0
         const int s = k % S;
-        if (lane == 0) am_mbar_expect_tx(full + s, (unsigned)(16 * AM_CW * 2));
+        if (lane == 0) mbar_expect_tx(full + s, (unsigned)(16 * AM_CW * 2));
         if (lane < 16)
-            am_bulk_g2s(ring + s * stage_bytes + (size_t)lane * AM_PITCH,
+            bulk_g2s(ring + s * stage_bytes + (size_t)lane * AM_PITCH,
                         p.Wt + (size_t)rows[k * 16 + lane] * p.row_bytes + (size_t)cs * AM_CW * 2, (unsigned)(AM_CW * 2), full + s);
     };
     if (warp == 0) for (int k = 0; k < S && k < n_tiles; k++) issue(k);
@@ -130,13 +113,13 @@ __global__ void __launch_bounds__(AM_THREADS) k_axpy_mma(const AxpyMmaP p) {
         if (!dead) {
             int spins = 0;
             bool gave_up = false;
-            while (!am_mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            while (!mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
             dead = __any_sync(0xffffffffu, gave_up) != 0;
             if (dead && lane == 0) atomicOr(p.status, 16u);
         }
         if (!dead) {
-            const uint32_t stage = am_smem_u32(ring + s * stage_bytes);
-            const uint32_t ct = am_smem_u32(coef + (size_t)k * TP * 16);
+            const uint32_t stage = smem_u32(ring + s * stage_bytes);
+            const uint32_t ct = smem_u32(coef + (size_t)k * TP * 16);
             uint32_t b[NT][2];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) am_ldmatrix_x2(b[nt], ct + (uint32_t)(nt * 8 * 16 * 2) + b_off);
@@ -154,7 +137,7 @@ __global__ void __launch_bounds__(AM_THREADS) k_axpy_mma(const AxpyMmaP p) {
         }
     }
     if (__syncthreads_or(dead) && tid == 0) {                        // do not exit with copies still landing in shared memory
-        for (int s = 0; s < S; s++) { int spins = 0; while (!am_mbar_try_wait(full + s, 0) && !am_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+        for (int s = 0; s < S; s++) { int spins = 0; while (!mbar_try_wait(full + s, 0) && !mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
     }
     // fragment element (row = column c of the slice, col = token): c0 (g, 2q) c1 (g, 2q+1) c2 (g+8, 2q) c3 (g+8, 2q+1)
     const int g4 = lane >> 2, q4 = lane & 3;
@@ -188,7 +171,7 @@ struct AxpyMmaQ4P {
 };
 
 __device__ __forceinline__ void aq_cp16(void * dst, const void * src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(am_smem_u32(dst)), "l"(src) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(dst)), "l"(src) : "memory");
 }
 
 template <int NT>
@@ -249,7 +232,7 @@ __global__ void __launch_bounds__(AM_THREADS) k_axpy_mma_q4(const AxpyMmaQ4P p) 
     const int j8 = lane >> 3;
     const uint32_t a_off = (uint32_t)((((j8 >> 1) * 8 + (lane & 7)) * AM_PITCH) + (warp * 64 + (j8 & 1) * 8) * 2);
     const uint32_t b_off = (uint32_t)((((lane & 7) * 16) + ((lane >> 3) & 1) * 8) * 2);
-    const uint32_t tile_a = am_smem_u32(tile);
+    const uint32_t tile_a = smem_u32(tile);
     const __half2 off8 = __floats2half2_rn(1032.f, 1032.f);
     for (int k = 0; k < n_tiles; k++) {
         if (k + S - 1 < n_tiles) issue(k + S - 1);                   // into the slot expanded in the previous iteration
@@ -280,7 +263,7 @@ __global__ void __launch_bounds__(AM_THREADS) k_axpy_mma_q4(const AxpyMmaQ4P p) 
             *reinterpret_cast<uint4 *>(tile + r * AM_PITCH + rem * 16) = o;
         }
         __syncthreads();
-        const uint32_t ct = am_smem_u32(coef + (size_t)k * TP * 16);
+        const uint32_t ct = smem_u32(coef + (size_t)k * TP * 16);
         uint32_t bfr[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) am_ldmatrix_x2(bfr[nt], ct + (uint32_t)(nt * 8 * 16 * 2) + b_off);

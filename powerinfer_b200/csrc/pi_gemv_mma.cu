@@ -25,23 +25,6 @@ static constexpr int MMA_THREADS = 256;
 static constexpr int MMA_WARPS = 8;
 static constexpr int MMA_MAX_TILES = 256;              // list tiles one CTA may own
 
-__device__ __forceinline__ uint32_t m_smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void m_mbar_init(uint64_t * bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(m_smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void m_mbar_expect_tx(uint64_t * bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(m_smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool m_mbar_try_wait(uint64_t * bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(m_smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void m_bulk_g2s(void * dst, const void * src, unsigned bytes, uint64_t * bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(m_smem_u32(dst)), "l"(src), "r"(bytes), "r"(m_smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
@@ -85,7 +68,7 @@ __global__ void __launch_bounds__(MMA_THREADS) k_gemv_mma(const MmaP p) {
 
     pdl_launch();
     if (tid == 0) {
-        for (int s = 0; s < S; s++) m_mbar_init(full + s, 1);
+        for (int s = 0; s < S; s++) mbar_init(full + s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -111,7 +94,7 @@ __global__ void __launch_bounds__(MMA_THREADS) k_gemv_mma(const MmaP p) {
             const int m = k / n, kk = k % n;                                              // matrix, row within the tile
             const int r = SPARSE ? rows[i * 16 + kk] : (cta + i * G) * 16 + kk;
             const uint8_t * src = (m ? p.W2 : p.W) + (size_t)r * p.row_bytes + col_off;
-            m_bulk_g2s(dstp + (size_t)(m * 16 + kk) * pitch, src, (unsigned)(KS * 2), full + s);
+            bulk_g2s(dstp + (size_t)(m * 16 + kk) * pitch, src, (unsigned)(KS * 2), full + s);
         }
     };
     auto issue_x = [&](int q) {
@@ -119,9 +102,9 @@ __global__ void __launch_bounds__(MMA_THREADS) k_gemv_mma(const MmaP p) {
         const int n = tile_rows(i);
         unsigned char * dstp = ring + (size_t)s * p.stage_bytes + (size_t)(NM * 16) * pitch;
         // the phase cannot complete before this arrive, whatever has landed already
-        if (lane == 0) m_mbar_expect_tx(full + s, (unsigned)((n * NM + p.T) * KS * 2));
+        if (lane == 0) mbar_expect_tx(full + s, (unsigned)((n * NM + p.T) * KS * 2));
         for (int t = lane; t < p.T; t += 32)
-            m_bulk_g2s(dstp + (size_t)t * pitch, p.x + (size_t)t * p.ncols + (size_t)sl * KS, (unsigned)(KS * 2), full + s);
+            bulk_g2s(dstp + (size_t)t * pitch, p.x + (size_t)t * p.ncols + (size_t)sl * KS, (unsigned)(KS * 2), full + s);
     };
 
     if (!SPARSE) {
@@ -160,11 +143,11 @@ __global__ void __launch_bounds__(MMA_THREADS) k_gemv_mma(const MmaP p) {
         if (!dead) {
             int spins = 0;
             bool gave_up = false;
-            while (!m_mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            while (!mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
             dead = __any_sync(0xffffffffu, gave_up) != 0;
             if (dead && lane == 0) atomicOr(p.status, 8u);
         }
-        const uint32_t base = m_smem_u32(ring + (size_t)s * p.stage_bytes);
+        const uint32_t base = smem_u32(ring + (size_t)s * p.stage_bytes);
         if (!dead) {
             for (int ks = warp; ks < ksteps; ks += MMA_WARPS) {
                 uint32_t a[NM][4];
@@ -223,7 +206,7 @@ __global__ void __launch_bounds__(MMA_THREADS) k_gemv_mma(const MmaP p) {
         }
     }
     if (__syncthreads_or(dead) && tid == 0) {                        // do not exit with copies still landing in shared memory
-        for (int s = 0; s < S; s++) { int spins = 0; while (!m_mbar_try_wait(full + s, 0) && !m_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+        for (int s = 0; s < S; s++) { int spins = 0; while (!mbar_try_wait(full + s, 0) && !mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
     }
 }
 

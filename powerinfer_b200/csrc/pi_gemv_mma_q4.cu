@@ -29,23 +29,6 @@ static constexpr int Q4M_THREADS = (Q4M_CWARPS + 1) * 32;   // + the serving war
 static constexpr int QK = 32;                          // values of a Q4_0 / Q8_0 block
 static constexpr int Q4M_TOK = 8;                      // tokens of one launch (the n extent of the fragment)
 
-__device__ __forceinline__ uint32_t q_smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void q_mbar_init(uint64_t * bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(q_smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void q_mbar_expect_tx(uint64_t * bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(q_smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool q_mbar_try_wait(uint64_t * bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(q_smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void q_bulk_g2s(void * dst, const void * src, unsigned bytes, uint64_t * bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(q_smem_u32(dst)), "l"(src), "r"(bytes), "r"(q_smem_u32(bar)) : "memory");
-}
 // D = A x B + C for a 16 x 32 u8 tile, a 32 x 8 s8 tile and s32 accumulators (fragment rows g and g+8, columns 2q, 2q+1)
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
                                          int k0, int k1, int k2, int k3) {
@@ -110,7 +93,7 @@ __global__ void __launch_bounds__(Q4M_THREADS, 1) k_gemv_mma_q4(const Q4mP p) {
 
     pdl_launch();
     if (tid == 0) {
-        for (int s = 0; s < S; s++) q_mbar_init(full + s, 1);
+        for (int s = 0; s < S; s++) mbar_init(full + s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -128,13 +111,13 @@ __global__ void __launch_bounds__(Q4M_THREADS, 1) k_gemv_mma_q4(const Q4mP p) {
     auto issue = [&](int i) {                                                              // all lanes of the serving warp
         const int s = i % S, n = tile_rows(i);
         unsigned char * dstp = ring + (size_t)s * p.stage_bytes;
-        if (lane == 0) q_mbar_expect_tx(full + s, (unsigned)(n * (GATED ? 2 : 1) * p.row_bytes));
+        if (lane == 0) mbar_expect_tx(full + s, (unsigned)(n * (GATED ? 2 : 1) * p.row_bytes));
         __syncwarp();
         for (int k = lane; k < n * (GATED ? 2 : 1); k += 32) {
             const int m = k / n, kk = k % n;                                               // matrix, item within the tile
             const int r = SPARSE ? rows[i * IT + kk] : (cta + i * G) * IT + kk;
             const uint8_t * src = (m ? p.W2 : p.W) + (size_t)r * p.row_bytes;
-            q_bulk_g2s(dstp + (size_t)(m * IT + kk) * pitch, src, (unsigned)p.row_bytes, full + s);
+            bulk_g2s(dstp + (size_t)(m * IT + kk) * pitch, src, (unsigned)p.row_bytes, full + s);
         }
     };
 
@@ -202,7 +185,7 @@ __global__ void __launch_bounds__(Q4M_THREADS, 1) k_gemv_mma_q4(const Q4mP p) {
             {
                 int spins = 0;
                 bool gave_up = false;
-                while (!q_mbar_try_wait(full + s, (unsigned)(i / S) & 1u)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+                while (!mbar_try_wait(full + s, (unsigned)(i / S) & 1u)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
                 dead = __any_sync(0xffffffffu, gave_up) != 0;
                 if (dead && lane == 0) atomicOr(p.status, 8u);
             }
@@ -313,7 +296,7 @@ __global__ void __launch_bounds__(Q4M_THREADS, 1) k_gemv_mma_q4(const Q4mP p) {
     }
     __syncthreads();
     if (tid == 0 && (*(volatile unsigned int *)p.status & 8u)) {     // do not exit with copies still landing in shared memory
-        for (int s = 0; s < S; s++) { int spins = 0; while (!q_mbar_try_wait(full + s, 0) && !q_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+        for (int s = 0; s < S; s++) { int spins = 0; while (!mbar_try_wait(full + s, 0) && !mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
     }
 }
 

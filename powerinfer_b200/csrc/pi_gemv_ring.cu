@@ -21,23 +21,6 @@ static constexpr int RING_WARPS = 8;
 static constexpr int RING_MAX_ITEMS = 1024;            // list entries one CTA may own
 static constexpr int RING_MAX_VEC = 128;               // row vectors in one stage (rows x matrices)
 
-__device__ __forceinline__ uint32_t r_smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void r_mbar_init(uint64_t * bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(r_smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void r_mbar_expect_tx(uint64_t * bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(r_smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool r_mbar_try_wait(uint64_t * bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(r_smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void r_bulk_g2s(void * dst, const void * src, unsigned bytes, uint64_t * bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(r_smem_u32(dst)), "l"(src), "r"(bytes), "r"(r_smem_u32(bar)) : "memory");
-}
 
 struct RingP {
     const uint8_t * W; const uint8_t * W2;
@@ -350,7 +333,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
 
     pdl_launch();                                                   // let the next kernel become resident and prefetch
     if (tid == 0) {
-        for (int s = 0; s < S; s++) r_mbar_init(full + s, 1);
+        for (int s = 0; s < S; s++) mbar_init(full + s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -366,16 +349,16 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
         unsigned char * dstp = ring + (size_t)s * p.stage_bytes;
         if (!SPARSE) {
             if (lane == 0) {
-                r_mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
-                r_bulk_g2s(dstp, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
+                mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
+                bulk_g2s(dstp, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
             }
         } else {
             // the phase cannot complete before the arrive below, whatever the order in which the lanes' copies land
-            if (lane == 0) r_mbar_expect_tx(full + s, (unsigned)(n * NM * p.row_bytes));
+            if (lane == 0) mbar_expect_tx(full + s, (unsigned)(n * NM * p.row_bytes));
             for (int k = lane; k < n; k += 32) {
                 const int r = items[st * R + k];
-                r_bulk_g2s(dstp + (size_t)k * p.row_bytes, p.W + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
-                if (GATED) r_bulk_g2s(dstp + (size_t)(R + k) * p.row_bytes, p.W2 + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
+                bulk_g2s(dstp + (size_t)k * p.row_bytes, p.W + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
+                if (GATED) bulk_g2s(dstp + (size_t)(R + k) * p.row_bytes, p.W2 + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
             }
         }
     };
@@ -433,7 +416,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
         if (!dead) {
             int spins = 0;
             bool gave_up = false;
-            while (!r_mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            while (!mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
             dead = __any_sync(0xffffffffu, gave_up) != 0;            // the whole warp agrees, so no shuffle runs half-populated
             if (dead && lane == 0) atomicOr(p.status, 4u);
         }
@@ -484,7 +467,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
         }
     }
     if (__syncthreads_or(dead) && tid == 0) {                       // do not exit with copies still landing in shared memory
-        for (int s = 0; s < S; s++) { int spins = 0; while (!r_mbar_try_wait(full + s, 0) && !r_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+        for (int s = 0; s < S; s++) { int spins = 0; while (!mbar_try_wait(full + s, 0) && !mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
     }
 }
 
@@ -493,9 +476,6 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
 // when it is done: only warp 0, which refills the stage, waits for the others; the rest go straight on to the next stage.
 // Halving the stage size in the kernel above costs 1.7 ms per 70B-shape token: its per-stage block barrier, shared-memory
 // exchange of partial sums and result hand-off are a fixed cost comparable to the stage's streaming time.
-__device__ __forceinline__ void r_mbar_arrive(uint64_t * bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(r_smem_u32(bar)) : "memory");
-}
 
 template <int WT>
 __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
@@ -511,7 +491,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
 
     pdl_launch();
     if (tid == 0) {
-        for (int s = 0; s < S; s++) { r_mbar_init(full + s, 1); r_mbar_init(empty + s, RING_WARPS); }
+        for (int s = 0; s < S; s++) { mbar_init(full + s, 1); mbar_init(empty + s, RING_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -522,8 +502,8 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
     auto stage_first = [&](int st) { return (cta + st * G) * R; };
     auto issue = [&](int st) {                                       // lane 0 of warp 0
         const int s = st % S, first = stage_first(st), n = min(R, n_items - first);
-        r_mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
-        r_bulk_g2s(ring + (size_t)s * p.stage_bytes, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
+        mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
+        bulk_g2s(ring + (size_t)s * p.stage_bytes, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
     };
     if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);   // weights need no producer: before the wait
     pdl_wait();
@@ -557,7 +537,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
         if (!dead) {
             int spins = 0;
             bool gave_up = false;
-            while (!r_mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            while (!mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
             dead = __any_sync(0xffffffffu, gave_up) != 0;
             if (dead && lane == 0) atomicOr(p.status, 4u);
         }
@@ -581,17 +561,17 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
             }
         }
         __syncwarp();
-        if (lane == 0) r_mbar_arrive(empty + s);                     // this warp is done with stage s (also when it gave up)
+        if (lane == 0) mbar_arrive(empty + s);                     // this warp is done with stage s (also when it gave up)
         if (warp == 0 && st + S < n_stages) {                        // refill: wait (bounded) until every warp has arrived
             int spins = 0;
             bool gave_up = false;
-            while (!r_mbar_try_wait(empty + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            while (!mbar_try_wait(empty + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
             if (gave_up) { if (lane == 0) atomicOr(p.status, 4u); }
             else if (lane == 0 && !dead) issue(st + S);
         }
     }
     if (__syncthreads_or(dead) && tid == 0) {                       // do not exit with copies still landing in shared memory
-        for (int s = 0; s < S; s++) { int spins = 0; while (!r_mbar_try_wait(full + s, 0) && !r_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+        for (int s = 0; s < S; s++) { int spins = 0; while (!mbar_try_wait(full + s, 0) && !mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
     }
 }
 
@@ -616,7 +596,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_g(const RingP p) {
 
     pdl_launch();
     if (tid == 0) {
-        for (int s = 0; s < S; s++) { r_mbar_init(full + s, 1); r_mbar_init(empty + s, RING_WARPS); }
+        for (int s = 0; s < S; s++) { mbar_init(full + s, 1); mbar_init(empty + s, RING_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -628,15 +608,15 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_g(const RingP p) {
         unsigned char * dstp = ring + (size_t)s * p.stage_bytes;
         if (!SPARSE) {
             if (lane == 0) {
-                r_mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
-                r_bulk_g2s(dstp, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
+                mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
+                bulk_g2s(dstp, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
             }
         } else {
-            if (lane == 0) r_mbar_expect_tx(full + s, (unsigned)(n * NM * p.row_bytes));
+            if (lane == 0) mbar_expect_tx(full + s, (unsigned)(n * NM * p.row_bytes));
             for (int k = lane; k < n; k += 32) {
                 const int r = items[st * R + k];
-                r_bulk_g2s(dstp + (size_t)k * p.row_bytes, p.W + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
-                if (GATED) r_bulk_g2s(dstp + (size_t)(R + k) * p.row_bytes, p.W2 + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
+                bulk_g2s(dstp + (size_t)k * p.row_bytes, p.W + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
+                if (GATED) bulk_g2s(dstp + (size_t)(R + k) * p.row_bytes, p.W2 + (size_t)r * p.row_bytes, (unsigned)p.row_bytes, full + s);
             }
         }
     };
@@ -693,7 +673,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_g(const RingP p) {
         if (!dead) {
             int spins = 0;
             bool gave_up = false;
-            while (!r_mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            while (!mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
             dead = __any_sync(0xffffffffu, gave_up) != 0;
             if (dead && lane == 0) atomicOr(p.status, 4u);
         }
@@ -727,17 +707,17 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_g(const RingP p) {
             if (p.dst16) p.dst16[g] = __float2half_rn(o);
         }
         __syncwarp();
-        if (lane == 0) r_mbar_arrive(empty + s);
+        if (lane == 0) mbar_arrive(empty + s);
         if (warp == 0 && st + S < n_stages) {
             int spins = 0;
             bool gave_up = false;
-            while (!r_mbar_try_wait(empty + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
+            while (!mbar_try_wait(empty + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
             if (gave_up) { if (lane == 0) atomicOr(p.status, 4u); }
             else if (!dead) issue(st + S);
         }
     }
     if (__syncthreads_or(dead) && tid == 0) {
-        for (int s = 0; s < S; s++) { int spins = 0; while (!r_mbar_try_wait(full + s, 0) && !r_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+        for (int s = 0; s < S; s++) { int spins = 0; while (!mbar_try_wait(full + s, 0) && !mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
     }
 }
 

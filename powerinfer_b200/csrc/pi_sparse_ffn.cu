@@ -20,23 +20,6 @@ static constexpr int FFN_THREADS = 1024;
 static constexpr int FFN_WARPS = 32;
 static constexpr int FFN_MAX_ROWS = 512;               // active rows one CTA may own
 
-__device__ __forceinline__ uint32_t f_smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void f_mbar_init(uint64_t * bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(f_smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void f_mbar_expect_tx(uint64_t * bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(f_smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool f_mbar_try_wait(uint64_t * bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(f_smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void f_bulk_g2s(void * dst, const void * src, unsigned bytes, uint64_t * bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(f_smem_u32(dst)), "l"(src), "r"(bytes), "r"(f_smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ float f_nib(uint32_t bytes, int k) {
     return __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7650u | (uint32_t)k)) - 8388616.0f;
 }
@@ -84,7 +67,7 @@ __global__ void __launch_bounds__(FFN_THREADS) k_sparse_ffn(const FfnP p) {
 
     pdl_launch();
     if (tid == 0) {
-        for (int s = 0; s < S; s++) f_mbar_init(full + s, 1);
+        for (int s = 0; s < S; s++) mbar_init(full + s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -126,7 +109,7 @@ __global__ void __launch_bounds__(FFN_THREADS) k_sparse_ffn(const FfnP p) {
         int first, cnt;
         if (st < n_st1) { first = st * J; cnt = min(J, jobs1 - first); }
         else            { first = (st - n_st1) * J; cnt = min(J, n_rows - first); }
-        f_mbar_expect_tx(full + s, (unsigned)(cnt * p.row_bytes));
+        mbar_expect_tx(full + s, (unsigned)(cnt * p.row_bytes));
         for (int k = 0; k < cnt; k++) {
             const uint8_t * src;
             if (st < n_st1) {
@@ -136,7 +119,7 @@ __global__ void __launch_bounds__(FFN_THREADS) k_sparse_ffn(const FfnP p) {
             } else {
                 src = p.down + (size_t)rows[first + k] * p.row_bytes;
             }
-            f_bulk_g2s(dstp + (size_t)k * p.row_stride, src, (unsigned)p.row_bytes, full + s);
+            bulk_g2s(dstp + (size_t)k * p.row_stride, src, (unsigned)p.row_bytes, full + s);
         }
     };
     if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
@@ -164,7 +147,7 @@ __global__ void __launch_bounds__(FFN_THREADS) k_sparse_ffn(const FfnP p) {
         const int s = st % S;
         const unsigned parity = (unsigned)(st / S) & 1u;
         int spins = 0;
-        while (!f_mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { dead = true; atomicOr(p.status, 8u); break; } }
+        while (!mbar_try_wait(full + s, parity)) { if (++spins > (1 << 20)) { dead = true; atomicOr(p.status, 8u); break; } }
     };
 
     // ---- pass 1: dot products.  W warps share one job; their partial sums meet in shared memory.
@@ -293,7 +276,7 @@ __global__ void __launch_bounds__(FFN_THREADS) k_sparse_ffn(const FfnP p) {
         if (tid == 0 && st + S < n_stages) issue(st + S);
     }
     if (__syncthreads_or(dead) && tid == 0) {             // something timed out: give outstanding copies a bounded chance to land
-        for (int s = 0; s < S; s++) { int spins = 0; while (!f_mbar_try_wait(full + s, 0) && !f_mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
+        for (int s = 0; s < S; s++) { int spins = 0; while (!mbar_try_wait(full + s, 0) && !mbar_try_wait(full + s, 1) && ++spins < (1 << 16)) {} }
     }
 
     float * out = p.partial + (size_t)cta * p.ncols;
