@@ -20,7 +20,6 @@
 namespace pi {
 
 static constexpr int AM_THREADS = 512;
-static constexpr int AM_WARPS = 16;
 static constexpr int AM_CW = 1024;                     // columns per CTA
 static constexpr int AM_PITCH = AM_CW * 2 + 16;
 

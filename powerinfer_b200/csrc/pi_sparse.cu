@@ -297,7 +297,6 @@ __global__ void __launch_bounds__(AXPY_Q4_THREADS) k_axpy_q4(const AxpyP p) {
 // int8 quant of h within its block of 32 neurons times that block's FP16 scale (ggml.c:14575-14581).
 // Every mbarrier wait is bounded; if one runs out the CTA raises bit 1 of *status, stops consuming and still writes
 // its partial, so a lost copy can never hang the GPU.
-static constexpr int PIPE_THREADS = 256;
 static constexpr int PIPE_MAX_ROWS = 512;               // list entries one CTA may own (F / G, rounded up)
 
 struct AxpyPipeP {
