@@ -1,6 +1,5 @@
 """PowerInfer GGUF model files and placement files: what the loader reads is what the generator wrote (CPU only)."""
 import dataclasses
-import os
 
 import numpy as np
 import pytest
