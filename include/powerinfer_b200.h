@@ -167,13 +167,14 @@ int pi_attention_decode(const float * q, const float * k, const float * v, void 
 /* ---- the decode token loop ------------------------------------------------------------------------------ */
 
 /* One step of llama_decode (llama.cpp:6764-7006) over device-resident weights for up to max_batch sequences, one new
- * token each (examples/batched-bench/batched-bench.cpp:205-216), for the three sparse architectures the reference
- * builds graphs for: llama (llama.cpp:4949-5084), falcon (5326-5468), opt (5086-5204).  The launch sequence of a step
+ * token each (examples/batched-bench/batched-bench.cpp:205-216), for the sparse architectures the reference builds
+ * graphs for: llama and its bamboo variant (llama.cpp:4949-5084), falcon (5326-5468), opt (5086-5204).  The launch sequence of a step
  * is captured once per batch size and replayed as a CUDA graph. */
 
 #define PI_ARCH_LLAMA   0
 #define PI_ARCH_FALCON  1
 #define PI_ARCH_OPT     2
+#define PI_ARCH_BAMBOO  3   /* the llama graph with the symmetric gate h = relu(gate) * relu(up) (LLM_FFN_SYM, llama.cpp:4732-4738, 5028) */
 #define PI_MAX_BATCH    32
 #define PI_MAX_RANKS    8
 

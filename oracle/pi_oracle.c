@@ -450,7 +450,10 @@ static void ffn_sparse(pio_ctx * c, const pio_layer * L, const float * ffn_input
     add_bias(c->up, L->up_b, F);
     if (L->gate) {
         pio_mul_mat_idx(m->wtype, L->gate, F, d, ffn_input, 1, c->pred, F, NULL, m->threshold, c->gate);
-        for (int64_t i = 0; i < F; i++) c->hbuf[i] = (c->gate[i] > 0.0f ? c->gate[i] : 0.0f) * c->up[i];
+        for (int64_t i = 0; i < F; i++) {                                     /* llama.cpp:4725-4738: LLM_FFN_PAR | LLM_FFN_SYM */
+            const float u = m->gate_sym ? (c->up[i] > 0.0f ? c->up[i] : 0.0f) : c->up[i];
+            c->hbuf[i] = (c->gate[i] > 0.0f ? c->gate[i] : 0.0f) * u;
+        }
     } else {
         for (int64_t i = 0; i < F; i++) c->hbuf[i] = c->up[i] > 0.0f ? c->up[i] : 0.0f;
     }

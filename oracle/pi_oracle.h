@@ -94,6 +94,8 @@ typedef struct {
     const float * out_norm_w, * out_norm_b;
     const void  * output;                          /* lm head [n_vocab, d] in wtype (OPT: NULL -> tied to tok_embd, F16) */
     const pio_layer * layers;
+    int gate_sym;                                  /* llama graph of the "bamboo" architecture: h = relu(gate) * relu(up)
+                                                    * (LLM_FFN_SYM, llama.cpp:4732-4738, 5028) instead of relu(gate) * up */
 } pio_model;
 
 typedef struct pio_ctx pio_ctx;

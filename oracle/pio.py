@@ -205,7 +205,7 @@ class _Model(C.Structure):
                 ("n_head", C.c_int), ("n_head_kv", C.c_int), ("rank", C.c_int), ("n_vocab", C.c_int), ("n_ctx", C.c_int),
                 ("norm_eps", C.c_float), ("rope_base", C.c_float), ("threshold", C.c_float),
                 ("tok_embd", _vp), ("pos_embd", _vp), ("out_norm_w", _vp), ("out_norm_b", _vp), ("output", _vp),
-                ("layers", C.POINTER(_Layer))]
+                ("layers", C.POINTER(_Layer)), ("gate_sym", C.c_int)]
 
 
 class OracleModel:
@@ -233,7 +233,7 @@ class OracleModel:
         self.m = _Model(spec.arch, spec.wtype, spec.n_layer, spec.d, spec.n_ff, spec.n_head, spec.n_head_kv,
                         spec.rank, spec.n_vocab, spec.n_ctx, spec.norm_eps, spec.rope_base, spec.threshold,
                         g("token_embd.weight"), g("position_embd.weight"), g("output_norm.weight"),
-                        g("output_norm.bias"), g("output.weight"), self.layers)
+                        g("output_norm.bias"), g("output.weight"), self.layers, int(getattr(spec, "gate_sym", False)))
         self.ctx = _vp(self.o.lib.pio_ctx_new(C.byref(self.m)))
 
     def decode(self, token: int, pos: int, want_pred: bool = False):

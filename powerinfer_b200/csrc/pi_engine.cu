@@ -124,6 +124,7 @@ struct pi_engine {
     float * pred_trace;                      // optional [n_layer, max_batch, F]: keeps every layer's predictor logits
     bool pdl;                                // programmatic dependent launch between the kernels of a step
     bool fuse;                               // batch 1: consumers build their own normalised input (no norm launches)
+    bool gate_sym;                           // bamboo: relu on the gated product as well
     bool ffn_fused;                          // batch 1: one kernel for up/gate + activation + down (PI_FFN_FUSED=1; off by default: parity-green but measured slower than the two-kernel path)
     int32_t * parts, * chunk_off;            // balanced chunk split made by the compaction for that kernel
     // Weight streamer (PI_PREFETCH=1; off by default): a second stream (a parallel branch of the step's graph) whose
@@ -182,7 +183,7 @@ static void carve(pi_engine * e, void * ws, size_t ws_bytes, bool dry, size_t * 
 }
 
 static int validate(const pi_engine_config & c) {
-    PI_REQUIRE(c.arch >= 0 && c.arch <= 2, "engine: unknown arch %d", c.arch);
+    PI_REQUIRE(c.arch >= 0 && c.arch <= PI_ARCH_BAMBOO, "engine: unknown arch %d", c.arch);
     PI_REQUIRE(c.wtype == PI_TYPE_F16 || c.wtype == PI_TYPE_Q4_0, "engine: unknown weight type %d", c.wtype);
     PI_REQUIRE(c.n_layer > 0 && c.d > 0 && c.n_ff > 0 && c.n_head > 0 && c.n_head_kv > 0 && c.rank > 0 && c.n_vocab > 0 && c.n_ctx > 0,
                "engine: non-positive dimension");
@@ -230,6 +231,10 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
     pi_engine * e = new (std::nothrow) pi_engine();
     PI_REQUIRE(e, "engine_create: out of host memory");
     e->c = *cfg; e->g = *gw;
+    // bamboo is the llama graph; relu(gate) * relu(up) == relu(relu(gate) * up) exactly (the first factor is >= 0), so the
+    // gated mat-vec's own relu-on-output switch gives the symmetric gate
+    e->gate_sym = cfg->arch == PI_ARCH_BAMBOO;
+    if (e->gate_sym) e->c.arch = PI_ARCH_LLAMA;
     e->layers.assign(lw, lw + cfg->n_layer);
     e->hd = cfg->d / cfg->n_head; e->dq = cfg->d / cfg->n_ranks; e->dkv = e->hd * cfg->n_head_kv / cfg->n_ranks;
     e->F = cfg->n_ff / cfg->n_ranks; e->T_max = cfg->max_batch;
@@ -558,7 +563,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
         // ---- mask -> active list (and, for batch 1, a balanced split of the 32-neuron chunks over the SMs).
         //      Where a row is inactive for a token the dense hidden vector holds 0 (or relu(bias)): the Q4_0 axpy quantises
         //      that vector per 32 neurons, and a union list leaves per-token holes.
-        const bool fuse_ffn = T == 1 && e->ffn_fused;
+        const bool fuse_ffn = T == 1 && e->ffn_fused && !e->gate_sym;          // the one-kernel FFN has the parallel gate only
         {
             CompactArgs ca;
             ca.pdl = pdl;
@@ -591,7 +596,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             g.status = e->status; g.pdl = pdl;
             g.wtype = wt; g.W = L->up; g.W2 = L->gate; g.nrows = F; g.ncols = d; g.x = e->act_a.view(); g.T = T;
             g.list = e->list; g.count = e->count; g.idx = pred; g.idx_stride = F; g.threshold = c.threshold;
-            g.bias = L->up_b; g.relu = L->gate ? 0 : 1;
+            g.bias = L->up_b; g.relu = L->gate ? (e->gate_sym ? 1 : 0) : 1;
             g.dst = e->h; g.dst_stride = F;
             STAGE(PI_STAGE_UPGATE, (T + 7) / 8, launch_gemv(g, st));
         }
@@ -738,7 +743,7 @@ int enqueue_step_fused(pi_engine * e, cudaStream_t st, StageTimer & tm) {
             else        { g.fin.w = L->ffn_norm_w;  g.fin.b = L->ffn_norm_b;  g.fin.stats = stats_of(il, 1); }
             g.wtype = wt; g.W = L->up; g.W2 = L->gate; g.nrows = F; g.ncols = d; g.T = T;
             g.list = e->list; g.count = e->count; g.idx = pred; g.idx_stride = F; g.threshold = c.threshold;
-            g.bias = L->up_b; g.relu = L->gate ? 0 : 1;
+            g.bias = L->up_b; g.relu = L->gate ? (e->gate_sym ? 1 : 0) : 1;
             g.dst = e->h; g.dst_stride = F;
             STAGE(PI_STAGE_UPGATE, 1, launch_gemv(g, st));
         }

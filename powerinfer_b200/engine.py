@@ -17,6 +17,7 @@ from . import synth
 from ._lib import PI_TYPE_F16, PI_TYPE_Q4_0, check, lib
 
 PI_MAX_RANKS = 8
+PI_ARCH_BAMBOO = 3                     # the llama graph with the symmetric gate relu(gate) * relu(up)
 N_STAGES = 11
 STAGE_NAMES = ["norm", "qkv", "attention", "out_proj", "predictor", "compact", "up_gate", "down", "lm_head", "exchange", "other"]
 
@@ -120,7 +121,7 @@ class DecodeEngine:
                  local_layers: list | None = None):
         self.spec, self.max_batch, self.n_ranks, self.rank = spec, max_batch, n_ranks, rank
         n_pos = synth.OPT_N_POS if spec.arch == synth.ARCH_OPT else 0
-        self.cfg = EngineConfig(spec.arch, spec.wtype, spec.n_layer, spec.d, spec.n_ff, spec.n_head, spec.n_head_kv, spec.rank,
+        self.cfg = EngineConfig(PI_ARCH_BAMBOO if getattr(spec, "gate_sym", False) else spec.arch, spec.wtype, spec.n_layer, spec.d, spec.n_ff, spec.n_head, spec.n_head_kv, spec.rank,
                                 spec.n_vocab, spec.n_ctx, n_pos, spec.norm_eps, spec.rope_base, spec.threshold, max_batch,
                                 n_ranks, rank)
         ws_bytes = lib.pi_engine_workspace_bytes(C.byref(self.cfg))

@@ -103,7 +103,8 @@ def read_gguf(path: str):
     return magic, kv, tensors
 
 
-_ARCH = {"llama": synth.ARCH_LLAMA, "falcon": synth.ARCH_FALCON, "opt": synth.ARCH_OPT}
+# "bamboo" is the llama graph with the symmetric gate (llama.cpp:2354-2355, 5028)
+_ARCH = {"llama": synth.ARCH_LLAMA, "bamboo": synth.ARCH_LLAMA, "falcon": synth.ARCH_FALCON, "opt": synth.ARCH_OPT}
 
 
 def load_model(path: str):
@@ -116,7 +117,7 @@ def load_model(path: str):
     magic, kv, t = read_gguf(path)
     arch_name = kv.get("general.architecture")
     if arch_name not in _ARCH:
-        raise ValueError(f"{path}: architecture {arch_name!r} is not one of llama / falcon / opt")
+        raise ValueError(f"{path}: architecture {arch_name!r} is not one of llama / bamboo / falcon / opt")
     for need in ("blk.0.ffn_down_t.weight", "blk.0.fc1.weight", "blk.0.fc2.weight"):
         if need not in t:
             raise ValueError(f"{path}: {need} is missing: not a PowerInfer (sparse) model file")
@@ -133,7 +134,7 @@ def load_model(path: str):
                            rank=int(t["blk.0.fc1.weight"].shape[0]), n_vocab=int(t["token_embd.weight"].shape[0]),
                            n_ctx=int(k("context_length", 512)), norm_eps=eps, rope_base=float(k("rope.freq_base", 10000.0)),
                            threshold=float(kv.get("powerinfer.sparse_threshold", 0.0)),
-                           falcon_two_norms="blk.0.attn_norm_2.weight" in t)
+                           falcon_two_norms="blk.0.attn_norm_2.weight" in t, gate_sym=arch_name == "bamboo")
     return spec, t
 
 

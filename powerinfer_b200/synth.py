@@ -53,6 +53,13 @@ class ModelSpec:
     sigma: float = 0.02
     seed: int = 0
     falcon_two_norms: bool = True
+    gate_sym: bool = False        # llama graph with the symmetric gate relu(gate) * relu(up): the reference's "bamboo"
+                                  # architecture (llama.cpp:4732-4738, 5028); everything else is the llama graph
+
+    @property
+    def arch_name(self) -> str:
+        """general.architecture of the model file the reference loads for this spec"""
+        return "bamboo" if self.gate_sym else ARCH_NAMES[self.arch]
 
     @property
     def head_dim(self) -> int:

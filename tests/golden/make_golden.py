@@ -35,6 +35,7 @@ MODEL_CASES = {
     "falcon_f16": synth.ModelSpec(arch=synth.ARCH_FALCON, wtype=synth.F16, n_head=8, n_head_kv=2, d=512, n_ff=2048,
                                   seed=14),
     "opt_f16": synth.ModelSpec(arch=synth.ARCH_OPT, wtype=synth.F16, seed=15, norm_eps=0.0),
+    "bamboo_f16": synth.ModelSpec(arch=synth.ARCH_LLAMA, wtype=synth.F16, gate_sym=True, seed=16),
 }
 
 
@@ -89,7 +90,7 @@ def write_gguf(spec, tensors, path):
     V = spec.n_vocab
     toks = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + [f"tok{i}" for i in range(V - 259)]
     types = [2, 3, 3] + [6] * 256 + [1] * (V - 259)
-    arch = synth.ARCH_NAMES[spec.arch]
+    arch = spec.arch_name
     w = gguf.GGUFWriter(path, arch)
     w.add_name("synthetic-" + arch)
     w.add_context_length(2050 if spec.arch == synth.ARCH_OPT else spec.n_ctx)
@@ -140,9 +141,7 @@ def run_ref_decode(gguf_path, tokens, n_prompt, n_steps, n_vocab, mode="batch", 
     return logits, greedy
 
 
-def main():
-    from oracle import pio
-    ref = pio.Ref()
+def write_op_fixtures(ref):
     out = {}
     for name, c in op_cases().items():
         x, W, Wt, idx = op_inputs(c)
@@ -166,7 +165,15 @@ def main():
     np.savez_compressed(os.path.join(HERE, "ops.npz"), **out)
     print("ops.npz:", len(out), "arrays")
 
+
+def main():
+    from oracle import pio
+    only = set(sys.argv[1:])          # model cases to (re)generate; none named: everything, the op fixtures included
+    if not only:
+        write_op_fixtures(pio.Ref())
     for name, spec in MODEL_CASES.items():
+        if only and name not in only:
+            continue
         tensors = synth.build_model(spec)
         prompt = prompt_for(spec)
         with tempfile.TemporaryDirectory() as td:

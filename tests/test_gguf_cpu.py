@@ -9,7 +9,7 @@ from powerinfer_b200 import gguf_loader as gl
 from powerinfer_b200 import placement, synth
 
 
-@pytest.mark.parametrize("name", ["llama_q4_0", "llama_gqa_f16", "falcon_f16", "opt_f16"])
+@pytest.mark.parametrize("name", ["llama_q4_0", "llama_gqa_f16", "falcon_f16", "opt_f16", "bamboo_f16"])
 def test_model_file_round_trip(tmp_path, name):
     pytest.importorskip("gguf")
     spec = mg.MODEL_CASES[name]
@@ -19,7 +19,7 @@ def test_model_file_round_trip(tmp_path, name):
     assert open(path, "rb").read(4) == b"PWRI"
     spec2, t2 = gl.load_model(path)
     a, b = dataclasses.asdict(spec), dataclasses.asdict(spec2)
-    for k in ("arch", "wtype", "n_layer", "d", "n_ff", "n_head", "n_head_kv", "rank", "n_vocab", "threshold", "rope_base"):
+    for k in ("arch", "gate_sym", "wtype", "n_layer", "d", "n_ff", "n_head", "n_head_kv", "rank", "n_vocab", "threshold", "rope_base"):
         assert a[k] == b[k], k
     assert np.float32(a["norm_eps"]) == np.float32(b["norm_eps"])
     assert synth.digest(t) == synth.digest({k: np.asarray(v) for k, v in t2.items()})
