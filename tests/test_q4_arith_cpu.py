@@ -53,3 +53,32 @@ def test_block_dot_operand_order_matches_the_cpu_dot():
             acc = acc + term[:, b]
         out[t] = acc
     assert np.abs(out - ref).max() <= 2e-5, np.abs(out - ref).max()
+
+
+def test_batch_1_axpy_nibble_to_float_trick_costs_about_four_bits():
+    """csrc/pi_sparse.cu (k_axpy_pipe, Q4_0 rows): nibble q becomes the float 0.5 + q/256 by one byte permute, the weight
+    term is accumulated as (0.5 + q/256) * (256 c d) and 0.53125 * sum(256 c d) is subtracted once per column at the end.
+    Restated in float32 (fma emulated through float64): the result stays within 5e-6 of sum |8 c d| of the exact sum."""
+    rng = np.random.default_rng(0)
+
+    def fmaf(a, b, c):
+        return np.float32(np.float64(a) * np.float64(b) + np.float64(c))
+
+    worst = 0.0
+    for _ in range(200):
+        n = int(rng.integers(1, 64))                                              # rows one CTA accumulates
+        q = rng.integers(0, 16, n)
+        c = (rng.standard_normal(n) * 0.5).astype(np.float32)                     # coefficient of the row
+        d = np.float16(np.abs(rng.standard_normal(n)) * 0.01 + 1e-3).astype(np.float32)
+        acc, corr = np.float32(0), np.float32(0)
+        for i in range(n):
+            sc = np.float32(np.float32(np.float32(256.0) * c[i]) * d[i])
+            corr = np.float32(corr + sc)
+            val = np.array([0x3F000000 | (int(q[i]) << 16)], np.uint32).view(np.float32)[0]
+            assert val == np.float32(0.5 + q[i] / 256.0)
+            acc = fmaf(val, sc, acc)
+        acc = fmaf(np.float32(-0.53125), corr, acc)
+        exact = np.sum((q - 8).astype(np.float64) * c.astype(np.float64) * d.astype(np.float64))
+        scale = np.sum(np.abs(c.astype(np.float64) * d.astype(np.float64))) * 8
+        worst = max(worst, abs(float(acc) - exact) / scale)
+    assert worst <= 5e-6, worst
