@@ -1,4 +1,5 @@
-"""The arithmetic the Q4_0 tensor-core mat-mat (csrc/pi_gemv_mma_q4.cu) relies on, restated in numpy and checked on the CPU:
+"""Arithmetic shortcuts of the Q4_0 kernels restated in numpy and checked on the CPU.  The tensor-core mat-mat
+(csrc/pi_gemv_mma_q4.cu) relies on:
 
 * operand order: the low nibbles of a block's 16 bytes pair with Q8_0 values 0..15, the high nibbles with 16..31, so one
   integer dot per block over (nibbles, int8) minus 8 x (sum of the int8) is the block term of vec_dot_q4_0_q8_0
