@@ -286,6 +286,36 @@ int  pi_engine_set_trace(pi_engine * e, float * pred_trace);
 int  pi_engine_active_total(pi_engine * e, int reset, unsigned long long * host_total, void * stream);
 int  pi_engine_launches(pi_engine * e);                            /* kernels enqueued by one step of the last batch size run */
 
+/* ---- model and placement files (host only: no device is touched) -------------------------------------- */
+
+/* Reader for the reference's files: PowerInfer model files (GGUF v2 / v3 container with the magic PWRI, ggml.c:19481-19495;
+ * tensors and keys as llm_load_hparams / llm_load_sparse_model_tensors read them, llama.cpp:2330-2400, 3159-3390) and
+ * `.generated.gpuidx` placement files (architecture generic.gpu_index, blk.i.gpu_idx / blk.i.gpu_bucket int32 tensors,
+ * split.vram_capacity; llama.cpp:2781-2871).  The file is mapped read-only; tensor data pointers point into the mapping
+ * and stay valid until pi_model_file_close.  Uploading is the caller's business (F16 as stored; Q4_0 through
+ * pi_q4_0_repack).  Malformed or truncated files give PI_ERR_INVALID, never a crash. */
+typedef struct pi_model_file pi_model_file;
+int     pi_model_file_open(const char * path, pi_model_file ** out);
+void    pi_model_file_close(pi_model_file * f);
+int     pi_model_file_is_powerinfer(const pi_model_file * f);       /* 1: magic PWRI, 0: plain GGUF */
+/* Key lookups.  PI_ERR_INVALID when the key is absent or holds another kind of value.  Any integer or bool type
+ * answers get_u64 (negative values are refused); F32 / F64 answer get_f32; the string is NOT NUL-terminated. */
+int     pi_model_file_get_u64(const pi_model_file * f, const char * key, uint64_t * value);
+int     pi_model_file_get_f32(const pi_model_file * f, const char * key, float * value);
+int     pi_model_file_get_str(const pi_model_file * f, const char * key, const char ** str, size_t * len);
+/* Tensors: ggml_type as in enum ggml_type (ggml.h:307-333: 0 F32, 1 F16, 2 Q4_0, 18 I32), ne[4] with ne[0] the fastest
+ * dimension (unused dimensions 1), nbytes 0 and data NULL for types whose size this reader does not know. */
+int64_t pi_model_file_n_tensors(const pi_model_file * f);
+int     pi_model_file_tensor_at(const pi_model_file * f, int64_t i, const char ** name, int * ggml_type, int64_t ne[4],
+                                const void ** data, size_t * nbytes);
+int     pi_model_file_tensor(const pi_model_file * f, const char * name, int * ggml_type, int64_t ne[4],
+                             const void ** data, size_t * nbytes);
+/* The hyper-parameters of a sparse model file as an engine configuration for one GPU and one sequence (max_batch 1,
+ * n_ranks 1): architecture (llama / bamboo / falcon / opt), weight type of blk.0.ffn_up, dimensions, norm epsilon key of
+ * the architecture, rope base, powerinfer.sparse_threshold, predictor rank = rows of blk.0.fc1, vocabulary = rows of
+ * token_embd.  PI_ERR_INVALID when the file is not a sparse model (no fc1 / fc2 / ffn_down_t tensors). */
+int     pi_model_file_engine_config(const pi_model_file * f, pi_engine_config * cfg);
+
 /* ---- plumbing for multi-GPU mailboxes (these DO allocate; nothing else does) ----------------------------- */
 int  pi_device_malloc(void ** ptr, size_t bytes);                  /* cudaMalloc + zero fill */
 int  pi_device_free(void * ptr);

@@ -60,4 +60,4 @@ EXPORTS = ["pi_last_error", "pi_version", "pi_row_bytes", "pi_workspace_bytes", 
 
 def check(rc: int) -> None:
     if rc != 0:
-        raise PiError(f"powerinfer_b200 error {rc}: {lib.pi_last_error().decode()}")
+        raise PiError(f"powerinfer_b200 error {rc}: {lib.pi_last_error().decode("utf-8", errors="replace")}")

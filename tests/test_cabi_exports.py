@@ -23,8 +23,8 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_binding_covers_header_and_host_helpers_work():
-    from powerinfer_b200 import _lib, engine
-    assert set(_lib.EXPORTS) | set(engine.ENGINE_EXPORTS) == set(declared_symbols())
+    from powerinfer_b200 import _lib, engine, model_file
+    assert set(_lib.EXPORTS) | set(engine.ENGINE_EXPORTS) | set(model_file.MODEL_FILE_EXPORTS) == set(declared_symbols())
     assert _lib.lib.pi_version() >= 1
     assert _lib.lib.pi_row_bytes(_lib.PI_TYPE_F16, 4096) == 8192
     assert _lib.lib.pi_row_bytes(_lib.PI_TYPE_Q4_0, 4096) == 2304
@@ -63,6 +63,12 @@ int main(void) {
     /* argument validation comes before any CUDA call: no device needed */
     if (pi_mul_mat(PI_TYPE_Q4_0, (const void *)16, 8, 100, (const float *)16, 1, NULL, (float *)16, (void *)256, 1u << 20, NULL) != PI_ERR_INVALID) return 6;
     if (strlen(pi_last_error()) == 0) return 7;
+    {
+        pi_model_file * f = NULL;
+        if (pi_model_file_open("/nonexistent/model.gguf", &f) != PI_ERR_INVALID || f != NULL) return 8;
+        pi_model_file_close(NULL);
+        if (pi_model_file_n_tensors(NULL) != 0) return 9;
+    }
     puts("c consumer ok");
     return 0;
 }
