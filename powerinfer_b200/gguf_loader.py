@@ -58,7 +58,15 @@ class _Cursor:
 
 
 def read_gguf(path: str):
-    """-> (magic, kv dict, tensors dict name -> numpy array).  The arrays are views on a read-only memory map."""
+    """-> (magic, kv dict, tensors dict name -> numpy array).  The arrays are views on a read-only memory map.
+    A truncated or corrupt file raises ValueError."""
+    try:
+        return _read_gguf(path)
+    except (struct.error, IndexError, OverflowError, MemoryError, TypeError, UnicodeError) as e:
+        raise ValueError(f"{path}: malformed GGUF file ({type(e).__name__}: {e})") from e
+
+
+def _read_gguf(path: str):
     f = open(path, "rb")
     mm = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ)
     c = _Cursor(mm)

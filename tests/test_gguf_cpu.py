@@ -56,3 +56,26 @@ def test_placement_file_round_trip(tmp_path):
         assert np.array_equal(gi, i2) and np.array_equal(gb, b2) and b2.size == k and i2.sum() == k
     magic, kv, _ = gl.read_gguf(path)
     assert kv["general.architecture"] == "generic.gpu_index" and kv["generic.gpu_index.block_count"] == L
+
+
+def test_corrupt_files_raise_value_error(tmp_path):
+    pytest.importorskip("gguf")
+    spec = mg.MODEL_CASES["llama_f16"]
+    good = tmp_path / "good.gguf"
+    mg.write_gguf(spec, synth.build_model(spec), str(good))
+    blob = good.read_bytes()
+    rng = np.random.default_rng(4)
+    p = tmp_path / "bad.gguf"
+    for i in range(150):
+        if i % 2:
+            data = blob[: int(rng.integers(1, len(blob)))]
+        else:
+            b = bytearray(blob[:60000])
+            for q in rng.integers(4, len(b), 6):
+                b[q] = int(rng.integers(0, 256))
+            data = bytes(b) + blob[60000:]
+        p.write_bytes(data)
+        try:
+            gl.read_gguf(str(p))
+        except ValueError:
+            pass
