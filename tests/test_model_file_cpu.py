@@ -98,3 +98,98 @@ def test_malformed_files_are_errors_not_faults(tmp_path):
             pass
     with pytest.raises(_lib.PiError, match="cannot open"):
         model_file.ModelFile(str(tmp_path / "missing.gguf"))
+
+
+def _s(b: bytes) -> bytes:
+    return len(b).to_bytes(8, "little") + b
+
+
+def _random_container(rng):
+    """A random GGUF v3 container: every key type (arrays of scalars and of strings included), tensors of the four types
+    the readers know with 1..4 dimensions, a random alignment.  -> (bytes, expected keys, expected tensors)."""
+    import struct
+    fmt = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
+    lim = {0: (0, 255), 1: (-128, 127), 2: (0, 65535), 3: (-32768, 32767), 4: (0, 2**32 - 1), 5: (-2**31, 2**31 - 1),
+           10: (0, 2**63 - 1), 11: (-2**63, 2**63 - 1)}
+
+    def scalar(t):
+        if t in lim:
+            v = int(rng.integers(lim[t][0], lim[t][1], endpoint=True))
+        elif t == 7:
+            v = bool(rng.integers(0, 2))
+        else:
+            v = float(np.float32(rng.standard_normal()))
+        return v, struct.pack(fmt[t], v)
+
+    align = int(rng.choice([16, 32, 64, 256]))
+    kvs, want_kv = [("general.alignment", 4, struct.pack("<I", align))], {"general.alignment": align}
+    for i in range(int(rng.integers(3, 12))):
+        key, t = f"k{i}.{'x' * int(rng.integers(0, 9))}", int(rng.choice([0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12]))
+        if t == 8:
+            v = bytes(rng.integers(97, 123, int(rng.integers(0, 20))).astype(np.uint8))
+            kvs.append((key, t, _s(v))); want_kv[key] = v.decode()
+        elif t == 9:
+            et, n = int(rng.choice([0, 4, 5, 6, 8, 10])), int(rng.integers(0, 6))
+            if et == 8:
+                items = [bytes(rng.integers(97, 123, int(rng.integers(0, 7))).astype(np.uint8)) for _ in range(n)]
+                kvs.append((key, t, struct.pack("<IQ", et, n) + b"".join(_s(x) for x in items))); want_kv[key] = [x.decode() for x in items]
+            else:
+                vals = [scalar(et) for _ in range(n)]
+                kvs.append((key, t, struct.pack("<IQ", et, n) + b"".join(b for _, b in vals))); want_kv[key] = [v for v, _ in vals]
+        else:
+            v, b = scalar(t)
+            kvs.append((key, t, b)); want_kv[key] = v
+    tensors, blobs, off = [], [], 0
+    for i in range(int(rng.integers(1, 7))):
+        ty = int(rng.choice([0, 1, 2, 18]))
+        nd = int(rng.integers(1, 5))
+        ne = [int(rng.integers(1, 5)) for _ in range(nd)]
+        if ty == 2:
+            ne[0] = 32 * int(rng.integers(1, 4))
+        n = int(np.prod(ne))
+        nbytes = {0: n * 4, 1: n * 2, 2: n // 32 * 18, 18: n * 4}[ty]
+        data = bytes(rng.integers(0, 256, nbytes).astype(np.uint8))
+        tensors.append((f"t{i}", ne, ty, off, data))
+        pad = (-nbytes) % align
+        blobs.append(data + b"\0" * pad)
+        off += nbytes + pad
+    head = b"PWRI" + struct.pack("<IQQ", 3, len(tensors), len(kvs))
+    for key, t, payload in kvs:
+        head += _s(key.encode()) + struct.pack("<I", t) + payload
+    for name, ne, ty, o, _ in tensors:
+        head += _s(name.encode()) + struct.pack("<I", len(ne)) + b"".join(struct.pack("<Q", e) for e in ne) + struct.pack("<IQ", ty, o)
+    head += b"\0" * ((-len(head)) % align)
+    return head + b"".join(blobs), want_kv, tensors
+
+
+def test_random_containers_read_the_same_by_both_readers(tmp_path):
+    rng = np.random.default_rng(11)
+    path = tmp_path / "r.gguf"
+    for _ in range(60):
+        blob, want_kv, want_t = _random_container(rng)
+        path.write_bytes(blob)
+        _, kv, tens = gguf_loader.read_gguf(str(path))
+        for k, v in want_kv.items():
+            if isinstance(v, float) or (isinstance(v, list) and v and isinstance(v[0], float)):
+                assert np.allclose(kv[k], v, rtol=1e-6), k
+            else:
+                assert kv[k] == v, (k, kv[k], v)
+        with model_file.ModelFile(str(path)) as f:
+            for k, v in want_kv.items():
+                if isinstance(v, str):
+                    assert f.string(k) == v
+                elif isinstance(v, bool) or (isinstance(v, int) and v >= 0):
+                    assert f.u64(k) == int(v)
+                elif isinstance(v, float):
+                    assert np.float32(f.f32(k)) == np.float32(v)
+                elif isinstance(v, int):
+                    with pytest.raises(_lib.PiError, match="negative"):
+                        f.u64(k)
+            got = f.tensors()
+            assert list(got) == [t[0] for t in want_t]
+            for name, ne, ty, _, data in want_t:
+                gty, gne, raw = got[name]
+                assert gty == ty and list(gne) == ne + [1] * (4 - len(ne))
+                assert raw.tobytes() == data
+                assert np.ascontiguousarray(tens[name]).tobytes() == data
+                assert tens[name].shape == (tuple(reversed(ne)) if ty != 2 else tuple(reversed(ne[1:])) + (ne[0] // 32 * 18,))
