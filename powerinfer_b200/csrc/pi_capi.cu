@@ -189,6 +189,7 @@ int pi_mul_mat_idx(int wtype, const void * W, int64_t n_w_rows, int64_t ncols,
     g.wtype = wtype; g.W = W; g.nrows = n_w_rows; g.ncols = ncols; g.x = act.view(); g.T = T;
     g.list = ss.list; g.count = ss.count; g.bucket = bucket; g.idx = idx; g.idx_stride = idx_stride; g.threshold = threshold;
     g.dst = dst; g.dst_stride = n_dst_rows; g.status = ss.status;
+    if (T == 1) g.masks = ss.masks;
     return launch_gemv(g, st);
 }
 
@@ -225,6 +226,7 @@ int pi_axpy(int wtype, const void * Wt, int64_t n_w_rows, int64_t ncols,
     a.wtype = wtype; a.Wt = Wt; a.nrows = n_w_rows; a.ncols = ncols; a.h = h; a.h_stride = h_stride; a.T = T;
     a.list = ss.list; a.count = ss.count; a.bucket = bucket; a.idx = idx; a.idx_stride = idx_stride; a.threshold = threshold;
     a.cq = cq; a.cd = cd; a.c_stride = h_stride; a.partial = partial; a.n_groups = G; a.status = ss.status;
+    if (T == 1) a.masks = ss.masks;
     int used = G;
     if ((rc = launch_axpy(a, st, &used))) return rc;
     return launch_reduce_partials(partial, used, T, ncols, nullptr, nullptr, dst, st);
@@ -273,6 +275,7 @@ int pi_sparse_ffn(int wtype, const void * up, const void * gate, const void * do
     g.list = ss.list; g.count = ss.count; g.bucket = bucket; g.idx = idx; g.idx_stride = idx_stride; g.threshold = threshold;
     g.bias = up_bias; g.relu = gate ? 0 : 1;
     g.dst = h; g.dst_stride = F; g.status = ss.status;
+    if (T == 1) g.masks = ss.masks;
     if ((rc = launch_gemv(g, st))) return rc;
     if (wtype == PI_TYPE_Q4_0 && T > 1 && (rc = launch_neuron_q8(h, F, F, T, cq, cd, st))) return rc;
     AxpyArgs a;
@@ -280,6 +283,7 @@ int pi_sparse_ffn(int wtype, const void * up, const void * gate, const void * do
     a.wtype = wtype; a.Wt = down_t; a.nrows = n_w_rows; a.ncols = ncols; a.h = h; a.h_stride = F; a.T = T;
     a.list = ss.list; a.count = ss.count; a.bucket = bucket; a.idx = idx; a.idx_stride = idx_stride; a.threshold = threshold;
     a.cq = cq; a.cd = cd; a.c_stride = F; a.partial = partial; a.n_groups = G; a.status = ss.status;
+    if (T == 1) a.masks = ss.masks;
     int used = G;
     if ((rc = launch_axpy(a, st, &used))) return rc;
     return launch_reduce_partials(partial, used, T, ncols, nullptr, nullptr, dst, st, T == 1);

@@ -84,22 +84,6 @@ int launch_quantize_q8_0_ggml(const float * x, void * q8, int64_t nrows, int64_t
 // x F32 [T, n] (row stride x_stride) -> activation planes for `wtype` weights
 int launch_convert_act(int wtype, const float * x, int64_t x_stride, int64_t n, int T, ActBuf out, cudaStream_t st);
 
-// How a consumer kernel builds its own input vector instead of reading activation planes somebody else made
-// (batch 1 only).  v = (vec | sum of n_slots mailbox / partial slots) + bias + res1 + res2, optionally written out as the
-// new residual stream by CTA 0, then optionally normalised (llm_build_norm: rms or layer norm, * w, + b) and rounded to
-// the form the weights consume.  Every CTA recomputes it (a few tens of KB from L2): cheaper than one more launch.
-struct FusedIn {
-    int on = 0;
-    const float * vec = nullptr;
-    const float * slots = nullptr; int n_slots = 0; int64_t slot_stride = 0;
-    const unsigned int * wait_flags = nullptr; const unsigned int * wait_epoch = nullptr;   // slots are mailbox slots of peer ranks
-    const float * bias = nullptr; const float * res1 = nullptr; const float * res2 = nullptr;
-    float * x_out = nullptr;
-    int norm = 0;                      // 0: none, 1: RMSNorm, 2: LayerNorm
-    float eps = 0.f; const float * w = nullptr; const float * b = nullptr;
-    const double * stats = nullptr;    // {sum, sum of squares} of v accumulated by the kernel that produced `vec`: no reduction here
-};
-
 // Byte ranges for l2_prefetch() below.
 struct Prefetch { const void * ptr[2] = {nullptr, nullptr}; size_t bytes[2] = {0, 0}; };
 
@@ -124,12 +108,10 @@ struct GemvArgs {
     __half * dst16 = nullptr;          // optional FP16 copy of the result [T, dst_stride] (feeds an F16 mat-vec)
     // second matrix sharing the row selection (gate with up): dst = relu(W2 row . x) * (W row . x)
     const void * W2 = nullptr;
+    // one token: activity bit masks (one word per 32 LOCAL rows) instead of a list; selects the register-streaming kernel
+    const uint32_t * masks = nullptr;
     unsigned int * status = nullptr;   // device status word; when given, T == 1 shapes use the bulk-copy ring kernel
     bool pdl = false;                  // launch with programmatic dependent launch (the kernel waits for its producer itself)
-    FusedIn fin;                       // ring kernel only: build the input in the prologue (x is then ignored)
-    // ring kernel only: dst[g] = result + res_add[g] (the residual stream), and {sum, sum of squares} of what was written are
-    // added to stats_out (so the next norm needs no reduction of its own)
-    const float * res_add = nullptr; double * stats_out = nullptr;
 };
 int launch_gemv(const GemvArgs & a, cudaStream_t st);
 int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaStream_t st);   // PI_ERR_UNSUPPORTED: not eligible
@@ -141,14 +123,12 @@ int launch_gemv_mma_q4(const GemvArgs & a, cudaStream_t st);                    
 struct CompactArgs {
     const float * idx = nullptr; int64_t idx_stride = 0; int T = 1; float threshold = 0.f;
     int64_t n_local = 0; const int32_t * bucket = nullptr;
-    int32_t * list = nullptr; int32_t * count = nullptr;
+    int32_t * list = nullptr; int32_t * count = nullptr;   // list == nullptr: only the bit masks are made (no list, no count, no ticket)
     float * zero_dst = nullptr; int64_t zero_stride = 0;   // dense [T, zero_stride] vector: entries of rows inactive for a token are
     const float * fill_bias = nullptr; int fill_relu = 0;  // set to 0, or to (relu of) fill_bias[g] (what the graph's bias add leaves there)
     uint32_t * masks = nullptr;        // scratch: one word per 32 local rows
     unsigned int * ticket = nullptr;   // scratch: one word, must be 0 on entry, is 0 again on exit
     unsigned long long * total = nullptr;   // optional running sum of the counts (statistics)
-    // optional balanced split for the fused sparse FFN: parts[n_parts + 1] chunk boundaries, chunk_off[n_chunks + 1] scratch
-    int32_t * parts = nullptr; int n_parts = 0; int32_t * chunk_off = nullptr;
     bool pdl = false;
 };
 int launch_compact(const CompactArgs & a, cudaStream_t st);
@@ -161,6 +141,7 @@ struct AxpyArgs {
     const void * Wt = nullptr; int64_t nrows = 0, ncols = 0;
     const float * h = nullptr; int64_t h_stride = 0; int T = 1;       // by global id
     const int32_t * list = nullptr; const int32_t * count = nullptr; const int32_t * bucket = nullptr;
+    const uint32_t * masks = nullptr;                                 // one token: activity bit masks instead of the list
     const float * idx = nullptr; int64_t idx_stride = 0; float threshold = 0.f;
     // Q4_0: coefficient planes made by launch_neuron_q8 (int8 by global id, float scale per 32-neuron block)
     const int8_t * cq = nullptr; const float * cd = nullptr; int64_t c_stride = 0;
@@ -172,24 +153,13 @@ struct AxpyArgs {
 int axpy_groups(int wtype, int64_t ncols, int T);                     // row groups the launcher will use
 int launch_axpy(const AxpyArgs & a, cudaStream_t st, int * groups_used = nullptr);   // groups_used: partial vectors written
 int launch_axpy_mma(const AxpyArgs & a, cudaStream_t st, int * groups_used);         // FP16, 2..32 tokens; PI_ERR_UNSUPPORTED: not eligible
+// one token, rows named by bit masks, weights streamed into registers (pi_rows.cu); PI_ERR_UNSUPPORTED: not eligible
+bool rows_eligible(int wtype, int64_t nrows, int64_t ncols);
+int launch_gather_rows(const GemvArgs & a, cudaStream_t st);
+int launch_axpy_rows(const AxpyArgs & a, cudaStream_t st, int * groups_used);
+int axpy_rows_groups(int64_t nrows, int64_t ncols);                                  // partial vectors launch_axpy_rows writes
 // h F32 [T, stride] -> Q8_0 over 32-neuron blocks: cq int8 [T, stride], cd float [T, stride/32]
 int launch_neuron_q8(const float * h, int64_t stride, int64_t n, int T, int8_t * cq, float * cd, cudaStream_t st);
-
-// Batch-1 fused sparse FFN: up (and gate) mat-vec over the active rows, activation, axpy coefficient and the down
-// accumulation in ONE kernel; each CTA owns a contiguous range of 32-neuron chunks (CompactArgs::parts).
-struct SparseFfnArgs {
-    int wtype = PI_TYPE_F16;
-    const void * up = nullptr; const void * gate = nullptr; const void * down_t = nullptr;
-    int64_t nrows = 0, ncols = 0;
-    Act x;                                         // FFN input in the form the weights consume
-    const uint32_t * masks = nullptr; const int32_t * parts = nullptr; int n_parts = 0;
-    const float * up_b = nullptr;                  // opt: h = relu(up + b)
-    float * partial = nullptr;                     // [n_parts, ncols]
-    unsigned int * status = nullptr;
-    bool pdl = false;
-};
-int sparse_ffn_parts();                            // CTAs (= partial vectors) the fused kernel uses
-int launch_sparse_ffn(const SparseFfnArgs & a, cudaStream_t st);   // PI_ERR_UNSUPPORTED: shape not eligible
 
 // sum partial [n_groups, T, n] in group order (+ residual + bias) -> dst [T, n]
 int launch_reduce_partials(const float * partial, int n_groups, int T, int64_t n, const float * residual,

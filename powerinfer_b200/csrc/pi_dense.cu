@@ -311,10 +311,11 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
             __syncthreads();
             partial += (size_t)par * p.n_groups * tn;
         }
-        float4 a[8], b[8];                                             // all slots in flight at once (n_groups <= 8 per pass)
-        for (int g0 = 0; g0 < p.n_groups; g0 += 8) {
+        constexpr int GP = 12;                                         // slots in flight per pass
+        float4 a[GP], b[GP];
+        for (int g0 = 0; g0 < p.n_groups; g0 += GP) {
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
+            for (int u = 0; u < GP; u++) {
                 a[u] = z4; b[u] = z4;
                 if (g0 + u < p.n_groups) {
                     a[u] = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)(g0 + u) * tn + o));
@@ -322,7 +323,7 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 8; u++) add8(a[u], b[u]);
+            for (int u = 0; u < GP; u++) add8(a[u], b[u]);
         }
     } else {
         add8(*reinterpret_cast<const float4 *>(p.x + o), *reinterpret_cast<const float4 *>(p.x + o + 4));

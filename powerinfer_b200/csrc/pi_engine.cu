@@ -22,10 +22,8 @@ namespace pi {
 // ggml_get_rows on the F16 embedding (+ OPT's learned positions at pos + 2: llama.cpp:5105-5108, 6486-6488)
 __global__ void k_embed(const __half * __restrict__ tok_embd, const __half * __restrict__ pos_embd,
                         const int32_t * __restrict__ tokens, const int32_t * __restrict__ pos, int n_vocab, int n_pos,
-                        int64_t d, float * __restrict__ x, double * __restrict__ stats, int n_stats) {
+                        int64_t d, float * __restrict__ x) {
     const int t = blockIdx.y;
-    if (stats && blockIdx.x == 0 && blockIdx.y == 0)
-        for (int i = threadIdx.x; i < n_stats; i += blockDim.x) stats[i] = 0.0;
     int tok = tokens[t];
     tok = tok < 0 ? 0 : (tok >= n_vocab ? n_vocab - 1 : tok);
     for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < d; c += (int64_t)gridDim.x * blockDim.x) {
@@ -116,26 +114,18 @@ struct pi_engine {
     __half * k_cache, * v_cache;             // [n_layer, max_batch, n_ctx, dkv]
     unsigned int * status;                   // device word: bit 0 = an exchange wait ran out
     unsigned long long * active_total;       // device counter: sum of active-list lengths over layers and steps
-    double * stats;                          // [n_layer + 1][2][2]: {sum, sum of squares} of the vectors the norms read
     pi_exchange xch;
     cudaGraphExec_t graphs[PI_MAX_BATCH + 1];
     bool warmed[PI_MAX_BATCH + 1];
     int launches;                            // kernels enqueued by the last enqueue_step
     float * pred_trace;                      // optional [n_layer, max_batch, F]: keeps every layer's predictor logits
     bool pdl;                                // programmatic dependent launch between the kernels of a step
-    bool fuse;                               // batch 1: consumers build their own normalised input (no norm launches)
     bool gate_sym;                           // bamboo: relu on the gated product as well
-    bool ffn_fused;                          // batch 1: one kernel for up/gate + activation + down (PI_FFN_FUSED=1; off by default: parity-green but measured slower than the two-kernel path)
-    int32_t * parts, * chunk_off;            // balanced chunk split made by the compaction for that kernel
-    // Weight streamer (PI_PREFETCH=1; off by default): a second stream (a parallel branch of the step's graph) whose
-    // kernels only pull the weights of the mat-vecs that come next into L2 while the main chain runs kernels that leave
-    // HBM idle (norms, attention, compaction).  Measured slower than no streamer: the latency-bound kernels it overlaps
-    // with slow down behind its traffic by more than the mat-vecs gain.
-    unsigned prefetch;
-    cudaStream_t pf_stream;
-    std::vector<cudaEvent_t> pf_events; size_t pf_used; bool pf_forked;
-    unsigned skip_mask;                      // PI_SKIP_STAGES: stages left out of the step (timing experiments only; results are garbage)
+    bool rows1;                              // one token: masks-only compaction + register-streaming sparse kernels (shape eligible)
+    unsigned skip_mask;                      // set only inside pi_engine_time_stage: the stages left out of the captured sequence
 };
+
+static constexpr int NORM_MAX_GROUPS = 48;      // partial vectors the norm adds itself; more go through k_reduce_partials first
 
 static size_t up256(size_t v) { return (v + 255) & ~size_t(255); }
 
@@ -162,7 +152,7 @@ static void carve(pi_engine * e, void * ws, size_t ws_bytes, bool dry, size_t * 
     const int T = e->T_max;
     const size_t d = c.d, F = e->F;
     e->tokens = cv.take<int32_t>(T); e->pos = cv.take<int32_t>(T); e->seq_ids = cv.take<int32_t>(T); e->argmax = cv.take<int32_t>(T);
-    e->status = cv.take<unsigned int>(1); e->active_total = cv.take<unsigned long long>(1); e->stats = cv.take<double>((size_t)4 * (c.n_layer + 1));
+    e->status = cv.take<unsigned int>(1); e->active_total = cv.take<unsigned long long>(1);
     e->x = cv.take<float>(T * d); e->x2 = cv.take<float>(T * d); e->attn_out = cv.take<float>(T * d); e->ffn_vec = cv.take<float>(T * d);
     e->qkv = cv.take<float>((size_t)T * (e->dq + 2 * e->dkv));
     e->pred = cv.take<float>(T * F); e->h = cv.take<float>(T * F);
@@ -171,7 +161,6 @@ static void carve(pi_engine * e, void * ws, size_t ws_bytes, bool dry, size_t * 
     e->cs = cv.take<float>((size_t)c.n_ctx * e->hd);
     e->list = cv.take<int32_t>(F); e->count = cv.take<int32_t>(1); e->ticket = cv.take<unsigned int>(1);
     e->masks = cv.take<uint32_t>((F + 31) / 32);
-    e->parts = cv.take<int32_t>(1024); e->chunk_off = cv.take<int32_t>((F + 31) / 32 + 1);
     e->cq = cv.take<int8_t>(T * F); e->cd = cv.take<float>(T * (F / 32 + 1));
     e->hidden16 = cv.take<__half>((size_t)T * c.rank);
     e->act_a = cv.act(c.wtype, c.d, T);
@@ -248,12 +237,8 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
     memset(&e->xch, 0, sizeof e->xch);
     e->pred_trace = nullptr; e->launches = 0;
     { const char * v = getenv("PI_PDL"); e->pdl = !(v && v[0] == '0'); }
-    { const char * v = getenv("PI_FUSE"); e->fuse = (v && v[0] == '1'); }
-    { const char * v = getenv("PI_FFN_FUSED"); e->ffn_fused = (v && v[0] == '1'); }
-    { const char * v = getenv("PI_PREFETCH"); e->prefetch = v ? (unsigned)strtoul(v, nullptr, 0) : 0u; }
-    e->pf_stream = nullptr; e->pf_used = 0; e->pf_forked = false;
-    if (e->prefetch && cudaStreamCreateWithFlags(&e->pf_stream, cudaStreamNonBlocking) != cudaSuccess) { delete e; return cuda_fail(cudaGetLastError(), "engine_create: stream"); }
-    { const char * v = getenv("PI_SKIP_STAGES"); e->skip_mask = v ? (unsigned)strtoul(v, nullptr, 0) : 0u; }
+    e->skip_mask = 0u;
+    e->rows1 = rows_eligible(cfg->wtype, e->F, cfg->d) && axpy_rows_groups(e->F, cfg->d) <= e->G;
     cudaStream_t st = (cudaStream_t)stream;
     // one-time device state: sequence ids 0..T-1, zeroed ticket / status, RoPE angle table
     std::vector<int32_t> ids(e->T_max);
@@ -275,8 +260,6 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
 void pi_engine_destroy(pi_engine * e) {
     if (!e) return;
     for (auto & g : e->graphs) if (g) cudaGraphExecDestroy(g);
-    for (auto ev : e->pf_events) cudaEventDestroy(ev);
-    if (e->pf_stream) cudaStreamDestroy(e->pf_stream);
     delete e;
 }
 
@@ -353,16 +336,19 @@ struct StageTimer {
 // what the previous layer left to be folded into the next norm: a vector (or mailbox slots) + bias + extra residual
 struct Pending {
     const float * vec = nullptr;          // single vector [T, d]
+    const float * partial = nullptr; int n_groups = 0;   // or: partial vectors [n_groups, T, d] to be added in group order
     bool mailbox = false;                 // or: the n_ranks slots of the local mailbox
     const float * bias = nullptr;
     const float * res = nullptr;          // added before the residual stream (falcon's attention branch)
-    bool any() const { return vec || mailbox; }
+    bool any() const { return vec || partial || mailbox; }
 };
 
 void norm_inputs(pi_engine * e, int T, const Pending & pd, NormArgs & n) {
     if (pd.mailbox) {
         n.partial = e->xch.mailbox_local; n.n_groups = e->c.n_ranks; n.partial_stride = e->xch.slot_floats;
         n.wait_flags = e->xch.flags_local; n.wait_epoch = e->xch.epoch; n.status = e->status;
+    } else if (pd.partial) {
+        n.partial = pd.partial; n.n_groups = pd.n_groups;
     } else {
         n.x = pd.vec;
     }
@@ -372,43 +358,7 @@ void norm_inputs(pi_engine * e, int T, const Pending & pd, NormArgs & n) {
     (void)T;
 }
 
-int enqueue_step_fused(pi_engine * e, cudaStream_t st, StageTimer & tm);
-
-static cudaEvent_t pf_event(pi_engine * e) {
-    if (e->pf_used == e->pf_events.size()) {
-        cudaEvent_t ev = nullptr;
-        if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return nullptr;
-        e->pf_events.push_back(ev);
-    }
-    return e->pf_events[e->pf_used++];
-}
-
-// The streamer branch starts pulling `pf` once everything enqueued on `st` so far has finished.
-static int fork_prefetch(pi_engine * e, cudaStream_t st, const Prefetch & pf) {
-    if (!e->prefetch || !pf.ptr[0]) return PI_OK;
-    cudaEvent_t ev = pf_event(e);
-    PI_REQUIRE(ev, "engine: cannot create an event");
-    PI_CUDA(cudaEventRecord(ev, st));
-    PI_CUDA(cudaStreamWaitEvent(e->pf_stream, ev, 0));
-    const int rc = launch_prefetch(pf, e->pf_stream);
-    if (rc) return rc;
-    e->pf_forked = true; e->launches++;
-    return PI_OK;
-}
-
-// The step is complete only when the streamer branch is (also what lets a stream capture end).
-static int join_prefetch(pi_engine * e, cudaStream_t st) {
-    if (!e->pf_forked) return PI_OK;
-    cudaEvent_t ev = pf_event(e);
-    PI_REQUIRE(ev, "engine: cannot create an event");
-    PI_CUDA(cudaEventRecord(ev, e->pf_stream));
-    PI_CUDA(cudaStreamWaitEvent(st, ev, 0));
-    e->pf_forked = false;
-    return PI_OK;
-}
-
 int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
-    if (T == 1 && e->fuse && e->c.n_ranks == 1) return enqueue_step_fused(e, st, tm);
     const pi_engine_config & c = e->c;
     const int64_t d = c.d, F = e->F;
     const int wt = c.wtype;
@@ -418,14 +368,12 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
     const int qkv_rows = e->dq + 2 * e->dkv;
     const bool pdl = e->pdl && !tm.on;       // profiling wants each kernel alone between its events
     e->launches = 0;
-    e->pf_used = 0; e->pf_forked = false;
-    int rc_pf = PI_OK;
 
     if (!(e->skip_mask & (1u << PI_STAGE_OTHER))) {
         const dim3 grid((unsigned)((d + 255) / 256), T);
         if (tm.begin()) return PI_ERR_CUDA;
         k_embed<<<grid, 256, 0, st>>>((const __half *)e->g.tok_embd, (const __half *)e->g.pos_embd, e->tokens, e->pos,
-                                      c.n_vocab, c.n_pos, d, e->x, nullptr, 0);
+                                      c.n_vocab, c.n_pos, d, e->x);
         PI_LAUNCH_CHECK("k_embed");
         if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA;
         e->launches++;
@@ -489,12 +437,6 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             g.bias = L->bqkv; g.dst = e->qkv; g.dst_stride = qkv_rows;
             STAGE(PI_STAGE_QKV, (T + 7) / 8, launch_gemv(g, st));
         }
-        if (e->prefetch & 1u) {                                           // HBM is idle during attention: out-projection and fc1 weights
-            Prefetch pf;
-            pf.ptr[0] = L->wo; pf.bytes[0] = (size_t)d * pi_row_bytes(wt, e->dq);
-            pf.ptr[1] = L->fc1; pf.bytes[1] = (size_t)c.rank * d * 2;
-            if ((rc_pf = fork_prefetch(e, st, pf))) return rc_pf;
-        }
         {
             AttnArgs a;
             a.pdl = pdl;
@@ -515,11 +457,6 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             g.bias = c.rank_id == 0 ? L->bo : nullptr;                    // the bias enters the sum over ranks once
             g.dst = e->attn_out; g.dst_stride = d;
             STAGE(PI_STAGE_WO, (T + 7) / 8, launch_gemv(g, st));
-        }
-        if (e->prefetch & 2u || e->prefetch == 1u) {                      // ... the FFN norm and fc1: fc2
-            Prefetch pf;
-            pf.ptr[0] = L->fc2; pf.bytes[0] = (size_t)F * c.rank * 2;
-            if ((rc_pf = fork_prefetch(e, st, pf))) return rc_pf;
         }
 
         // ---- FFN input.  llama / opt: ffn_inp = attn_out + x, then the FFN norm; the complete attention output is needed,
@@ -555,61 +492,41 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             g2.W = L->fc2; g2.nrows = F; g2.ncols = c.rank; g2.x = hx; g2.T = T; g2.dst = pred; g2.dst_stride = F;
             STAGE(PI_STAGE_PRED, (T + 7) / 8, launch_gemv(g2, st));
         }
-        if ((e->prefetch & 4u || e->prefetch == 1u) && il + 1 < c.n_layer) {   // ... the sparse FFN (far from saturating HBM): next layer's QKV
-            Prefetch pf;
-            pf.ptr[0] = e->layers[il + 1].wqkv; pf.bytes[0] = (size_t)qkv_rows * pi_row_bytes(wt, d);
-            if ((rc_pf = fork_prefetch(e, st, pf))) return rc_pf;
-        }
-        // ---- mask -> active list (and, for batch 1, a balanced split of the 32-neuron chunks over the SMs).
+        // ---- mask -> activity bit masks, and for batches the sorted list of rows active for at least one token.
         //      Where a row is inactive for a token the dense hidden vector holds 0 (or relu(bias)): the Q4_0 axpy quantises
         //      that vector per 32 neurons, and a union list leaves per-token holes.
-        const bool fuse_ffn = T == 1 && e->ffn_fused && !e->gate_sym;          // the one-kernel FFN has the parallel gate only
+        const bool rows1 = T == 1 && e->rows1;
         {
             CompactArgs ca;
             ca.pdl = pdl;
             ca.idx = pred; ca.idx_stride = F; ca.T = T; ca.threshold = c.threshold; ca.n_local = F;
-            ca.list = e->list; ca.count = e->count; ca.masks = e->masks; ca.ticket = e->ticket; ca.total = e->active_total;
-            if (fuse_ffn) { ca.parts = e->parts; ca.n_parts = sparse_ffn_parts(); ca.chunk_off = e->chunk_off; }
-            else if (wt == PI_TYPE_Q4_0) { ca.zero_dst = e->h; ca.zero_stride = F; ca.fill_bias = L->up_b; ca.fill_relu = 1; }
+            if (!rows1) { ca.list = e->list; ca.count = e->count; }
+            ca.masks = e->masks; ca.ticket = e->ticket; ca.total = e->active_total;
+            if (wt == PI_TYPE_Q4_0) { ca.zero_dst = e->h; ca.zero_stride = F; ca.fill_bias = L->up_b; ca.fill_relu = 1; }
             STAGE(PI_STAGE_COMPACT, 1, launch_compact(ca, st));
         }
         int used = e->G;
-        bool ffn_done = false;
-        if (fuse_ffn) {
-            // ---- up (+ gate), activation, coefficients and down in one kernel
-            SparseFfnArgs fa;
-            fa.wtype = wt; fa.up = L->up; fa.gate = L->gate; fa.down_t = L->down_t; fa.nrows = F; fa.ncols = d;
-            fa.x = e->act_a.view(); fa.masks = e->masks; fa.parts = e->parts; fa.n_parts = sparse_ffn_parts();
-            fa.up_b = L->up_b; fa.partial = e->partial; fa.status = e->status; fa.pdl = pdl;
-            if (!(e->skip_mask & (1u << PI_STAGE_UPGATE))) {
-                if (tm.begin()) return PI_ERR_CUDA;
-                const int rc = launch_sparse_ffn(fa, st);
-                if (rc == PI_OK) { if (tm.end(PI_STAGE_UPGATE)) return PI_ERR_CUDA; e->launches++; ffn_done = true; used = fa.n_parts; }
-                else if (rc != PI_ERR_UNSUPPORTED) return rc;
-                else if (tm.on) { if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA; }
-            } else { ffn_done = true; used = fa.n_parts; }
-        }
-        if (!ffn_done) {
         // ---- up (and gate) over the active rows: h = relu(gate.x) * (up.x) | relu(up.x + b)
         {
             GemvArgs g;
             g.status = e->status; g.pdl = pdl;
             g.wtype = wt; g.W = L->up; g.W2 = L->gate; g.nrows = F; g.ncols = d; g.x = e->act_a.view(); g.T = T;
-            g.list = e->list; g.count = e->count; g.idx = pred; g.idx_stride = F; g.threshold = c.threshold;
+            if (rows1) g.masks = e->masks; else { g.list = e->list; g.count = e->count; }
+            g.idx = pred; g.idx_stride = F; g.threshold = c.threshold;
             g.bias = L->up_b; g.relu = L->gate ? (e->gate_sym ? 1 : 0) : 1;
             g.dst = e->h; g.dst_stride = F;
             STAGE(PI_STAGE_UPGATE, (T + 7) / 8, launch_gemv(g, st));
         }
-        // ---- down: axpy over the same list, then the sum over row groups (and, sharded, over ranks)
+        // ---- down: axpy over the same rows; the sum over row groups (and, sharded, over ranks) is left to the next norm
         if (wt == PI_TYPE_Q4_0 && T > 1) STAGE(PI_STAGE_DOWN, 1, launch_neuron_q8(e->h, F, F, T, e->cq, e->cd, st));
         {
             AxpyArgs a;
             a.pdl = pdl;
             a.wtype = wt; a.Wt = L->down_t; a.nrows = F; a.ncols = d; a.h = e->h; a.h_stride = F; a.T = T;
-            a.list = e->list; a.count = e->count; a.idx = pred; a.idx_stride = F; a.threshold = c.threshold;
+            if (rows1) a.masks = e->masks; else { a.list = e->list; a.count = e->count; }
+            a.idx = pred; a.idx_stride = F; a.threshold = c.threshold;
             a.cq = e->cq; a.cd = e->cd; a.c_stride = F; a.partial = e->partial; a.n_groups = e->G; a.status = e->status;
             STAGE(PI_STAGE_DOWN, T == 1 ? 1 : (wt == PI_TYPE_Q4_0 ? (T + 1) / 2 : (T + 3) / 4), launch_axpy(a, st, &used));
-        }
         }
         pend = Pending();
         pend.bias = L->down_b;
@@ -617,149 +534,14 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             // falcon sums its two branches locally first: one exchange per layer (llama.cpp:5443-5447)
             STAGE(PI_STAGE_EXCHANGE, 1, launch_exchange_push(e->xch, e->partial, used, T, d, falcon ? e->attn_out : nullptr, e->status, st, pdl && T == 1));
             pend.mailbox = true;
+        } else if (used <= NORM_MAX_GROUPS) {
+            pend.partial = e->partial; pend.n_groups = used;
+            pend.res = falcon ? e->attn_out : nullptr;
         } else {
             STAGE(PI_STAGE_DOWN, 1, launch_reduce_partials(e->partial, used, T, d, nullptr, nullptr, e->ffn_vec, st, pdl));
             pend.vec = e->ffn_vec;
             pend.res = falcon ? e->attn_out : nullptr;
         }
-    }
-    return join_prefetch(e, st);
-}
-
-// Batch-1, single-GPU step with the norm launches gone.  The two kernels that finish a residual-stream vector (the
-// out-projection mat-vec, which adds the residual in its epilogue, and the reduction of the axpy partials) also accumulate
-// that vector's {sum, sum of squares}; the mat-vecs that consume the normalised vector (QKV, up/gate, lm head) build it in
-// their prologue from the vector and those two numbers: one pass, no reduction, no extra launch.  The residual stream
-// ping-pongs between two buffers because the producer writes the new one while nothing may still read the old one.
-int enqueue_step_fused(pi_engine * e, cudaStream_t st, StageTimer & tm) {
-    const pi_engine_config & c = e->c;
-    const int T = 1;
-    const int64_t d = c.d, F = e->F;
-    const int wt = c.wtype;
-    const bool falcon = c.arch == PI_ARCH_FALCON;
-    const int norm_kind = c.arch == PI_ARCH_LLAMA ? 1 : 2;
-    const int qkv_rows = e->dq + 2 * e->dkv;
-    const bool pdl = e->pdl && !tm.on;
-    e->launches = 0;
-    float * x_cur = e->x, * x_nxt = e->x2;
-    auto swap_x = [&]() { float * t = x_cur; x_cur = x_nxt; x_nxt = t; };
-    auto stats_of = [&](int il, int which) { return e->stats + ((size_t)il * 2 + which) * 2; };
-    {
-        const dim3 grid((unsigned)((d + 255) / 256), T);
-        if (tm.begin()) return PI_ERR_CUDA;
-        k_embed<<<grid, 256, 0, st>>>((const __half *)e->g.tok_embd, (const __half *)e->g.pos_embd, e->tokens, e->pos,
-                                      c.n_vocab, c.n_pos, d, x_cur, e->stats, 4 * (c.n_layer + 1));
-        PI_LAUNCH_CHECK("k_embed");
-        if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA;
-        e->launches++;
-    }
-    for (int il = 0; il <= c.n_layer; il++) {
-        const bool last = il == c.n_layer;
-        const pi_layer_weights * L = last ? nullptr : &e->layers[il];
-        // statistics of the layer input: layer 0 reads the embedding, whose statistics nobody made (the prologue reduces itself)
-        const double * in_stats = il == 0 ? nullptr : stats_of(il, 0);
-        if (last) {
-            const int out_t = e->g.output ? wt : PI_TYPE_F16;
-            GemvArgs g;
-            g.status = e->status; g.pdl = pdl;
-            g.fin.on = 1; g.fin.vec = x_cur; g.fin.stats = in_stats;
-            g.fin.norm = norm_kind; g.fin.eps = c.norm_eps; g.fin.w = e->g.out_norm_w; g.fin.b = e->g.out_norm_b;
-            g.wtype = out_t; g.W = e->g.output ? e->g.output : e->g.tok_embd; g.nrows = c.n_vocab; g.ncols = d;
-            g.T = T; g.dst = e->logits; g.dst_stride = c.n_vocab;
-            STAGE(PI_STAGE_LM_HEAD, 1, launch_gemv(g, st));
-            if (tm.begin()) return PI_ERR_CUDA;
-            k_argmax<<<T, 1024, 0, st>>>(e->logits, c.n_vocab, e->argmax);
-            PI_LAUNCH_CHECK("k_argmax");
-            if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA;
-            e->launches++;
-            break;
-        }
-        // ---- QKV on norm(layer input)
-        {
-            GemvArgs g;
-            g.status = e->status; g.pdl = pdl;
-            g.fin.on = 1; g.fin.vec = x_cur; g.fin.stats = in_stats;
-            g.fin.norm = norm_kind; g.fin.eps = c.norm_eps;
-            if (falcon && L->attn_norm2_w) { g.fin.w = L->attn_norm2_w; g.fin.b = L->attn_norm2_b; }
-            else                           { g.fin.w = L->attn_norm_w;  g.fin.b = L->attn_norm_b; }
-            g.wtype = wt; g.W = L->wqkv; g.nrows = qkv_rows; g.ncols = d; g.T = T;
-            g.bias = L->bqkv; g.dst = e->qkv; g.dst_stride = qkv_rows;
-            STAGE(PI_STAGE_QKV, 1, launch_gemv(g, st));
-        }
-        {
-            AttnArgs a;
-            a.pdl = pdl;
-            a.q = e->qkv; a.k = e->qkv + e->dq; a.v = e->qkv + e->dq + e->dkv;
-            a.q_stride = qkv_rows; a.kv_stride = qkv_rows;
-            const size_t layer_off = (size_t)il * c.max_batch * c.n_ctx * e->dkv;
-            a.k_cache = e->k_cache + layer_off; a.v_cache = e->v_cache + layer_off;
-            a.seq = e->seq_ids; a.pos = e->pos; a.T = T;
-            a.n_head = c.n_head; a.n_head_kv = c.n_head_kv; a.head_dim = e->hd; a.n_ctx = c.n_ctx;
-            if (c.arch != PI_ARCH_OPT) { a.cs = e->cs; a.neox = falcon; }
-            a.out_act_type = wt; a.out_act = e->act_o;
-            STAGE(PI_STAGE_ATTN, 1, launch_attention(a, st));
-        }
-        // ---- out-projection.  llama / opt: its epilogue finishes ffn_inp = attn_out + x (the new residual stream) and the
-        //      statistics of the FFN norm; falcon keeps attn_out aside, its residual stream does not change here
-        {
-            GemvArgs g;
-            g.status = e->status; g.pdl = pdl;
-            g.wtype = wt; g.W = L->wo; g.nrows = d; g.ncols = e->dq; g.x = e->act_o.view(); g.T = T;
-            g.bias = L->bo; g.dst_stride = d;
-            if (falcon) { g.dst = e->attn_out; }
-            else        { g.dst = x_nxt; g.res_add = x_cur; g.stats_out = stats_of(il, 1); }
-            STAGE(PI_STAGE_WO, 1, launch_gemv(g, st));
-            if (!falcon) swap_x();
-        }
-        // ---- predictor on the (un-normalised) FFN input / layer input
-        float * pred = e->pred_trace ? e->pred_trace + (size_t)il * c.max_batch * F : e->pred;
-        {
-            GemvArgs g1;
-            g1.status = e->status; g1.pdl = pdl;
-            g1.fin.on = 1; g1.fin.vec = x_cur;
-            g1.W = L->fc1; g1.nrows = c.rank; g1.ncols = d; g1.T = T; g1.relu = 1;
-            g1.dst16 = e->hidden16; g1.dst_stride = c.rank;
-            STAGE(PI_STAGE_PRED, 1, launch_gemv(g1, st));
-            Act hx; hx.h16 = e->hidden16;
-            GemvArgs g2;
-            g2.status = e->status; g2.pdl = pdl;
-            g2.W = L->fc2; g2.nrows = F; g2.ncols = c.rank; g2.x = hx; g2.T = T; g2.dst = pred; g2.dst_stride = F;
-            STAGE(PI_STAGE_PRED, 1, launch_gemv(g2, st));
-        }
-        {
-            CompactArgs ca;
-            ca.pdl = pdl;
-            ca.idx = pred; ca.idx_stride = F; ca.T = T; ca.threshold = c.threshold; ca.n_local = F;
-            ca.list = e->list; ca.count = e->count; ca.masks = e->masks; ca.ticket = e->ticket; ca.total = e->active_total;
-            if (wt == PI_TYPE_Q4_0) { ca.zero_dst = e->h; ca.zero_stride = F; ca.fill_bias = L->up_b; ca.fill_relu = 1; }
-            STAGE(PI_STAGE_COMPACT, 1, launch_compact(ca, st));
-        }
-        // ---- up (and gate) over the active rows on the FFN norm (falcon: attn_norm of the layer input)
-        {
-            GemvArgs g;
-            g.status = e->status; g.pdl = pdl;
-            g.fin.on = 1; g.fin.vec = x_cur; g.fin.norm = norm_kind; g.fin.eps = c.norm_eps;
-            if (falcon) { g.fin.w = L->attn_norm_w; g.fin.b = L->attn_norm_b; g.fin.stats = in_stats; }
-            else        { g.fin.w = L->ffn_norm_w;  g.fin.b = L->ffn_norm_b;  g.fin.stats = stats_of(il, 1); }
-            g.wtype = wt; g.W = L->up; g.W2 = L->gate; g.nrows = F; g.ncols = d; g.T = T;
-            g.list = e->list; g.count = e->count; g.idx = pred; g.idx_stride = F; g.threshold = c.threshold;
-            g.bias = L->up_b; g.relu = L->gate ? (e->gate_sym ? 1 : 0) : 1;
-            g.dst = e->h; g.dst_stride = F;
-            STAGE(PI_STAGE_UPGATE, 1, launch_gemv(g, st));
-        }
-        int used = e->G;
-        {
-            AxpyArgs a;
-            a.pdl = pdl;
-            a.wtype = wt; a.Wt = L->down_t; a.nrows = F; a.ncols = d; a.h = e->h; a.h_stride = F; a.T = T;
-            a.list = e->list; a.count = e->count; a.idx = pred; a.idx_stride = F; a.threshold = c.threshold;
-            a.cq = e->cq; a.cd = e->cd; a.c_stride = F; a.partial = e->partial; a.n_groups = e->G; a.status = e->status;
-            STAGE(PI_STAGE_DOWN, 1, launch_axpy(a, st, &used));
-        }
-        // ---- l_out = (ffn_out + down_b [+ attn_out]) + residual, with the next norm's statistics
-        STAGE(PI_STAGE_DOWN, 1, launch_reduce_partials(e->partial, used, T, d, x_cur, L->down_b, x_nxt, st, pdl,
-                                                       falcon ? e->attn_out : nullptr, stats_of(il + 1, 0)));
-        swap_x();
     }
     return PI_OK;
 }

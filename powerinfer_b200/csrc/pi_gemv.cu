@@ -300,6 +300,11 @@ static int launch_wt(const GemvP & p, int tt, bool sparse, bool gated, size_t sm
 
 int launch_gemv(const GemvArgs & a, cudaStream_t st) {
     if (a.T <= 0 || a.nrows <= 0) return PI_OK;
+    if (a.T == 1 && a.masks) {                                     // one token, rows named by bit masks
+        const int rc = launch_gather_rows(a, st);
+        if (rc != PI_ERR_UNSUPPORTED) return rc;
+        if (!a.list) { set_error("gemv: masks given but the shape is not eligible and there is no list"); return PI_ERR_UNSUPPORTED; }
+    }
     if (a.wtype == PI_TYPE_F16 && a.status) {                      // FP16 rows, up to 32 tokens: tensor-core ring kernel
         const int rc = launch_gemv_mma(a, st);
         if (rc != PI_ERR_UNSUPPORTED) return rc;

@@ -262,7 +262,7 @@ int launch_gemv_mma(const GemvArgs & a, cudaStream_t st) {
     static int enabled = -1;
     static int min_T = 2;
     if (enabled < 0) { const char * v = getenv("PI_MMA"); enabled = !(v && v[0] == '0'); const char * m = getenv("PI_MMA_MIN_T"); if (m) min_T = atoi(m); }
-    if (!enabled || a.T < min_T || a.wtype != PI_TYPE_F16 || !a.status || !a.x.h16 || a.fin.on || a.res_add || a.stats_out) return PI_ERR_UNSUPPORTED;
+    if (!enabled || a.T < min_T || a.wtype != PI_TYPE_F16 || !a.status || !a.x.h16) return PI_ERR_UNSUPPORTED;
     const bool sparse = a.list != nullptr, gated = a.W2 != nullptr;
     if (!sparse && a.nrows / 16 < sm_count()) return PI_ERR_UNSUPPORTED;      // too few row tiles to fill the GPU (e.g. fc1)
     if (a.nrows % 16 != 0 && !sparse) return PI_ERR_UNSUPPORTED;

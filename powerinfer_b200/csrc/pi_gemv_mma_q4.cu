@@ -367,7 +367,7 @@ int launch_gemv_mma_q4(const GemvArgs & a, cudaStream_t st) {
         const char * v = getenv("PI_MMA_Q4"); enabled = !(v && v[0] == '0');
     }
     const bool sparse = a.list != nullptr, gated = a.W2 != nullptr;
-    if (!enabled || a.wtype != PI_TYPE_Q4_0 || !a.status || !a.x.lo || a.fin.on || a.res_add || a.stats_out) return PI_ERR_UNSUPPORTED;
+    if (!enabled || a.wtype != PI_TYPE_Q4_0 || !a.status || !a.x.lo) return PI_ERR_UNSUPPORTED;
     if (a.ncols % QK != 0) return PI_ERR_UNSUPPORTED;
     const int nb = (int)(a.ncols / QK);
     // tiles of 16 vectors when their ring fits next to the activation planes (rows up to 8192 columns), else of 8

@@ -32,8 +32,6 @@ struct RingP {
     float * dst; __half * dst16;
     unsigned int * status;
     int R, split, stages, max_items; size_t stage_bytes;
-    FusedIn fin;
-    const float * res_add; double * stats_out;
 };
 
 __device__ __forceinline__ int r_block_dot(const uint4 q, const uint4 lo, const uint4 hi, int s8) {
@@ -136,186 +134,7 @@ __device__ __forceinline__ void ring_dot_rows(const unsigned char * base, size_t
     }
 }
 
-// ---- fused input (see FusedIn): every CTA builds the activation it consumes
-__device__ __forceinline__ double ring_block_sum_d(double v, double * s_red) {
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    v = warp_sum_d(v);
-    __syncthreads();
-    if (lane == 0) s_red[wid] = v;
-    __syncthreads();
-    double t = 0.0;
-#pragma unroll
-    for (int i = 0; i < RING_WARPS; i++) t += s_red[i];
-    return t;
-}
-
-// the 8 values of chunk c8 (columns 8*c8 ..) of v
-__device__ __forceinline__ void fused_load8(const FusedIn & f, const float * slots, int c8, float (&v)[8]) {
-    const size_t o = (size_t)c8 * 8;
-#pragma unroll
-    for (int j = 0; j < 8; j++) v[j] = 0.f;
-    if (f.vec) {
-        const float4 a = __ldcg(reinterpret_cast<const float4 *>(f.vec + o)), b = __ldcg(reinterpret_cast<const float4 *>(f.vec + o + 4));
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    } else {
-        for (int g = 0; g < f.n_slots; g++) {
-            const float * sp = slots + (size_t)g * f.slot_stride + o;
-            const float4 a = __ldcg(reinterpret_cast<const float4 *>(sp)), b = __ldcg(reinterpret_cast<const float4 *>(sp + 4));
-            v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
-        }
-    }
-    if (f.bias) {
-#pragma unroll
-        for (int j = 0; j < 8; j++) v[j] += f.bias[o + j];
-    }
-    if (f.res1) {
-        const float4 a = __ldcg(reinterpret_cast<const float4 *>(f.res1 + o)), b = __ldcg(reinterpret_cast<const float4 *>(f.res1 + o + 4));
-        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
-    }
-    if (f.res2) {
-        const float4 a = __ldcg(reinterpret_cast<const float4 *>(f.res2 + o)), b = __ldcg(reinterpret_cast<const float4 *>(f.res2 + o + 4));
-        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
-    }
-}
-
-// Builds the staged activation in shared memory (FP16 vector, or Q8_0 planes lo | hi | {scale, sum}) from FusedIn.
-// Values are recomputed in each pass instead of being kept in registers across the kernel's main loop.
-template <int WT>
-__device__ __forceinline__ void ring_build_input(const FusedIn & f, int n, unsigned char * xs, unsigned int * status) {
-    __shared__ double s_red[RING_WARPS];
-    const int tid = threadIdx.x;
-    const int n8 = n / 8, nb = n / QK;
-    const float * slots = f.slots;
-    if (f.wait_flags) {                                             // peers' partial vectors: bounded wait for their flags
-        const unsigned int epoch = *reinterpret_cast<const volatile unsigned int *>(f.wait_epoch);
-        const unsigned int par = epoch & 1u;
-        if (tid < f.n_slots) {
-            const unsigned int * fl = f.wait_flags + par * f.n_slots + tid;
-            const long long t0 = clock64();
-            bool ok = false;
-            for (;;) {
-                unsigned int seen;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(fl));
-                if ((int)(seen - epoch) >= 0) { ok = true; break; }
-                if (clock64() - t0 > 2000000000LL) break;
-                __nanosleep(64);
-            }
-            if (!ok) atomicOr(status, 1u);
-        }
-        __syncthreads();
-        slots += (size_t)par * f.n_slots * f.slot_stride;
-    }
-    float scale = 1.f, mean = 0.f;
-    if (f.norm && f.stats) {
-        const double s1 = __ldcg(f.stats), s2 = __ldcg(f.stats + 1);
-        if (f.norm == 1) {
-            scale = 1.0f / sqrtf((float)(s2 / (double)n) + f.eps);
-        } else {
-            const double m = s1 / (double)n;
-            mean = (float)m;
-            scale = 1.0f / sqrtf((float)(s2 / (double)n - m * m) + f.eps);
-        }
-    } else if (f.norm || (f.x_out && blockIdx.x == 0)) {
-        double s1 = 0.0;
-        for (int c8 = tid; c8 < n8; c8 += RING_THREADS) {
-            float v[8];
-            fused_load8(f, slots, c8, v);
-            if (f.x_out && blockIdx.x == 0) {
-                *reinterpret_cast<float4 *>(f.x_out + (size_t)c8 * 8)     = make_float4(v[0], v[1], v[2], v[3]);
-                *reinterpret_cast<float4 *>(f.x_out + (size_t)c8 * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
-            }
-#pragma unroll
-            for (int j = 0; j < 8; j++) s1 += f.norm == 1 ? (double)(v[j] * v[j]) : (double)v[j];
-        }
-        if (f.norm == 1) {
-            s1 = ring_block_sum_d(s1, s_red);
-            scale = 1.0f / sqrtf((float)(s1 / (double)n) + f.eps);
-        } else if (f.norm == 2) {
-            s1 = ring_block_sum_d(s1, s_red);
-            mean = (float)(s1 / (double)n);
-            double s2 = 0.0;
-            for (int c8 = tid; c8 < n8; c8 += RING_THREADS) {
-                float v[8];
-                fused_load8(f, slots, c8, v);
-#pragma unroll
-                for (int j = 0; j < 8; j++) { const float dv = v[j] - mean; s2 += (double)(dv * dv); }
-            }
-            s2 = ring_block_sum_d(s2, s_red);
-            scale = 1.0f / sqrtf((float)(s2 / (double)n) + f.eps);
-        }
-    }
-    // emit: a thread owns chunk c8; 4 consecutive threads own one Q8_0 block, so every lane takes part in the shuffles.
-    // Two chunks per trip, all their loads (vector, norm weight, norm bias) issued before anything is consumed.
-    const int n8_pad = (n8 + 2 * RING_THREADS - 1) / (2 * RING_THREADS) * (2 * RING_THREADS);
-    for (int c0 = tid; c0 < n8_pad; c0 += 2 * RING_THREADS) {
-        float y[2][8], wv[2][8], bv[2][8];
-        bool valid[2];
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-            const int c8 = c0 + u * RING_THREADS;
-            valid[u] = c8 < n8;
-#pragma unroll
-            for (int j = 0; j < 8; j++) { y[u][j] = 0.f; wv[u][j] = 1.f; bv[u][j] = 0.f; }
-            if (valid[u]) {
-                fused_load8(f, slots, c8, y[u]);
-                if (f.norm && f.w) {
-                    const float4 a = __ldg(reinterpret_cast<const float4 *>(f.w + (size_t)c8 * 8)), b = __ldg(reinterpret_cast<const float4 *>(f.w + (size_t)c8 * 8 + 4));
-                    wv[u][0] = a.x; wv[u][1] = a.y; wv[u][2] = a.z; wv[u][3] = a.w; wv[u][4] = b.x; wv[u][5] = b.y; wv[u][6] = b.z; wv[u][7] = b.w;
-                }
-                if (f.norm && f.b) {
-                    const float4 a = __ldg(reinterpret_cast<const float4 *>(f.b + (size_t)c8 * 8)), b = __ldg(reinterpret_cast<const float4 *>(f.b + (size_t)c8 * 8 + 4));
-                    bv[u][0] = a.x; bv[u][1] = a.y; bv[u][2] = a.z; bv[u][3] = a.w; bv[u][4] = b.x; bv[u][5] = b.y; bv[u][6] = b.z; bv[u][7] = b.w;
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-            const int c8 = c0 + u * RING_THREADS;
-            if (f.norm) {
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    float r = __fmul_rn(y[u][j] - mean, scale);
-                    if (f.w) r = __fmul_rn(r, wv[u][j]);
-                    if (f.b) r = __fadd_rn(r, bv[u][j]);
-                    y[u][j] = valid[u] ? r : 0.f;
-                }
-            }
-            if (WT == PI_TYPE_F16) {
-                if (valid[u]) {
-                    __half2 hh[4];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) hh[j] = __floats2half2_rn(y[u][2 * j], y[u][2 * j + 1]);
-                    reinterpret_cast<uint4 *>(xs)[c8] = *reinterpret_cast<uint4 *>(hh);
-                }
-            } else {
-                float amax = 0.f;
-#pragma unroll
-                for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(y[u][j]));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                const float id = amax != 0.0f ? 127.0f / amax : 0.0f;
-                int q[8], sum = 0;
-#pragma unroll
-                for (int j = 0; j < 8; j++) { q[j] = __float2int_rn(y[u][j] * id); sum += q[j]; }
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                if (valid[u]) {
-                    uint2 packed;
-                    packed.x = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
-                    packed.y = (uint32_t)(q[4] & 0xFF) | ((uint32_t)(q[5] & 0xFF) << 8) | ((uint32_t)(q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
-                    uint4 * lo = reinterpret_cast<uint4 *>(xs);
-                    uint4 * hi = lo + nb;
-                    uint2 * ds = reinterpret_cast<uint2 *>(hi + nb);
-                    const int blk = c8 >> 2, part = c8 & 3;
-                    reinterpret_cast<uint2 *>(part < 2 ? lo + blk : hi + blk)[part & 1] = packed;
-                    if (part == 0) ds[blk] = make_uint2(__float_as_uint(round_f16(amax / 127.0f)), (unsigned)sum);
-                }
-            }
-        }
-    }
-}
-
-template <int WT, bool SPARSE, bool GATED, bool FUSED, int RW>
+template <int WT, bool SPARSE, bool GATED, int RW>
 __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ float s_part[2][RING_MAX_VEC][RING_WARPS];          // [stage parity][vector of the stage][column part]
@@ -385,9 +204,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
         if (warp == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
     }
     // ---- stage the activation
-    if (FUSED) {
-        ring_build_input<WT>(p.fin, p.ncols, xs, p.status);
-    } else if (WT == PI_TYPE_F16) {
+    if (WT == PI_TYPE_F16) {
         const uint4 * src = reinterpret_cast<const uint4 *>(p.x.h16);
         uint4 * dstx = reinterpret_cast<uint4 *>(xs);
         for (int i = tid; i < p.ncols / 8; i += RING_THREADS) dstx[i] = src[i];
@@ -409,7 +226,6 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
     const int per = units / split;
     const int NV = R * NM, groups = NV / RW;
     bool dead = false;                                              // warp-uniform
-    double st_sum = 0.0, st_sq = 0.0;                               // statistics of what this thread wrote
     for (int st = 0; st < n_stages; st++) {
         const int s = st % S;
         const unsigned parity = (unsigned)(st / S) & 1u;
@@ -448,22 +264,8 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring(const RingP p) {
             if (GATED) o = fmaxf(v2, 0.f) * v;
             if (p.bias) o += p.bias[g];
             if (p.relu) o = fmaxf(o, 0.f);
-            if (p.res_add) o += p.res_add[g];
             if (p.dst)   p.dst[g] = o;
             if (p.dst16) p.dst16[g] = __float2half_rn(o);
-            st_sum += (double)o; st_sq += (double)(o * o);
-        }
-    }
-    if (p.stats_out) {                                              // one pair of atomics per CTA
-        __shared__ double s_stat[RING_WARPS][2];
-        st_sum = warp_sum_d(st_sum); st_sq = warp_sum_d(st_sq);
-        if (lane == 0) { s_stat[warp][0] = st_sum; s_stat[warp][1] = st_sq; }
-        __syncthreads();
-        if (tid == 0) {
-            double a = 0.0, b = 0.0;
-#pragma unroll
-            for (int w = 0; w < RING_WARPS; w++) { a += s_stat[w][0]; b += s_stat[w][1]; }
-            atomicAdd(p.stats_out, a); atomicAdd(p.stats_out + 1, b);
         }
     }
     if (__syncthreads_or(dead) && tid == 0) {                       // do not exit with copies still landing in shared memory
@@ -781,12 +583,12 @@ static RingPlan ring_plan(int wtype, int64_t nrows, int64_t ncols, bool sparse, 
     return pl;
 }
 
-template <int WT, bool SPARSE, bool GATED, bool FUSED, int RW>
+template <int WT, bool SPARSE, bool GATED, int RW>
 static int launch_ring_inst(const RingP & p, const RingPlan & pl, bool pdl, cudaStream_t st) {
     static bool attr_done[16] = {false};
     int dev = 0;
     PI_CUDA(cudaGetDevice(&dev));
-    auto kern = k_gemv_ring<WT, SPARSE, GATED, FUSED, RW>;
+    auto kern = k_gemv_ring<WT, SPARSE, GATED, RW>;
     if (dev >= 0 && dev < 16 && !attr_done[dev]) {
         PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
         attr_done[dev] = true;
@@ -811,13 +613,13 @@ int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaSt
     p.W = (const uint8_t *)a.W; p.W2 = (const uint8_t *)a.W2; p.row_bytes = (int64_t)pi_row_bytes(a.wtype, a.ncols);
     p.nrows = (int)a.nrows; p.ncols = (int)a.ncols; p.nb = (int)(a.ncols / QK); p.x = a.x;
     p.list = a.list; p.count = a.count; p.bucket = a.bucket; p.idx = a.idx; p.threshold = a.threshold;
-    p.bias = a.bias; p.relu = a.relu; p.dst = a.dst; p.dst16 = a.dst16; p.status = status; p.fin = a.fin; p.res_add = a.res_add; p.stats_out = a.stats_out;
+    p.bias = a.bias; p.relu = a.relu; p.dst = a.dst; p.dst16 = a.dst16; p.status = status;
     p.R = pl.R; p.split = pl.split; p.stages = pl.stages; p.max_items = pl.max_items; p.stage_bytes = pl.stage_bytes;
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
     {
         static int warp_rows = -1;
         if (warp_rows < 0) { const char * v = getenv("PI_RING_W"); warp_rows = !(v && v[0] == '0'); }
-        if (warp_rows && !sparse && !a.fin.on && !a.res_add && !a.stats_out && pl.R >= RING_WARPS && pl.stages <= 8) {
+        if (warp_rows && !sparse && pl.R >= RING_WARPS && pl.stages <= 8) {
             static bool attr_w[2][16] = {{false}};
             int dev = 0;
             PI_CUDA(cudaGetDevice(&dev));
@@ -837,32 +639,26 @@ int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaSt
         if (grp < 0) { const char * v = getenv("PI_RING_G"); grp = !(v && v[0] == '0'); }
         const int nv = pl.R * (gated ? 2 : 1);
         const int units = q4 ? (int)(a.ncols / QK) : (int)(a.ncols / 8);
-        if (grp && !a.fin.on && !a.res_add && !a.stats_out && pl.stages <= 8 && nv <= RING_WARPS && RING_WARPS % nv == 0 &&
+        if (grp && pl.stages <= 8 && nv <= RING_WARPS && RING_WARPS % nv == 0 &&
             units % (RING_WARPS / nv) == 0 && (sparse || pl.R < RING_WARPS)) {
             if (!sparse) return q4 ? launch_ring_g<PI_TYPE_Q4_0, false, false>(p, pl, pdl, st) : launch_ring_g<PI_TYPE_F16, false, false>(p, pl, pdl, st);
             if (gated)   return q4 ? launch_ring_g<PI_TYPE_Q4_0, true, true>(p, pl, pdl, st) : launch_ring_g<PI_TYPE_F16, true, true>(p, pl, pdl, st);
             return q4 ? launch_ring_g<PI_TYPE_Q4_0, true, false>(p, pl, pdl, st) : launch_ring_g<PI_TYPE_F16, true, false>(p, pl, pdl, st);
         }
     }
-#define PI_RING_DISPATCH_RW(FUSED, RW)                                                                                                     \
+#define PI_RING_DISPATCH_RW(RW)                                                                                                            \
     do {                                                                                                                                   \
-        if (!sparse) return q4 ? launch_ring_inst<PI_TYPE_Q4_0, false, false, FUSED, RW>(p, pl, pdl, st)                                   \
-                               : launch_ring_inst<PI_TYPE_F16, false, false, FUSED, RW>(p, pl, pdl, st);                                   \
-        if (gated)   return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, true, FUSED, RW>(p, pl, pdl, st)                                     \
-                               : launch_ring_inst<PI_TYPE_F16, true, true, FUSED, RW>(p, pl, pdl, st);                                     \
-        return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, false, FUSED, RW>(p, pl, pdl, st)                                                 \
-                  : launch_ring_inst<PI_TYPE_F16, true, false, FUSED, RW>(p, pl, pdl, st);                                                 \
+        if (!sparse) return q4 ? launch_ring_inst<PI_TYPE_Q4_0, false, false, RW>(p, pl, pdl, st)                                          \
+                               : launch_ring_inst<PI_TYPE_F16, false, false, RW>(p, pl, pdl, st);                                          \
+        if (gated)   return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, true, RW>(p, pl, pdl, st)                                            \
+                               : launch_ring_inst<PI_TYPE_F16, true, true, RW>(p, pl, pdl, st);                                            \
+        return q4 ? launch_ring_inst<PI_TYPE_Q4_0, true, false, RW>(p, pl, pdl, st)                                                        \
+                  : launch_ring_inst<PI_TYPE_F16, true, false, RW>(p, pl, pdl, st);                                                        \
     } while (0)
-#define PI_RING_DISPATCH(FUSED)                                                                                                            \
-    do {                                                                                                                                   \
-        if (pl.rw == 4) PI_RING_DISPATCH_RW(FUSED, 4);                                                                                     \
-        if (pl.rw == 2) PI_RING_DISPATCH_RW(FUSED, 2);                                                                                     \
-        PI_RING_DISPATCH_RW(FUSED, 1);                                                                                                     \
-    } while (0)
-    if (a.fin.on) PI_RING_DISPATCH(true);
-    PI_RING_DISPATCH(false);
+    if (pl.rw == 4) PI_RING_DISPATCH_RW(4);
+    if (pl.rw == 2) PI_RING_DISPATCH_RW(2);
+    PI_RING_DISPATCH_RW(1);
 #undef PI_RING_DISPATCH_RW
-#undef PI_RING_DISPATCH
 }
 
 }  // namespace pi

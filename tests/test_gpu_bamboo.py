@@ -2,8 +2,7 @@
 (LLM_FFN_SYM, llama.cpp:4732-4738, 5028).  The engine gets it from the gated mat-vec's relu-on-output switch, since
 relu(gate) * relu(up) == relu(relu(gate) * up) exactly when the first factor is non-negative.  Checked like the other
 architectures: teacher-forced logits and the greedy stream against the reference's llama.cpp run of a `bamboo` model file
-(golden fixture), the active sets against the CPU checker, a batch against single sequences, and the file loader.  The
-file name sorts last so that a run that stops at the first failure has already executed every other test."""
+(golden fixture), the active sets against the CPU checker, a batch against single sequences, and the file loader."""
 import os
 
 import numpy as np

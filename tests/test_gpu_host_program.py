@@ -1,8 +1,7 @@
 """The C++ host program powerinfer_b200/host/pi_decode.cpp on a GPU: model file -> native reader -> uploads (Q4_0 through
 pi_q4_0_repack, q / k / v stacked, falcon's fused matrix as stored) -> engine -> greedy ids, which must equal the
 reference's llama.cpp stream for the same file and prompt (golden fixtures).  No Python touches the data path; this test
-only writes the file and compares the printed ids.  The file name sorts last so that a run that stops at the first failure
-has already executed every other test."""
+only writes the file and compares the printed ids."""
 import os
 import subprocess
 

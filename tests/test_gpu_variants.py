@@ -1,6 +1,7 @@
-"""Alternative launch sequences of the batch-1 step (kept behind environment switches) must give the same results as the
-default one: the fused sparse-FFN kernel (PI_FFN_FUSED=1), consumer-side norms (PI_FUSE=1), no programmatic dependent
-launch (PI_PDL=0), the weight streamer, the ring kernels with a block barrier per stage, the single-CTA norm.  Each variant runs in a child process because the switches are read when an engine is created."""
+"""Alternative launch sequences of the one-token step (diagnostic environment switches) must give the same results as the
+default one: the list-driven sparse kernels instead of the mask-driven register-streaming ones (PI_ROWS=0), no
+programmatic dependent launch (PI_PDL=0), the ring kernels with a block barrier per stage, the single-CTA norm.  Each
+variant runs in a child process because the switches are read when an engine is created."""
 import os
 import subprocess
 import sys
@@ -45,8 +46,8 @@ def test_step_variants_agree(tmp_path):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     base = run_variant(tmp_path, "base", {})
-    for tag, env in (("ffn_fused", {"PI_FFN_FUSED": "1"}), ("fused_norms", {"PI_FUSE": "1"}), ("no_pdl", {"PI_PDL": "0"}), ("streamer", {"PI_PREFETCH": "1"}), ("rw4", {"PI_RING_RW": "4"}),
-                     ("block_barrier_ring", {"PI_RING_W": "0", "PI_RING_G": "0"}), ("single_cta_norm", {"PI_NORM_CLUSTER": "0"})):
+    for tag, env in (("list_kernels", {"PI_ROWS": "0"}), ("no_pdl", {"PI_PDL": "0"}), ("rw4", {"PI_RING_RW": "4"}),
+                     ("block_barrier_ring", {"PI_RING_W": "0", "PI_RING_G": "0", "PI_ROWS": "0"}), ("single_cta_norm", {"PI_NORM_CLUSTER": "0"})):
         got = run_variant(tmp_path, tag, env)
         for name in base.files:
             err = float(np.abs(got[name] - base[name]).max())

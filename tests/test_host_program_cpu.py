@@ -1,7 +1,7 @@
 """powerinfer_b200/host/pi_decode.cpp (a C++ program that decodes through the C ABI alone) compiles and links against the
 header and the library, reads a model file with the native reader and reports its configuration; without a device it stops
 at its first CUDA call with a message and exit code 1 (there is no CPU path to fall back to).  Its output on a GPU is
-checked in tests/test_zzzz_gpu_host_program.py."""
+checked in tests/test_gpu_host_program.py."""
 import os
 import shutil
 import subprocess

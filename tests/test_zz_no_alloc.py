@@ -4,9 +4,9 @@ A host that owns every byte of HBM (a serving process with a fixed arena) can fo
 code that runs during a stream capture cannot allocate either; such callers have no workspace to hand to pi_axpy.  This
 entry point takes its scratch from an array inside the library instead.  The test calls it through the C ABI twice in a
 row with different masks (so stale scratch contents from the first call would show in the second) and compares with
-pi_axpy given an ordinary workspace; both run the same kernels in the same order, so the outputs must be identical,
-which is inside the 2e-4 tolerance the other operator tests use.  The file name sorts last so that a run that stops at the
-first failure has already executed every other test.
+pi_axpy given an ordinary workspace (both run the same kernels in the same order, so the outputs must be identical) and
+with the CPU checker's axpy on the same inputs, within the 2e-4 tolerance the other operator tests use.  The file name
+sorts last so that a run that stops at the first failure has already executed every other test.
 """
 import ctypes as C
 
@@ -25,7 +25,7 @@ def dev(a):
 
 
 @pytest.mark.parametrize("wtype", [synth.F16, synth.Q4_0])
-def test_axpy_static_matches_axpy_on_two_calls_in_a_row(wtype):
+def test_axpy_static_matches_axpy_on_two_calls_in_a_row(wtype, oracle):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     from powerinfer_b200 import ggml_ops
@@ -48,6 +48,8 @@ def test_axpy_static_matches_axpy_on_two_calls_in_a_row(wtype):
         torch.cuda.synchronize()
         assert np.abs(got.cpu().numpy() - want.cpu().numpy()).max() <= ATOL, f"call {call}"
         assert torch.equal(got, want), f"call {call}: same kernels, same order"
+        ref = oracle.axpy(wtype, Wt, F, d, h, idx, np.zeros(F, np.int32))
+        assert np.abs(got.cpu().numpy() - ref).max() <= ATOL, f"call {call}: against the CPU checker"
 
 
 def test_axpy_static_rejects_shapes_beyond_its_scratch():
