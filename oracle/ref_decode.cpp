@@ -1,8 +1,13 @@
 // ref_decode.cpp -- drives the REFERENCE's own llama.cpp through llama.h (TEST INFRASTRUCTURE ONLY).
 //
-// Compiled by oracle/Makefile against the reference's unmodified llama.cpp + ggml (CPU-only build,
-// which is the --vram-budget 0 path: nothing offloaded, every layer's gpu_idx all zero) into
-// oracle/_ref/ref_decode.  It loads a PowerInfer ("PWRI") GGUF, feeds explicit token ids, and dumps
+// Compiled by oracle/Makefile against the reference's unmodified llama.cpp + ggml twice:
+//   oracle/_ref/ref_decode       CPU-only build, which is the --vram-budget 0 path (nothing offloaded, every layer's
+//                                gpu_idx all zero): the parity oracle;
+//   oracle/_ref/ref_decode_b200  the same sources with -DGGML_USE_CUBLAS, linked against libggml_cuda_b200.so instead
+//                                of the reference's ggml-cuda.cu: the reference's own llama_decode -> llm_build_ffn_sparse
+//                                -> ggml_graph_compute running over this repository's back end.  REF_VRAM_GB sets
+//                                llama_model_params::vram_budget_gb (default 0 = nothing offloaded); at exit it prints,
+//                                per ggml op, how many nodes the back end served and how many it handed back to the CPU.  It loads a PowerInfer ("PWRI") GGUF, feeds explicit token ids, and dumps
 // the raw logits of every step plus the greedy (argmax of raw logits) continuation, which is what
 // llama_sample_token_greedy does; examples/main is not used because its sampler applies a repeat
 // penalty even at temperature 0.
@@ -22,6 +27,19 @@
 #include <cstring>
 #include <string>
 #include <vector>
+
+#ifdef GGML_USE_CUBLAS
+#include "ggml.h"
+extern "C" void ggml_cuda_b200_counts(int op, long long * served, long long * declined);
+extern "C" int  ggml_cuda_b200_op_count(void);
+static void print_backend_counts() {
+    for (int op = 0; op < ggml_cuda_b200_op_count(); op++) {
+        long long s = 0, d = 0;
+        ggml_cuda_b200_counts(op, &s, &d);
+        if (s || d) fprintf(stderr, "b200_nodes op=%s served=%lld declined=%lld\n", ggml_op_name((enum ggml_op)op), s, d);
+    }
+}
+#endif
 
 static int argmax(const float * x, int n) {
     int b = 0;
@@ -55,7 +73,7 @@ int main(int argc, char ** argv) {
     llama_backend_init(false);
     llama_model_params mp = llama_model_default_params();
     mp.n_gpu_layers = 0;
-    mp.vram_budget_gb = 0;
+    mp.vram_budget_gb = getenv("REF_VRAM_GB") ? (float)atof(getenv("REF_VRAM_GB")) : 0.0f;
     mp.use_mmap = true;
     llama_model * model = llama_load_model_from_file(model_path, mp);
     if (!model) { fprintf(stderr, "load failed\n"); return 1; }
@@ -100,6 +118,9 @@ int main(int argc, char ** argv) {
     const int64_t t1 = llama_time_us();
     fprintf(stderr, "ref_decode: %d decode steps in %.3f ms (%d threads)\n", n_steps - 1, (t1 - t0)/1000.0, n_threads);
     fclose(out);
+#ifdef GGML_USE_CUBLAS
+    print_backend_counts();
+#endif
     llama_free(ctx);
     llama_free_model(model);
     llama_backend_free();

@@ -62,5 +62,35 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+GGML_LIB = os.path.join(HERE, "libggml_cuda_b200.so")
+
+
+def reference_dir():
+    """The reference checkout whose ggml.h the drop-in back end is compiled against: $POWERINFER_REF, else a sibling
+    directory `reference` next to this repository; None when neither exists."""
+    for cand in (os.environ.get("POWERINFER_REF"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "ggml-cuda.h")):
+            return os.path.abspath(cand)
+    return None
+
+
+def build_ggml_backend(force: bool = False) -> str | None:
+    """powerinfer_b200/libggml_cuda_b200.so: the ggml-cuda.h symbol set over libpowerinfer_b200.so.  It reads struct
+    ggml_tensor, so it needs the reference's headers at compile time; where they are absent the prebuilt file is kept."""
+    ref = reference_dir()
+    src = os.path.join(HERE, "ggml_backend", "ggml_cuda_b200.cu")
+    if ref is None:
+        return GGML_LIB if os.path.exists(GGML_LIB) else None
+    if force or _stale(GGML_LIB, [src, LIB, os.path.join(os.path.dirname(HERE), "include", "powerinfer_b200.h")]):
+        r = subprocess.run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+                            "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", ref, "-I", os.path.join(os.path.dirname(HERE), "include"),
+                            "-o", GGML_LIB, src, "-L", HERE, "-lpowerinfer_b200", "-Xlinker", "-rpath=$ORIGIN"],
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("ggml back end failed to build:\n" + r.stdout + r.stderr)
+    return GGML_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True))
+    print(build_ggml_backend(force="--force" in sys.argv))
