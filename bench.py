@@ -44,13 +44,37 @@ def measured_peaks():
         return 6650.0, "fallback"
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each stage's kernels from the committed
-# `ncu --set full` capture of the 4-layer case of the same layer shape (profiles/step_kernels_*_ncu_full.md); traffic per
-# launch does not depend on the layer count.  Stages with two kernels give the mean over their launches.
-NCU_TRAFFIC = {
-    "relu-llama-70b-q4_0": {"predictor": (16.82e6 + 58.78e6) / 2, "qkv": 47.22e6, "out_proj": 37.78e6, "up_gate": 30.50e6,
-                            "down": (15.49e6 + 4.86e6) / 2},
-}
+def ncu_traffic(cfg_name: str) -> dict:
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each stage's kernels, from the ncu capture
+    of the 4-layer case of the same layer shape (traffic per launch does not depend on the layer count).  The figures
+    live in a text file next to the ncu summaries, one `stage bytes` pair per line after a header naming the commit they
+    were captured at; a stage whose kernel changed since is simply absent there and reports null."""
+    out = {}
+    try:
+        with open(os.path.join(ROOT, "profiles", f"dram_traffic_{cfg_name}.txt")) as f:
+            for line in f:
+                parts = line.split()
+                if len(parts) >= 2 and not line.startswith("#"):
+                    out[parts[0]] = float(parts[1])
+    except OSError:
+        pass
+    return out
+
+
+def physical_cores() -> int:
+    try:
+        import psutil
+        n = psutil.cpu_count(logical=False)
+        if n:
+            return int(n)
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+def pi_env() -> dict:
+    """Every PI_* switch in effect: a line with an empty dict ran the default kernels."""
+    return {k: v for k, v in sorted(os.environ.items()) if k.startswith("PI_")}
 
 # ------------------------------------------------------------------------------------------------ clocks
 
@@ -104,7 +128,7 @@ def cpu_reference(spec, n_threads: int | None = None) -> dict:
     from oracle import pio
     from powerinfer_b200 import synth
     ref = pio.Ref()
-    nth = n_threads or os.cpu_count() or 1
+    nth = n_threads or physical_cores()
     rng = np.random.default_rng(0)
     d, F, R, dkv = spec.d, spec.n_ff, spec.rank, spec.d_kv
     q4 = spec.wtype == synth.Q4_0
@@ -144,7 +168,7 @@ def cpu_reference(spec, n_threads: int | None = None) -> dict:
     return {"value": 1.0 / per_token, "unit": "tok/s", "cores": nth, "kind": "reference",
             "sample": f"reference ggml CPU ops (oracle/_ref, AVX2 build) for 1 of {spec.n_layer} layers "
                       f"(qkv, out-proj, predictor, mul_mat_idx up/gate, axpy down) + lm head at the config's shape, best of {reps}, "
-                      f"{nth} threads, extrapolated x{spec.n_layer}; attention/norm/RoPE nodes not included",
+                      f"{nth} threads (the machine's physical cores), extrapolated x{spec.n_layer}; attention/norm/RoPE nodes not included",
             "ms_per_layer": {k: round(v * 1e3, 4) for k, v in t.items()}, "ms_per_token": per_token * 1e3}
 
 
@@ -229,7 +253,7 @@ def sparse_ffn_microbench(args):
         try:
             from oracle import pio
             ref = pio.Ref()
-            nth = os.cpu_count() or 1
+            nth = physical_cores()
             for wtype, wname in ((synth.F16, "F16"), (synth.Q4_0, "Q4_0")):
                 wf = rng.standard_normal((F, d), dtype=np.float32) * np.float32(0.02)
                 W = ref.quantize_q4_0(wf) if wtype == synth.Q4_0 else wf.astype(np.float16)
@@ -260,7 +284,7 @@ def sparse_ffn_microbench(args):
                          "frac": head["sparse_ffn"]["frac_of_measured_peak"], "peak_source": f"of {peak_kind}", "traffic": None},
             "cpu_baseline": ({"value": head_cpu["sparse_ffn"]["GBps"], "unit": "GB/s", "cores": head_cpu["threads"], "kind": "reference",
                               "sample": "reference ggml mul_mat_idx x2 + axpy on the same shape and sparsity, batch 1, best of 3"} if head_cpu else None),
-            "table": table, "cpu_table": cpu}
+            "table": table, "cpu_table": cpu, "env_overrides": pi_env()}
     _emit(line)
 
 
@@ -335,8 +359,8 @@ def main():
             if time.time() - t0 > 120:
                 break
         best = max(steps, key=lambda r: r["value"])
-        line = {"impl": "reference", "metric": metric, "value": best["value"], "unit": "tok/s", "n_gpus": args.gpus, "steps": K,
-                "warmup": W, "ms_per_step": best["ms_per_token"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        line = {"impl": "reference", "metric": metric, "value": best["value"], "unit": "tok/s", "n_gpus": args.gpus, "steps": len(steps),
+                "warmup": 0, "steps_requested": K, "ms_per_step": best["ms_per_token"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "q4_0xq8_0 int8 dot, f32 accumulate" if spec.wtype == 2 else "f16 weights, f32 accumulate",
                 "data": "synthetic", "config": config, "cpu_baseline": best,
                 "e2e": {"value": best["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -446,14 +470,14 @@ def main():
                        "serialised_ms_per_step": round(stage_ms[st], 4)}
         dom = max(ops, key=lambda k: ops[k]["ms_per_step"])
         roofline = {"bound": "hbm", "kernel": {"qkv": "k_gemv_ring_w (dense, QKV rows)", "out_proj": "k_gemv_ring_w (dense, out-proj)",
-                                               "predictor": "k_gemv_ring_g + k_gemv_ring_w (dense F16, fc1 + fc2)", "up_gate": "k_gemv_ring_g (gather, up+gate)",
-                                               "down": "k_axpy_pipe + k_reduce_partials", "lm_head": "k_gemv_ring_w (dense, lm head)"}[dom],
+                                               "predictor": "k_gemv_ring_g + k_gemv_ring_w (dense F16, fc1 + fc2)", "up_gate": "k_gather_rows (gather, up+gate)",
+                                               "down": "k_axpy_rows", "lm_head": "k_gemv_ring_w (dense, lm head)"}[dom],
                     "achieved": ops[dom]["GBps"], "peak": peak, "unit": "GB/s", "frac": round(ops[dom]["GBps"] / peak, 3),
                     "peak_source": f"of {peak_kind}", "launches_per_step": ops[dom]["launches_per_step"],
                     "bytes_per_launch": bytes_tok[dom] / world / ops[dom]["launches_per_step"],
                     "mean_launch_us": ops[dom]["us_per_launch"],
                     "how": "this stage's kernels for every layer, back to back in a CUDA graph as inside a step, CUDA events around 5 replays",
-                    "traffic": NCU_TRAFFIC.get(cfg_name, {}).get(dom) if world == 1 else None}
+                    "traffic": ncu_traffic(cfg_name).get(dom) if world == 1 else None}
         step_bytes = bytes_tok["total"] / world
         line = {"metric": metric, "value": K * T / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -466,7 +490,7 @@ def main():
                              "GBps": round(step_bytes / (ms / K * 1e-3) / 1e9, 1),
                              "frac_of_measured_peak": round(step_bytes / (ms / K * 1e-3) / 1e9 / peak, 3)},
                 "ops": ops, "stage_ms_profiled": {k: round(v, 4) for k, v in stage_ms.items()},
-                "mean_active_neurons_per_layer": round(active, 1)}
+                "mean_active_neurons_per_layer": round(active, 1), "env_overrides": pi_env()}
         if world == 1 and not args.no_cpu_baseline:
             try:
                 line["cpu_baseline"] = cpu_reference(spec)

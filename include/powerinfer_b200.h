@@ -211,15 +211,19 @@ typedef struct {
 } pi_model_weights;
 
 /* Peer mailboxes for the per-layer exchange of partial d_model vectors (n_ranks > 1).  Every rank owns a mailbox
- * [2, n_ranks, slot_floats] F32 and flags [2, n_ranks] u32 in ITS OWN memory; peers write into it with plain stores
- * (the mapped addresses of every rank's mailbox and flags, own included, are listed here), nobody reads remote memory.
- * slot_floats >= max_batch * d.  `epoch` and `ticket` are zero-initialised u32 words in this rank's memory. */
+ * [2, n_ranks, slot_floats] F32 and flags [2, n_ranks, flag_words] u32 in ITS OWN memory; peers write into it with plain
+ * stores (the mapped addresses of every rank's mailbox and flags, own included, are listed here), nobody reads remote
+ * memory.  slot_floats >= max_batch * d, flag_words >= 8 * max_batch.  `epoch` is a zero-initialised u32 word in this
+ * rank's memory: the engine counts its steps there (all ranks run the same steps, so all agree on the number of every
+ * exchange); `ticket` is not used.  The exchange itself is part of the norm kernel that consumes the sum: it pushes this
+ * rank's share, raises one flag per slice of the vector, waits (bounded) for the other ranks' flags of its own slice. */
 typedef struct {
     int n_ranks, rank_id;
     int64_t slot_floats;
     float * mailbox_local; unsigned int * flags_local;
     float * mailbox_peer[PI_MAX_RANKS]; unsigned int * flags_peer[PI_MAX_RANKS];
     unsigned int * epoch, * ticket;
+    int flag_words;
 } pi_exchange;
 
 typedef struct pi_engine pi_engine;
@@ -274,11 +278,16 @@ int  pi_engine_profile_step(pi_engine * e, int T, float * host_ms, int * host_la
  * inputs: run a real step afterwards before using results.  Synchronises `stream`. */
 int  pi_engine_time_stage(pi_engine * e, int T, int stage, int reps, float * host_ms_per_rep, int * host_launches, void * stream);
 
-/* Device status word: 0, or PI_ERR_TIMEOUT after an exchange wait ran out.  Synchronises `stream`. */
+/* Device status word: PI_OK, or PI_ERR_TIMEOUT after a bounded device-side wait ran out (an exchange whose peer never
+ * delivered, a bulk copy that never landed); the step that hit it still ran to its end.  The word is cleared once it has
+ * been reported, and the engine stays usable.  Synchronises `stream`. */
 int  pi_engine_status(pi_engine * e, void * stream);
+/* Bound of the exchange waits in SM clock cycles (0: the default, about a second). */
+int  pi_engine_set_wait_cycles(pi_engine * e, long long cycles);
 
-/* For tests: device pointers of the predictor logits F32 [T, n_ff/n_ranks], active list and count that the LAST layer
- * of the last step left behind. */
+/* For tests: device pointers of the predictor logits F32 [T, n_ff/n_ranks] that the LAST layer of the last step left
+ * behind, and the sorted active list and count of its first sequence (built here when the step itself only made bit
+ * masks).  Synchronises the device. */
 int  pi_engine_debug(pi_engine * e, float ** pred, int32_t ** list, int32_t ** count);
 /* For tests: keep every layer's predictor logits.  pred_trace F32 [n_layer, max_batch, n_ff/n_ranks] (NULL: off). */
 int  pi_engine_set_trace(pi_engine * e, float * pred_trace);

@@ -174,9 +174,13 @@ struct NormArgs {
     const float * partial = nullptr; int n_groups = 0; const float * residual = nullptr; const float * residual2 = nullptr;
     const float * in_bias = nullptr;
     int64_t partial_stride = 0;        // floats between consecutive partials (0: T * n)
-    // when the partials are another ranks' mailbox slots: wait (bounded) until every flag reached *wait_epoch first;
-    // the slot set in use is parity (*wait_epoch & 1): partial += parity * n_groups * partial_stride
-    const unsigned int * wait_flags = nullptr; const unsigned int * wait_epoch = nullptr; unsigned int * status = nullptr;
+    // Sharded runs (xch != nullptr): the vector built so far (sum of the partials | x, + xch_extra) is this rank's share.
+    // The norm pushes it into slot rank_id of every rank's mailbox (plain stores, then a release flag per slice of the
+    // vector), waits (bounded by wait_cycles; on expiry bit 0 of *status is raised and the kernel carries on) for every
+    // rank's flag of the same slice in ITS OWN mailbox, and adds the slots in rank order, so all ranks hold identical sums.
+    // xch_index is the number of this exchange within the step (0 .. xch_per_step - 1).
+    const pi_exchange * xch = nullptr; int xch_index = 0, xch_per_step = 1; const float * xch_extra = nullptr;
+    long long wait_cycles = 0; unsigned int * status = nullptr;
     float * x_out = nullptr;
     float * y = nullptr;               // optional F32 output
     int act_type = 0; ActBuf act;      // optional activation planes of the normalised vector (0: none, else PI_TYPE_*)
@@ -200,10 +204,8 @@ struct AttnArgs {
 };
 int launch_attention(const AttnArgs & a, cudaStream_t st);
 
-// v = sum_g partial[g, t, :] (+ extra[t, :]) is written into slot rank_id of every rank's mailbox, then the flags are
-// raised to the next epoch (see pi_exchange in the public header)
-int launch_exchange_push(const pi_exchange & x, const float * partial, int n_groups, int T, int64_t n, const float * extra,
-                         unsigned int * status, cudaStream_t st, bool pdl = false);
+// flag words per (parity, rank) in a mailbox: one per (token, slice of the vector)
+static constexpr int XCH_SLICES = 8;
 
 // ------------------------------------------------------------------------------------ device primitives
 #ifdef __CUDACC__

@@ -20,7 +20,11 @@ static constexpr int NORM_CHUNKS = 2;
 struct NormP {
     const float * x; int64_t n; int rms; float eps; const float * w; const float * b;
     const float * partial; int n_groups; int T; const float * residual; const float * residual2; const float * in_bias; float * x_out;
-    int64_t partial_stride; const unsigned int * wait_flags; const unsigned int * wait_epoch; unsigned int * status;
+    int64_t partial_stride; unsigned int * status;
+    // exchange (see NormArgs): mailboxes and flags of every rank, this rank's own, the step counter
+    int x_ranks, x_rank, x_index, x_per_step, x_flag_words; int64_t x_slot; long long x_wait;
+    float * x_mbox[PI_MAX_RANKS]; unsigned int * x_flags[PI_MAX_RANKS]; const float * x_mbox_local; const unsigned int * x_flags_local;
+    const unsigned int * x_step; const float * x_extra;
     float * y; int act_type; ActBuf act; int act2_type; ActBuf act2; int act2_src;
 };
 
@@ -92,26 +96,6 @@ __global__ void __launch_bounds__(MAXT) k_norm(const NormP p) {
     pdl_wait();
     const size_t tn = p.partial_stride ? (size_t)p.partial_stride : (size_t)p.T * n;
     const float * partial = p.partial;
-    if (p.wait_flags) {
-        // the partials are mailbox slots written by the other ranks: wait for their flags, but never forever
-        const unsigned int epoch = *p.wait_epoch;
-        const unsigned int par = epoch & 1u;
-        if (threadIdx.x < (unsigned)p.n_groups) {
-            const volatile unsigned int * f = p.wait_flags + par * p.n_groups + threadIdx.x;
-            const long long t0 = clock64();
-            bool ok_flag = false;
-            for (;;) {
-                unsigned int seen;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f));
-                if ((int)(seen - epoch) >= 0) { ok_flag = true; break; }
-                if (clock64() - t0 > 2000000000LL) break;          // about a second
-                __nanosleep(64);
-            }
-            if (!ok_flag) atomicOr(p.status, 1u);
-        }
-        __syncthreads();
-        partial += (size_t)par * p.n_groups * tn;
-    }
     // ---- all loads of all chunks first (x_out may alias the inputs, so the compiler cannot move a load across a store
     //      itself): one round trip instead of one per chunk
     float v[NORM_CHUNKS][8];
@@ -288,29 +272,8 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
         v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
     };
     if (p.partial) {
-        // the vector is the sum of n_groups slots (the ranks' mailbox slots when wait_flags is given: every CTA of the
-        // cluster waits, bounded, for all flags, then adds its slice of the slots in rank order)
         const size_t tn = p.partial_stride ? (size_t)p.partial_stride : (size_t)p.T * n;
         const float * partial = p.partial;
-        if (p.wait_flags) {
-            const unsigned int epoch = *p.wait_epoch;
-            const unsigned int par = epoch & 1u;
-            if (threadIdx.x < (unsigned)p.n_groups) {
-                const volatile unsigned int * f = p.wait_flags + par * p.n_groups + threadIdx.x;
-                const long long t0 = clock64();
-                bool ok_flag = false;
-                for (;;) {
-                    unsigned int seen;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f));
-                    if ((int)(seen - epoch) >= 0) { ok_flag = true; break; }
-                    if (clock64() - t0 > 2000000000LL) break;          // about a second
-                    __nanosleep(64);
-                }
-                if (!ok_flag) atomicOr(p.status, 1u);
-            }
-            __syncthreads();
-            partial += (size_t)par * p.n_groups * tn;
-        }
         constexpr int GP = 12;                                         // slots in flight per pass
         float4 a[GP], b[GP];
         for (int g0 = 0; g0 < p.n_groups; g0 += GP) {
@@ -327,6 +290,51 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
         }
     } else {
         add8(*reinterpret_cast<const float4 *>(p.x + o), *reinterpret_cast<const float4 *>(p.x + o + 4));
+    }
+    if (p.x_ranks > 1) {
+        // ---- exchange: v is this rank's share.  Push it to every rank's mailbox, flag this (token, slice), wait for every
+        //      rank's flag of the same (token, slice) in this rank's own mailbox, add the slots in rank order.
+        if (p.x_extra) add8(*reinterpret_cast<const float4 *>(p.x_extra + o), *reinterpret_cast<const float4 *>(p.x_extra + o + 4));
+        const unsigned int epoch = __ldcg(p.x_step) * (unsigned)p.x_per_step + (unsigned)p.x_index + 1u;
+        const unsigned int par = epoch & 1u;
+        const size_t slot = ((size_t)par * p.x_ranks + p.x_rank) * (size_t)p.x_slot + o;
+        const float4 v0 = make_float4(v[0], v[1], v[2], v[3]), v1 = make_float4(v[4], v[5], v[6], v[7]);
+        for (int q = 0; q < p.x_ranks; q++) {
+            *reinterpret_cast<float4 *>(p.x_mbox[q] + slot) = v0;
+            *reinterpret_cast<float4 *>(p.x_mbox[q] + slot + 4) = v1;
+        }
+        __threadfence_system();
+        __syncthreads();
+        const size_t fl = ((size_t)par * p.x_ranks) * p.x_flag_words + blockIdx.x;          // + rank * flag_words
+        if (threadIdx.x < (unsigned)p.x_ranks) {
+            unsigned int * f = p.x_flags[threadIdx.x] + fl + (size_t)p.x_rank * p.x_flag_words;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(f), "r"(epoch) : "memory");
+            const unsigned int * mine = p.x_flags_local + fl + (size_t)threadIdx.x * p.x_flag_words;
+            const long long t0 = clock64();
+            bool ok_flag = false;
+            for (;;) {
+                unsigned int seen;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine));
+                if ((int)(seen - epoch) >= 0) { ok_flag = true; break; }
+                if (clock64() - t0 > p.x_wait) break;                  // never forever: the step finishes, the host reads the status
+                __nanosleep(64);
+            }
+            if (!ok_flag) atomicOr(p.status, 1u);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = 0.f;
+        float4 a[PI_MAX_RANKS], b[PI_MAX_RANKS];
+#pragma unroll
+        for (int q = 0; q < PI_MAX_RANKS; q++) {
+            a[q] = z4; b[q] = z4;
+            if (q < p.x_ranks) {
+                const float * sp = p.x_mbox_local + ((size_t)par * p.x_ranks + q) * (size_t)p.x_slot + o;
+                a[q] = __ldcg(reinterpret_cast<const float4 *>(sp)); b[q] = __ldcg(reinterpret_cast<const float4 *>(sp + 4));
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < PI_MAX_RANKS; q++) add8(a[q], b[q]);
     }
     if (p.in_bias) add8(*reinterpret_cast<const float4 *>(p.in_bias + c), *reinterpret_cast<const float4 *>(p.in_bias + c + 4));
     if (p.residual) add8(r0, r1);
@@ -411,14 +419,29 @@ int launch_norm(const NormArgs & a, cudaStream_t st) {
     NormP p;
     p.x = a.x; p.n = a.n; p.rms = a.rms; p.eps = a.eps; p.w = a.w; p.b = a.b;
     p.partial = a.partial; p.n_groups = a.n_groups; p.T = a.T; p.residual = a.residual; p.residual2 = a.residual2; p.in_bias = a.in_bias; p.x_out = a.x_out;
-    p.partial_stride = a.partial_stride; p.wait_flags = a.wait_flags; p.wait_epoch = a.wait_epoch; p.status = a.status;
+    p.partial_stride = a.partial_stride; p.status = a.status;
+    p.x_ranks = 1; p.x_rank = 0; p.x_index = 0; p.x_per_step = 1; p.x_flag_words = 0; p.x_slot = 0; p.x_wait = 0;
+    p.x_mbox_local = nullptr; p.x_flags_local = nullptr; p.x_step = nullptr; p.x_extra = nullptr;
+    for (int q = 0; q < PI_MAX_RANKS; q++) { p.x_mbox[q] = nullptr; p.x_flags[q] = nullptr; }
+    const bool xch = a.xch && a.xch->n_ranks > 1;
+    if (xch) {
+        const pi_exchange & x = *a.xch;
+        PI_REQUIRE(x.n_ranks <= PI_MAX_RANKS && x.mailbox_local && x.flags_local && x.epoch && a.status, "norm: exchange not configured");
+        PI_REQUIRE((int64_t)a.T * a.n <= x.slot_floats, "norm: vector of %lld floats does not fit a mailbox slot", (long long)a.T * a.n);
+        PI_REQUIRE(a.T * XCH_SLICES <= x.flag_words, "norm: %d tokens need %d flag words per rank, the mailbox has %d", a.T, a.T * XCH_SLICES, x.flag_words);
+        p.x_ranks = x.n_ranks; p.x_rank = x.rank_id; p.x_index = a.xch_index; p.x_per_step = a.xch_per_step; p.x_flag_words = x.flag_words;
+        p.x_slot = x.slot_floats; p.x_wait = a.wait_cycles > 0 ? a.wait_cycles : 2000000000LL;       // about a second
+        for (int q = 0; q < x.n_ranks; q++) { p.x_mbox[q] = x.mailbox_peer[q]; p.x_flags[q] = x.flags_peer[q]; }
+        p.x_mbox_local = x.mailbox_local; p.x_flags_local = x.flags_local; p.x_step = x.epoch; p.x_extra = a.xch_extra;
+    }
     p.y = a.y; p.act_type = a.act_type; p.act = a.act; p.act2_type = a.act2_type; p.act2 = a.act2; p.act2_src = a.act2_src;
     static int use_cluster = -1;
     if (use_cluster < 0) { const char * v = getenv("PI_NORM_CLUSTER"); use_cluster = !(v && v[0] == '0'); }
-    if (use_cluster && (a.x || a.partial)) {
+    if ((use_cluster || xch) && (a.x || a.partial)) {
         int cs = 0;
-        for (int k = 8; k >= 2; k /= 2) if (a.n % (k * 256) == 0 && a.n / k / 8 <= 256) { cs = k; break; }
+        for (int k = 8; k >= (xch ? 1 : 2); k /= 2) if (a.n % (k * 256) == 0 && a.n / k / 8 <= 256) { cs = k; break; }
         if (cs) {
+            PI_REQUIRE(cs <= XCH_SLICES, "norm: cluster larger than the flag layout");
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(a.T * cs); cfg.blockDim = dim3((unsigned)(a.n / cs / 8)); cfg.dynamicSmemBytes = 0; cfg.stream = st;
             cudaLaunchAttribute attr[2];
@@ -431,6 +454,7 @@ int launch_norm(const NormArgs & a, cudaStream_t st) {
             return PI_OK;
         }
     }
+    PI_REQUIRE(!xch, "norm: the exchange needs a vector length that is a multiple of 256 with at most 2048 values per slice (got %lld)", (long long)a.n);
     int threads = (int)((a.n / 8 + NORM_CHUNKS - 1) / NORM_CHUNKS);
     threads = min(1024, max(32, (threads + 31) / 32 * 32));
     if (threads <= 512) PI_CUDA(launch_k(k_norm<512>, dim3(a.T), dim3(threads), 0, st, a.pdl, p));

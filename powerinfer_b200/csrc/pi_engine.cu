@@ -22,8 +22,9 @@ namespace pi {
 // ggml_get_rows on the F16 embedding (+ OPT's learned positions at pos + 2: llama.cpp:5105-5108, 6486-6488)
 __global__ void k_embed(const __half * __restrict__ tok_embd, const __half * __restrict__ pos_embd,
                         const int32_t * __restrict__ tokens, const int32_t * __restrict__ pos, int n_vocab, int n_pos,
-                        int64_t d, float * __restrict__ x) {
+                        int64_t d, float * __restrict__ x, unsigned int * __restrict__ step_no) {
     const int t = blockIdx.y;
+    if (step_no && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *step_no += 1u;   // numbers the exchanges of this step
     int tok = tokens[t];
     tok = tok < 0 ? 0 : (tok >= n_vocab ? n_vocab - 1 : tok);
     for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < d; c += (int64_t)gridDim.x * blockDim.x) {
@@ -122,6 +123,7 @@ struct pi_engine {
     bool pdl;                                // programmatic dependent launch between the kernels of a step
     bool gate_sym;                           // bamboo: relu on the gated product as well
     bool rows1;                              // one token: masks-only compaction + register-streaming sparse kernels (shape eligible)
+    long long wait_cycles;                   // bound of the exchange waits (0: about a second)
     unsigned skip_mask;                      // set only inside pi_engine_time_stage: the stages left out of the captured sequence
 };
 
@@ -237,7 +239,7 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
     memset(&e->xch, 0, sizeof e->xch);
     e->pred_trace = nullptr; e->launches = 0;
     { const char * v = getenv("PI_PDL"); e->pdl = !(v && v[0] == '0'); }
-    e->skip_mask = 0u;
+    e->skip_mask = 0u; e->wait_cycles = 0;
     e->rows1 = rows_eligible(cfg->wtype, e->F, cfg->d) && axpy_rows_groups(e->F, cfg->d) <= e->G;
     cudaStream_t st = (cudaStream_t)stream;
     // one-time device state: sequence ids 0..T-1, zeroed ticket / status, RoPE angle table
@@ -275,6 +277,8 @@ int pi_engine_io(pi_engine * e, int32_t ** tokens, int32_t ** pos, float ** logi
 int pi_engine_set_exchange(pi_engine * e, const pi_exchange * x) {
     PI_REQUIRE(e && x, "engine_set_exchange: null argument");
     PI_REQUIRE(x->n_ranks == e->c.n_ranks && x->rank_id == e->c.rank_id, "engine_set_exchange: rank layout differs from the engine's");
+    PI_REQUIRE(x->flag_words >= e->T_max * XCH_SLICES && x->slot_floats >= (int64_t)e->T_max * e->c.d,
+               "engine_set_exchange: need flag_words >= %d and slot_floats >= %lld", e->T_max * XCH_SLICES, (long long)e->T_max * e->c.d);
     e->xch = *x;
     for (auto & g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
     return PI_OK;
@@ -337,25 +341,24 @@ struct StageTimer {
 struct Pending {
     const float * vec = nullptr;          // single vector [T, d]
     const float * partial = nullptr; int n_groups = 0;   // or: partial vectors [n_groups, T, d] to be added in group order
-    bool mailbox = false;                 // or: the n_ranks slots of the local mailbox
+    bool exchange = false;                // sharded run: the above is this rank's share, to be exchanged by the norm
     const float * bias = nullptr;
     const float * res = nullptr;          // added before the residual stream (falcon's attention branch)
-    bool any() const { return vec || partial || mailbox; }
+    bool any() const { return vec || partial; }
 };
 
-void norm_inputs(pi_engine * e, int T, const Pending & pd, NormArgs & n) {
-    if (pd.mailbox) {
-        n.partial = e->xch.mailbox_local; n.n_groups = e->c.n_ranks; n.partial_stride = e->xch.slot_floats;
-        n.wait_flags = e->xch.flags_local; n.wait_epoch = e->xch.epoch; n.status = e->status;
-    } else if (pd.partial) {
-        n.partial = pd.partial; n.n_groups = pd.n_groups;
-    } else {
-        n.x = pd.vec;
-    }
+// what the norm reads: its own share (a vector or partial vectors), exchanged first when the run is sharded
+void norm_inputs(pi_engine * e, const Pending & pd, NormArgs & n, int * xch_index, int xch_per_step) {
+    if (pd.partial) { n.partial = pd.partial; n.n_groups = pd.n_groups; }
+    else            { n.x = pd.vec; }
     n.in_bias = pd.bias;
-    if (pd.res) { n.residual = pd.res; n.residual2 = e->x; } else { n.residual = e->x; }
+    if (pd.exchange) {
+        n.xch = &e->xch; n.xch_index = (*xch_index)++; n.xch_per_step = xch_per_step; n.xch_extra = pd.res;
+        n.wait_cycles = e->wait_cycles; n.status = e->status;
+        n.residual = e->x;
+    } else if (pd.res) { n.residual = pd.res; n.residual2 = e->x; }
+    else               { n.residual = e->x; }
     n.x_out = e->x;
-    (void)T;
 }
 
 int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
@@ -368,12 +371,14 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
     const int qkv_rows = e->dq + 2 * e->dkv;
     const bool pdl = e->pdl && !tm.on;       // profiling wants each kernel alone between its events
     e->launches = 0;
+    const int xch_per_step = falcon ? c.n_layer : 2 * c.n_layer;      // exchanges of one step (falcon sums its branches locally first)
+    int xch_index = 0;
 
     if (!(e->skip_mask & (1u << PI_STAGE_OTHER))) {
         const dim3 grid((unsigned)((d + 255) / 256), T);
         if (tm.begin()) return PI_ERR_CUDA;
         k_embed<<<grid, 256, 0, st>>>((const __half *)e->g.tok_embd, (const __half *)e->g.pos_embd, e->tokens, e->pos,
-                                      c.n_vocab, c.n_pos, d, e->x);
+                                      c.n_vocab, c.n_pos, d, e->x, multi ? e->xch.epoch : nullptr);
         PI_LAUNCH_CHECK("k_embed");
         if (tm.end(PI_STAGE_OTHER)) return PI_ERR_CUDA;
         e->launches++;
@@ -390,7 +395,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
         n1.T = T; n1.n = d; n1.rms = rms; n1.eps = c.norm_eps;
         n1.w = last ? e->g.out_norm_w : L->attn_norm_w;
         n1.b = last ? e->g.out_norm_b : L->attn_norm_b;
-        if (pend.any()) norm_inputs(e, T, pend, n1); else n1.x = e->x;
+        if (pend.any()) norm_inputs(e, pend, n1, &xch_index, xch_per_step); else n1.x = e->x;
         if (last) {
             const int out_t = e->g.output ? wt : PI_TYPE_F16;            // opt: tied F16 embedding
             n1.act_type = out_t; n1.act = out_t == wt ? e->act_a : e->act_p;
@@ -463,16 +468,11 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
         //      so sharded runs exchange here.  falcon: n1 already produced both inputs.
         if (!falcon) {
             Pending pa;
-            if (multi) {
-                STAGE(PI_STAGE_EXCHANGE, 1, launch_exchange_push(e->xch, e->attn_out, 1, T, d, nullptr, e->status, st, pdl));
-                pa.mailbox = true;
-            } else {
-                pa.vec = e->attn_out;
-            }
+            pa.vec = e->attn_out; pa.exchange = multi;
             NormArgs n2;
             n2.pdl = pdl;
             n2.T = T; n2.n = d; n2.rms = rms; n2.eps = c.norm_eps; n2.w = L->ffn_norm_w; n2.b = L->ffn_norm_b;
-            norm_inputs(e, T, pa, n2);
+            norm_inputs(e, pa, n2, &xch_index, xch_per_step);
             n2.act_type = wt; n2.act = e->act_a;
             n2.act2_type = PI_TYPE_F16; n2.act2 = e->act_p; n2.act2_src = 0;      // the predictor reads ffn_inp itself
             STAGE(PI_STAGE_NORM, 1, launch_norm(n2, st));
@@ -530,17 +530,13 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
         }
         pend = Pending();
         pend.bias = L->down_b;
-        if (multi) {
-            // falcon sums its two branches locally first: one exchange per layer (llama.cpp:5443-5447)
-            STAGE(PI_STAGE_EXCHANGE, 1, launch_exchange_push(e->xch, e->partial, used, T, d, falcon ? e->attn_out : nullptr, e->status, st, pdl && T == 1));
-            pend.mailbox = true;
-        } else if (used <= NORM_MAX_GROUPS) {
+        pend.exchange = multi;
+        pend.res = falcon ? e->attn_out : nullptr;        // falcon sums its two branches locally first: one exchange per layer (llama.cpp:5443-5447)
+        if (used <= NORM_MAX_GROUPS) {
             pend.partial = e->partial; pend.n_groups = used;
-            pend.res = falcon ? e->attn_out : nullptr;
         } else {
             STAGE(PI_STAGE_DOWN, 1, launch_reduce_partials(e->partial, used, T, d, nullptr, nullptr, e->ffn_vec, st, pdl));
             pend.vec = e->ffn_vec;
-            pend.res = falcon ? e->attn_out : nullptr;
         }
     }
     return PI_OK;
@@ -550,6 +546,7 @@ int check_T(pi_engine * e, int T) {
     PI_REQUIRE(e, "engine: null");
     PI_REQUIRE(T >= 1 && T <= e->T_max, "engine: T=%d outside 1..%d", T, e->T_max);
     PI_REQUIRE(e->c.n_ranks == 1 || e->xch.mailbox_local, "engine: sharded engine has no exchange configured");
+    PI_REQUIRE(e->c.n_ranks == 1 || (e->c.d % 256 == 0), "engine: sharded runs need d_model to be a multiple of 256");
     return PI_OK;
 }
 
@@ -689,9 +686,17 @@ int pi_engine_status(pi_engine * e, void * stream) {
     PI_REQUIRE(e, "engine_status: null");
     unsigned int s = 0;
     PI_CUDA(cudaMemcpyAsync(&s, e->status, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    if (s) PI_CUDA(cudaMemsetAsync(e->status, 0, 4, (cudaStream_t)stream));      // reported once
     PI_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (s & 1u) { set_error("an exchange wait ran out: a peer rank did not deliver its partial vector"); return PI_ERR_TIMEOUT; }
     if (s & 14u) { set_error("a bulk-copy wait ran out in a weight-streaming kernel (status %u)", s); return PI_ERR_TIMEOUT; }
+    return PI_OK;
+}
+
+int pi_engine_set_wait_cycles(pi_engine * e, long long cycles) {
+    PI_REQUIRE(e && cycles >= 0, "engine_set_wait_cycles: bad arguments");
+    e->wait_cycles = cycles;
+    for (auto & g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }     // the bound is a kernel argument
     return PI_OK;
 }
 
@@ -704,7 +709,19 @@ int pi_engine_set_trace(pi_engine * e, float * pred_trace) {
 
 int pi_engine_debug(pi_engine * e, float ** pred, int32_t ** list, int32_t ** count) {
     PI_REQUIRE(e, "engine_debug: null");
-    if (pred) *pred = e->pred_trace ? e->pred_trace + (size_t)(e->c.n_layer - 1) * e->c.max_batch * e->F : e->pred;
+    float * p = e->pred_trace ? e->pred_trace + (size_t)(e->c.n_layer - 1) * e->c.max_batch * e->F : e->pred;
+    if (e->rows1 && (list || count)) {
+        // one-token steps make bit masks only: build the list of the last layer's logits (first sequence) here, on the
+        // default stream, after everything queued so far
+        PI_CUDA(cudaDeviceSynchronize());
+        CompactArgs ca;
+        ca.idx = p; ca.idx_stride = e->F; ca.T = 1; ca.threshold = e->c.threshold; ca.n_local = e->F;
+        ca.list = e->list; ca.count = e->count; ca.masks = e->masks; ca.ticket = e->ticket;
+        const int rc = launch_compact(ca, nullptr);
+        if (rc) return rc;
+        PI_CUDA(cudaDeviceSynchronize());
+    }
+    if (pred) *pred = p;
     if (list) *list = e->list;
     if (count) *count = e->count;
     return PI_OK;

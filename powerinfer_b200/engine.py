@@ -44,7 +44,7 @@ class Exchange(C.Structure):
     _fields_ = [("n_ranks", C.c_int), ("rank_id", C.c_int), ("slot_floats", C.c_int64),
                 ("mailbox_local", _vp), ("flags_local", _vp),
                 ("mailbox_peer", _vp * PI_MAX_RANKS), ("flags_peer", _vp * PI_MAX_RANKS),
-                ("epoch", _vp), ("ticket", _vp)]
+                ("epoch", _vp), ("ticket", _vp), ("flag_words", C.c_int)]
 
 
 for _name, _res, _args in [
@@ -60,6 +60,7 @@ for _name, _res, _args in [
     ("pi_engine_decode_host", C.c_int, [_vp, _vp, _vp, C.c_int, _vp, _vp, _vp]),
     ("pi_engine_profile_step", C.c_int, [_vp, C.c_int, _vp, C.POINTER(C.c_int), _vp]),
     ("pi_engine_status", C.c_int, [_vp, _vp]),
+    ("pi_engine_set_wait_cycles", C.c_int, [_vp, C.c_longlong]),
     ("pi_engine_debug", C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp)]),
     ("pi_engine_launches", C.c_int, [_vp]),
     ("pi_engine_set_trace", C.c_int, [_vp, _vp]),
@@ -76,7 +77,7 @@ for _name, _res, _args in [
 
 ENGINE_EXPORTS = ["pi_engine_workspace_bytes", "pi_engine_kv_bytes", "pi_engine_create", "pi_engine_destroy",
                   "pi_engine_set_exchange", "pi_engine_io", "pi_engine_decode", "pi_engine_advance", "pi_engine_decode_host",
-                  "pi_engine_profile_step", "pi_engine_time_stage", "pi_engine_status", "pi_engine_debug", "pi_engine_launches", "pi_engine_set_trace", "pi_engine_active_total",
+                  "pi_engine_profile_step", "pi_engine_time_stage", "pi_engine_status", "pi_engine_set_wait_cycles", "pi_engine_debug", "pi_engine_launches", "pi_engine_set_trace", "pi_engine_active_total",
                   "pi_device_malloc", "pi_device_free", "pi_ipc_export", "pi_ipc_import", "pi_ipc_close"]
 
 
@@ -263,7 +264,8 @@ class DecodeEngine:
         assert self.n_ranks > 1
         slot = self.max_batch * self.spec.d
         mbox_bytes = 2 * self.n_ranks * slot * 4
-        flag_bytes = 256
+        flag_words = 8 * self.max_batch
+        flag_bytes = (2 * self.n_ranks * flag_words * 4 + 255) // 256 * 256
         total = mbox_bytes + 2 * flag_bytes
         base = _vp()
         check(lib.pi_device_malloc(C.byref(base), total))
@@ -273,7 +275,7 @@ class DecodeEngine:
         allh = [torch.empty_like(mine) for _ in range(self.n_ranks)]
         dist.all_gather(allh, mine, group=group)
         x = Exchange()
-        x.n_ranks, x.rank_id, x.slot_floats = self.n_ranks, self.rank, slot
+        x.n_ranks, x.rank_id, x.slot_floats, x.flag_words = self.n_ranks, self.rank, slot, flag_words
         self._peer_ptrs = []
         for r in range(self.n_ranks):
             if r == self.rank:
@@ -295,6 +297,45 @@ class DecodeEngine:
         check(lib.pi_engine_set_exchange(self.handle, C.byref(x)))
         dist.barrier(group=group)
 
+    def setup_exchange_loopback(self):
+        """A sharded engine alone on one GPU (tests of the bounded waits): this rank's pushes to the other ranks land in a
+        spare buffer nobody reads, and the other ranks' flags in this rank's mailbox are raised by nobody, so every
+        exchange wait runs out, unless `raise_peer_flags` is called."""
+        assert self.n_ranks > 1
+        slot = self.max_batch * self.spec.d
+        mbox_bytes = 2 * self.n_ranks * slot * 4
+        flag_words = 8 * self.max_batch
+        flag_bytes = (2 * self.n_ranks * flag_words * 4 + 255) // 256 * 256
+        total = mbox_bytes + 2 * flag_bytes
+        base, spare = _vp(), _vp()
+        check(lib.pi_device_malloc(C.byref(base), total))
+        check(lib.pi_device_malloc(C.byref(spare), total))
+        x = Exchange()
+        x.n_ranks, x.rank_id, x.slot_floats, x.flag_words = self.n_ranks, self.rank, slot, flag_words
+        for r in range(self.n_ranks):
+            p = base.value if r == self.rank else spare.value
+            x.mailbox_peer[r] = p
+            x.flags_peer[r] = p + mbox_bytes
+        x.mailbox_local = base.value
+        x.flags_local = base.value + mbox_bytes
+        x.epoch = base.value + mbox_bytes + flag_bytes
+        x.ticket = base.value + mbox_bytes + flag_bytes + 64
+        self._xch_mem, self._xch_spare, self._peer_ptrs = base, spare, []
+        self._flags_view = _wrap_device(base.value + mbox_bytes, 2 * self.n_ranks * flag_words, torch.int32)
+        self.xch = x
+        check(lib.pi_engine_set_exchange(self.handle, C.byref(x)))
+
+    def raise_peer_flags(self):
+        """Loopback only: mark every other rank's flags as delivered for all future exchanges (their slots hold zeros)."""
+        fl = self._flags_view.view(2, self.n_ranks, -1)
+        for r in range(self.n_ranks):
+            if r != self.rank:
+                fl[:, r, :] = 0x3fffffff
+        torch.cuda.synchronize()
+
+    def set_wait_cycles(self, cycles: int):
+        check(lib.pi_engine_set_wait_cycles(self.handle, cycles))
+
     def close(self):
         if getattr(self, "handle", None) and self.handle.value:
             torch.cuda.synchronize()
@@ -305,6 +346,9 @@ class DecodeEngine:
             if self._xch_mem is not None:
                 lib.pi_device_free(self._xch_mem)
                 self._xch_mem = None
+            if getattr(self, "_xch_spare", None) is not None:
+                lib.pi_device_free(self._xch_spare)
+                self._xch_spare = None
 
     def __del__(self):
         try:

@@ -360,9 +360,9 @@ void op_mul_mat(ggml_tensor * dst) {
         const int64_t nrows = a->ne[1], ncols = a->ne[0], T = b->ne[1];
         for (int64_t t0 = 0; t0 < T; t0 += TOKENS_PER_CALL) {
             const int tt = (int)(T - t0 < TOKENS_PER_CALL ? T - t0 : TOKENS_PER_CALL);
-            const size_t need = pi_workspace_bytes(ncols, nrows, tt);
+            void * ws = workspace(pi_workspace_bytes(ncols, nrows, tt));
             PI(pi_mul_mat(pi_type(a->type), dev_of(a)->data, nrows, ncols, (const float *)pb + t0 * ncols, tt, nullptr,
-                          (float *)r.dev + t0 * nrows, workspace(need), g_ws_bytes, g_stream));
+                          (float *)r.dev + t0 * nrows, ws, g_ws_bytes, g_stream));
         }
         finish(r);
         return;
@@ -394,16 +394,16 @@ void op_sparse(ggml_tensor * dst, bool axpy) {
         const int tt = (int)(T - t0 < TOKENS_PER_CALL ? T - t0 : TOKENS_PER_CALL);
         if (!axpy) {
             const int64_t n_dst = dst->ne[0];
-            const size_t need = pi_workspace_bytes(ncols, n_dst > n_w_rows ? n_dst : n_w_rows, tt);
+            void * ws = workspace(pi_workspace_bytes(ncols, n_dst > n_w_rows ? n_dst : n_w_rows, tt));
             PI(pi_mul_mat_idx(pi_type(w->type), dev_of(w)->data, n_w_rows, ncols, (const float *)px + t0 * ncols, tt,
                               (const float *)pidx + t0 * idx_stride, idx_stride, pbucket, g_threshold,
-                              (float *)r.dev + t0 * n_dst, n_dst, workspace(need), g_ws_bytes, g_stream));
+                              (float *)r.dev + t0 * n_dst, n_dst, ws, g_ws_bytes, g_stream));
         } else {
             const int64_t h_stride = x->ne[0];
-            const size_t need = pi_workspace_bytes(ncols, h_stride > n_w_rows ? h_stride : n_w_rows, tt);
+            void * ws = workspace(pi_workspace_bytes(ncols, h_stride > n_w_rows ? h_stride : n_w_rows, tt));
             PI(pi_axpy(pi_type(w->type), dev_of(w)->data, n_w_rows, ncols, (const float *)px + t0 * h_stride, tt, h_stride,
                        (const float *)pidx + t0 * idx_stride, idx_stride, pbucket, g_threshold,
-                       (float *)r.dev + t0 * ncols, workspace(need), g_ws_bytes, g_stream));
+                       (float *)r.dev + t0 * ncols, ws, g_ws_bytes, g_stream));
         }
     }
     finish(r);

@@ -25,7 +25,7 @@ sys.path.insert(0, ROOT)
 
 from powerinfer_b200 import synth  # noqa: E402
 
-N_PROMPT, N_STEPS = 8, 25
+N_PROMPT, N_STEPS = 8, 32
 
 MODEL_CASES = {
     "llama_f16": synth.ModelSpec(arch=synth.ARCH_LLAMA, wtype=synth.F16, seed=11),
@@ -37,6 +37,22 @@ MODEL_CASES = {
     "opt_f16": synth.ModelSpec(arch=synth.ARCH_OPT, wtype=synth.F16, seed=15, norm_eps=0.0),
     "bamboo_f16": synth.ModelSpec(arch=synth.ARCH_LLAMA, wtype=synth.F16, gate_sym=True, seed=16),
 }
+
+
+# Two-layer models at the PER-LAYER SHAPES of the benchmarked configurations (vocabulary cut to 1024 rows to keep the
+# fixtures small): the kernels choose tile, slice and ring geometry from the layer shape, so parity on toy shapes does not
+# cover them.  `python make_golden.py shapes` regenerates these (minutes of CPU time and ~10 GB of memory each).
+SHAPE_CASES = {
+    "shape_7b_f16": synth.ModelSpec(arch=synth.ARCH_LLAMA, wtype=synth.F16, d=4096, n_ff=11008, n_head=32, n_head_kv=32,
+                                    rank=1024, n_vocab=1024, firing=0.10, seed=21),
+    "shape_falcon40b_f16": synth.ModelSpec(arch=synth.ARCH_FALCON, wtype=synth.F16, d=8192, n_ff=32768, n_head=128, n_head_kv=8,
+                                           rank=1024, n_vocab=1024, firing=0.10, seed=22),
+    "shape_70b_q4_0": synth.ModelSpec(arch=synth.ARCH_LLAMA, wtype=synth.Q4_0, d=8192, n_ff=28672, n_head=64, n_head_kv=8,
+                                      rank=1024, n_vocab=1024, firing=0.12, seed=23),
+    "shape_opt175b_f16": synth.ModelSpec(arch=synth.ARCH_OPT, wtype=synth.F16, d=12288, n_ff=49152, n_head=96, n_head_kv=96,
+                                         rank=1536, n_vocab=1024, firing=0.08, norm_eps=0.0, seed=24),
+}
+ALL_CASES = {**MODEL_CASES, **SHAPE_CASES}
 
 
 def prompt_for(spec):
@@ -168,10 +184,12 @@ def write_op_fixtures(ref):
 
 def main():
     from oracle import pio
-    only = set(sys.argv[1:])          # model cases to (re)generate; none named: everything, the op fixtures included
+    only = set(sys.argv[1:])          # cases to (re)generate; none named: the op fixtures and the small models;
+    if "shapes" in only:              # `shapes`: the configuration-shaped models
+        only = (only - {"shapes"}) | set(SHAPE_CASES)
     if not only:
         write_op_fixtures(pio.Ref())
-    for name, spec in MODEL_CASES.items():
+    for name, spec in (ALL_CASES if only else MODEL_CASES).items():
         if only and name not in only:
             continue
         tensors = synth.build_model(spec)
