@@ -424,10 +424,13 @@ def main():
         eng.decode_host_raw(T)
         eng.h_tokens[:T] = eng.h_argmax[:T]; eng.h_pos[:T] += 1
     barrier()
+    greedy_ids = []                                   # sequence 0's greedy continuation: the same at every GPU count
     t0 = time.perf_counter()
     for _ in range(K):
         eng.decode_host_raw(T)                        # H2D ids+positions, graph, D2H logits + greedy id, synchronize
         eng.h_tokens[:T] = eng.h_argmax[:T]; eng.h_pos[:T] += 1
+        if len(greedy_ids) < 32:
+            greedy_ids.append(int(eng.h_argmax[0]))
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
 
@@ -449,10 +452,26 @@ def main():
     active = eng.active_total() / (n_prof * spec.n_layer) * world     # mean active neurons per layer (all ranks)
     # ---- per-kernel durations: each stage's kernels for all layers, back to back (overlapped as inside the step)
     b2b = {}
-    for st in ("qkv", "out_proj", "predictor", "up_gate", "down", "lm_head"):
-        ms_launch, n_launch = eng.time_stage(T, st)
+    for st in ("qkv", "out_proj", "predictor", "up_gate", "down", "lm_head", "norm", "attention", "compact"):
+        ms_launch, n_launch = eng.time_stage(T, st)     # the norms of a sharded run carry the exchange (all ranks replay them together)
         if n_launch > 0:
             b2b[st] = (ms_launch * 1e3, n_launch)
+    # the stated baseline for the exchange: an NCCL all-reduce of one partial vector (T x d floats), timed alone
+    nccl_us = None
+    if world > 1:
+        buf = torch.zeros(T * spec.d, dtype=torch.float32, device="cuda")
+        for _ in range(10):
+            dist.all_reduce(buf)
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(100):
+            dist.all_reduce(buf)
+        a1.record()
+        torch.cuda.synchronize()
+        tt = torch.tensor([a0.elapsed_time(a1) * 10.0], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        nccl_us = float(tt[0])
 
     if rank == 0:
         from powerinfer_b200 import configs as C2
@@ -489,7 +508,13 @@ def main():
                 "step_hbm": {"algorithmic_GB_per_step_per_gpu": round(step_bytes / 1e9, 3),
                              "GBps": round(step_bytes / (ms / K * 1e-3) / 1e9, 1),
                              "frac_of_measured_peak": round(step_bytes / (ms / K * 1e-3) / 1e9 / peak, 3)},
-                "ops": ops, "stage_ms_profiled": {k: round(v, 4) for k, v in stage_ms.items()},
+                "ops": ops, "latency_stages": {st: {"ms_per_step": round(b2b[st][0] * b2b[st][1] * 1e-3, 4), "launches_per_step": b2b[st][1],
+                                                    "us_per_launch": round(b2b[st][0], 2)} for st in ("norm", "attention", "compact") if st in b2b},
+                "exchange": ({"kernel": "inside the norm that consumes the sum (k_norm_cluster): peer stores, per-slice flags, bounded wait",
+                              "per_step": spec.n_layer * (1 if spec.arch == 1 else 2), "bytes_per_exchange_per_peer": T * spec.d * 4,
+                              "nccl_all_reduce_same_bytes_us": round(nccl_us, 2)} if world > 1 else None),
+                "greedy_ids": greedy_ids,
+                "stage_ms_profiled": {k: round(v, 4) for k, v in stage_ms.items()},
                 "mean_active_neurons_per_layer": round(active, 1), "env_overrides": pi_env()}
         if world == 1 and not args.no_cpu_baseline:
             try:

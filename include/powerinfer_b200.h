@@ -257,6 +257,16 @@ int  pi_engine_advance(pi_engine * e, int T, void * stream);
 int  pi_engine_decode_host(pi_engine * e, const int32_t * host_tokens, const int32_t * host_pos, int T,
                            float * host_logits, int32_t * host_argmax, void * stream);
 
+/* Prompt processing (llama_decode with a batch of n_tokens > 1 tokens of one sequence: llama.cpp:6764-7006; the reference's
+ * batched sparse kernels are ggml-cuda.cu:4607-4682, 4758-4824): n_tokens consecutive tokens of sequence `seq`, the first
+ * at position pos0, go through the engine in chunks of up to max_batch tokens per step.  A chunk's step stores the K / V of
+ * all its tokens first and then attends causally, reads every weight row once for the whole chunk, and applies each
+ * token's own predictor mask (union list for reading, per-token predicate for writing: ggml.c:14250-14259).  Only the last
+ * token's logits are computed and copied back (host_logits_last F32 [n_vocab], host_argmax_last int32 [1]; both may be
+ * NULL: then no lm head runs at all).  Synchronises `stream`. */
+int  pi_engine_prefill_host(pi_engine * e, const int32_t * host_tokens, int n_tokens, int seq, int pos0,
+                            float * host_logits_last, int32_t * host_argmax_last, void * stream);
+
 /* Same step launched kernel by kernel with CUDA events around each stage; adds the milliseconds of each stage to
  * host_ms[PI_N_STAGES] and the number of kernel launches to *host_launches.  Synchronises. */
 #define PI_STAGE_NORM      0

@@ -200,6 +200,10 @@ struct AttnArgs {
     const float * cs = nullptr; int neox = 0;          // fused RoPE of q and k from the angle table (nullptr: already rotated)
     float * out = nullptr;                             // optional F32 [T, n_head*head_dim]
     int out_act_type = 0; ActBuf out_act;              // optional activation planes of the output
+    // 0: store the new K / V and attend in one launch (tokens of DIFFERENT sequences); 1: store only; 2: attend only.
+    // Several tokens of one sequence in a step (prompt chunks) take a store pass, then an attend pass: a token must see
+    // the rows of the tokens before it, which other CTAs write.
+    int store_mode = 0;
     bool pdl = false;
 };
 int launch_attention(const AttnArgs & a, cudaStream_t st);

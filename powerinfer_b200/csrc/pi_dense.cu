@@ -509,7 +509,7 @@ struct AttnP {
     const float * q; const float * k; const float * v; __half * k_cache; __half * v_cache;
     const int32_t * seq; const int32_t * pos; int n_head, n_head_kv, hd, n_ctx;
     const float * cs; int neox; int sc_floats; int64_t q_stride, kv_stride;
-    float * out; ActBuf out_act; int out_act_type;
+    float * out; ActBuf out_act; int out_act_type; int store_mode;
 };
 
 __device__ __forceinline__ float dot8(const uint4 kv, const float * __restrict__ q) {
@@ -540,7 +540,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     const int slices = ATTN_THREADS / chunks;
     const int c8 = tid % chunks, sl = tid / chunks;
     // L2 prefetch hints cost no registers, so this CTA still fits beside the mat-vec CTAs it overlaps with
-    for (int j = tid; j < pos; j += ATTN_THREADS) {
+    for (int j = tid; j < pos && p.store_mode == 0; j += ATTN_THREADS) {
         const char * kr = reinterpret_cast<const char *>(kc + (size_t)j * dkv);
         const char * vr = reinterpret_cast<const char *>(vc + (size_t)j * dkv);
         for (int o = 0; o < hd * 2; o += 128) {
@@ -576,12 +576,13 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
         for (int e = tid; e < hd; e += ATTN_THREADS) { q32[e] = round_f16(qh[e]); k16[e] = __float2half_rn(kh[e]); }
     }
     __syncthreads();
-    if (h % group == 0) {
+    if (h % group == 0 && p.store_mode != 2) {
         for (int e = tid; e < hd; e += ATTN_THREADS) {
             kc[(size_t)pos * dkv + e] = k16[e];
             vc[(size_t)pos * dkv + e] = v16[e];
         }
     }
+    if (p.store_mode == 1) return;                              // store pass of a prompt chunk
 
     PI_TL_MARK(0);
     // ---- scores.  head_dim/8 a power of two <= 32 (head_dim 32, 64, 128, 256): a group of head_dim/8 lanes reads one
@@ -734,7 +735,7 @@ int launch_attention(const AttnArgs & a, cudaStream_t st) {
     p.n_head = a.n_head; p.n_head_kv = a.n_head_kv; p.hd = a.head_dim; p.n_ctx = a.n_ctx;
     p.q_stride = a.q_stride ? a.q_stride : (int64_t)a.n_head * a.head_dim;
     p.kv_stride = a.kv_stride ? a.kv_stride : (int64_t)a.n_head_kv * a.head_dim;
-    p.cs = a.cs; p.neox = a.neox; p.out = a.out; p.out_act = a.out_act; p.out_act_type = a.out_act_type;
+    p.cs = a.cs; p.neox = a.neox; p.out = a.out; p.out_act = a.out_act; p.out_act_type = a.out_act_type; p.store_mode = a.store_mode;
     // sc must hold max(n_ctx, slices*hd) floats
     const int slices = ATTN_THREADS / (a.head_dim / 8);
     const size_t sc_floats = (size_t)((max(a.n_ctx, slices * a.head_dim) + 3) / 4 * 4);

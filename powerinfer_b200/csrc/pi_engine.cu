@@ -106,7 +106,7 @@ struct pi_engine {
     int hd, dq, dkv, F, T_max;
     int G;                                   // axpy row groups
     // device buffers carved from the caller's workspace
-    int32_t * tokens, * pos, * seq_ids, * argmax;
+    int32_t * tokens, * pos, * seq_ids, * seq_pf, * argmax;   // seq_pf: the sequence of every token of a prompt chunk
     float * x, * x2, * attn_out, * ffn_vec, * qkv, * pred, * h, * partial, * logits, * cs;
     int32_t * list, * count; unsigned int * ticket; uint32_t * masks;
     int8_t * cq; float * cd;
@@ -116,8 +116,8 @@ struct pi_engine {
     unsigned int * status;                   // device word: bit 0 = an exchange wait ran out
     unsigned long long * active_total;       // device counter: sum of active-list lengths over layers and steps
     pi_exchange xch;
-    cudaGraphExec_t graphs[PI_MAX_BATCH + 1];
-    bool warmed[PI_MAX_BATCH + 1];
+    cudaGraphExec_t graphs[3][PI_MAX_BATCH + 1];   // [0] decode, [1] prompt chunk, [2] prompt chunk without the lm head
+    bool warmed[3][PI_MAX_BATCH + 1];
     int launches;                            // kernels enqueued by the last enqueue_step
     float * pred_trace;                      // optional [n_layer, max_batch, F]: keeps every layer's predictor logits
     bool pdl;                                // programmatic dependent launch between the kernels of a step
@@ -153,7 +153,7 @@ static void carve(pi_engine * e, void * ws, size_t ws_bytes, bool dry, size_t * 
     Carver cv{(char *)ws, dry ? (char *)ws + (size_t(1) << 60) : (char *)ws + ws_bytes};
     const int T = e->T_max;
     const size_t d = c.d, F = e->F;
-    e->tokens = cv.take<int32_t>(T); e->pos = cv.take<int32_t>(T); e->seq_ids = cv.take<int32_t>(T); e->argmax = cv.take<int32_t>(T);
+    e->tokens = cv.take<int32_t>(T); e->pos = cv.take<int32_t>(T); e->seq_ids = cv.take<int32_t>(T); e->seq_pf = cv.take<int32_t>(T); e->argmax = cv.take<int32_t>(T);
     e->status = cv.take<unsigned int>(1); e->active_total = cv.take<unsigned long long>(1);
     e->x = cv.take<float>(T * d); e->x2 = cv.take<float>(T * d); e->attn_out = cv.take<float>(T * d); e->ffn_vec = cv.take<float>(T * d);
     e->qkv = cv.take<float>((size_t)T * (e->dq + 2 * e->dkv));
@@ -261,7 +261,7 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
 
 void pi_engine_destroy(pi_engine * e) {
     if (!e) return;
-    for (auto & g : e->graphs) if (g) cudaGraphExecDestroy(g);
+    for (auto & gm : e->graphs) for (auto & g : gm) if (g) cudaGraphExecDestroy(g);
     delete e;
 }
 
@@ -280,7 +280,7 @@ int pi_engine_set_exchange(pi_engine * e, const pi_exchange * x) {
     PI_REQUIRE(x->flag_words >= e->T_max * XCH_SLICES && x->slot_floats >= (int64_t)e->T_max * e->c.d,
                "engine_set_exchange: need flag_words >= %d and slot_floats >= %lld", e->T_max * XCH_SLICES, (long long)e->T_max * e->c.d);
     e->xch = *x;
-    for (auto & g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
+    for (auto & gm : e->graphs) for (auto & g : gm) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
     return PI_OK;
 }
 
@@ -361,7 +361,9 @@ void norm_inputs(pi_engine * e, const Pending & pd, NormArgs & n, int * xch_inde
     n.x_out = e->x;
 }
 
-int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
+// mode 0: T sequences, one new token each; 1: T consecutive tokens of one sequence (a prompt chunk); 2: the same without
+// the final norm / lm head (chunks whose logits nobody reads)
+int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm, int mode = 0) {
     const pi_engine_config & c = e->c;
     const int64_t d = c.d, F = e->F;
     const int wt = c.wtype;
@@ -396,6 +398,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
         n1.w = last ? e->g.out_norm_w : L->attn_norm_w;
         n1.b = last ? e->g.out_norm_b : L->attn_norm_b;
         if (pend.any()) norm_inputs(e, pend, n1, &xch_index, xch_per_step); else n1.x = e->x;
+        if (last && mode == 2) break;
         if (last) {
             const int out_t = e->g.output ? wt : PI_TYPE_F16;            // opt: tied F16 embedding
             n1.act_type = out_t; n1.act = out_t == wt ? e->act_a : e->act_p;
@@ -449,10 +452,15 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm) {
             a.q_stride = qkv_rows; a.kv_stride = qkv_rows;
             const size_t layer_off = (size_t)il * c.max_batch * c.n_ctx * e->dkv;
             a.k_cache = e->k_cache + layer_off; a.v_cache = e->v_cache + layer_off;
-            a.seq = e->seq_ids; a.pos = e->pos; a.T = T;
+            a.seq = mode ? e->seq_pf : e->seq_ids; a.pos = e->pos; a.T = T;
             a.n_head = c.n_head / c.n_ranks; a.n_head_kv = c.n_head_kv / c.n_ranks; a.head_dim = e->hd; a.n_ctx = c.n_ctx;
             if (c.arch != PI_ARCH_OPT) { a.cs = e->cs; a.neox = falcon; }
             a.out_act_type = wt; a.out_act = e->act_o;
+            if (mode) {                                                   // prompt chunk: every token's K / V first, then attention
+                a.store_mode = 1;
+                STAGE(PI_STAGE_ATTN, 1, launch_attention(a, st));
+                a.store_mode = 2;
+            }
             STAGE(PI_STAGE_ATTN, 1, launch_attention(a, st));
         }
         {
@@ -566,16 +574,16 @@ int count_kernel_nodes(cudaGraph_t graph) {
 }
 
 // first call for a batch size: one plain run (fills every per-kernel attribute cache), then capture
-int run_step(pi_engine * e, int T, cudaStream_t st) {
+int run_step(pi_engine * e, int T, cudaStream_t st, int mode = 0) {
     StageTimer tm;
-    if (e->graphs[T]) { PI_CUDA(cudaGraphLaunch(e->graphs[T], st)); return PI_OK; }
-    if (!e->warmed[T]) {
-        e->warmed[T] = true;
-        return enqueue_step(e, T, st, tm);
+    if (e->graphs[mode][T]) { PI_CUDA(cudaGraphLaunch(e->graphs[mode][T], st)); return PI_OK; }
+    if (!e->warmed[mode][T]) {
+        e->warmed[mode][T] = true;
+        return enqueue_step(e, T, st, tm, mode);
     }
     cudaGraph_t graph = nullptr;
     PI_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-    const int rc = enqueue_step(e, T, st, tm);
+    const int rc = enqueue_step(e, T, st, tm, mode);
     const cudaError_t ce = cudaStreamEndCapture(st, &graph);
     if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
     if (ce != cudaSuccess) return cuda_fail(ce, "cudaStreamEndCapture");
@@ -584,7 +592,7 @@ int run_step(pi_engine * e, int T, cudaStream_t st) {
     const cudaError_t ci = cudaGraphInstantiate(&exec, graph, 0);
     cudaGraphDestroy(graph);
     if (ci != cudaSuccess) return cuda_fail(ci, "cudaGraphInstantiate");
-    e->graphs[T] = exec;
+    e->graphs[mode][T] = exec;
     PI_CUDA(cudaGraphLaunch(exec, st));
     return PI_OK;
 }
@@ -620,6 +628,34 @@ int pi_engine_decode_host(pi_engine * e, const int32_t * host_tokens, const int3
     if ((rc = run_step(e, T, st))) return rc;
     if (host_logits) PI_CUDA(cudaMemcpyAsync(host_logits, e->logits, (size_t)T * e->c.n_vocab * 4, cudaMemcpyDeviceToHost, st));
     if (host_argmax) PI_CUDA(cudaMemcpyAsync(host_argmax, e->argmax, (size_t)T * 4, cudaMemcpyDeviceToHost, st));
+    PI_CUDA(cudaStreamSynchronize(st));
+    return PI_OK;
+}
+
+int pi_engine_prefill_host(pi_engine * e, const int32_t * host_tokens, int n_tokens, int seq, int pos0,
+                           float * host_logits_last, int32_t * host_argmax_last, void * stream) {
+    PI_REQUIRE(e && host_tokens && n_tokens >= 1, "engine_prefill_host: bad arguments");
+    PI_REQUIRE(seq >= 0 && seq < e->T_max, "engine_prefill_host: sequence %d outside 0..%d", seq, e->T_max - 1);
+    PI_REQUIRE(pos0 >= 0 && (int64_t)pos0 + n_tokens <= e->c.n_ctx, "engine_prefill_host: positions %d..%d outside the context of %d", pos0, pos0 + n_tokens - 1, e->c.n_ctx);
+    int rc = check_T(e, 1);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    std::vector<int32_t> ids(e->T_max, seq), pos(e->T_max);
+    PI_CUDA(cudaMemcpyAsync(e->seq_pf, ids.data(), (size_t)e->T_max * 4, cudaMemcpyHostToDevice, st));
+    int last_T = 0;
+    for (int t0 = 0; t0 < n_tokens; t0 += e->T_max) {
+        const int T = n_tokens - t0 < e->T_max ? n_tokens - t0 : e->T_max;
+        const bool final_chunk = t0 + T == n_tokens;
+        for (int t = 0; t < T; t++) pos[t] = pos0 + t0 + t;
+        PI_CUDA(cudaMemcpyAsync(e->tokens, host_tokens + t0, (size_t)T * 4, cudaMemcpyHostToDevice, st));
+        PI_CUDA(cudaMemcpyAsync(e->pos, pos.data(), (size_t)T * 4, cudaMemcpyHostToDevice, st));
+        PI_CUDA(cudaStreamSynchronize(st));                               // `pos` is rewritten for the next chunk
+        const bool head = final_chunk && (host_logits_last || host_argmax_last);
+        if ((rc = run_step(e, T, st, head ? 1 : 2))) return rc;
+        last_T = T;
+    }
+    if (host_logits_last) PI_CUDA(cudaMemcpyAsync(host_logits_last, e->logits + (size_t)(last_T - 1) * e->c.n_vocab, (size_t)e->c.n_vocab * 4, cudaMemcpyDeviceToHost, st));
+    if (host_argmax_last) PI_CUDA(cudaMemcpyAsync(host_argmax_last, e->argmax + (last_T - 1), 4, cudaMemcpyDeviceToHost, st));
     PI_CUDA(cudaStreamSynchronize(st));
     return PI_OK;
 }
@@ -696,14 +732,14 @@ int pi_engine_status(pi_engine * e, void * stream) {
 int pi_engine_set_wait_cycles(pi_engine * e, long long cycles) {
     PI_REQUIRE(e && cycles >= 0, "engine_set_wait_cycles: bad arguments");
     e->wait_cycles = cycles;
-    for (auto & g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }     // the bound is a kernel argument
+    for (auto & gm : e->graphs) for (auto & g : gm) if (g) { cudaGraphExecDestroy(g); g = nullptr; }     // the bound is a kernel argument
     return PI_OK;
 }
 
 int pi_engine_set_trace(pi_engine * e, float * pred_trace) {
     PI_REQUIRE(e, "engine_set_trace: null");
     e->pred_trace = pred_trace;
-    for (auto & g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }     // captured pointers are stale
+    for (auto & gm : e->graphs) for (auto & g : gm) if (g) { cudaGraphExecDestroy(g); g = nullptr; }     // captured pointers are stale
     return PI_OK;
 }
 

@@ -58,6 +58,7 @@ for _name, _res, _args in [
     ("pi_engine_decode", C.c_int, [_vp, C.c_int, _vp]),
     ("pi_engine_advance", C.c_int, [_vp, C.c_int, _vp]),
     ("pi_engine_decode_host", C.c_int, [_vp, _vp, _vp, C.c_int, _vp, _vp, _vp]),
+    ("pi_engine_prefill_host", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),
     ("pi_engine_profile_step", C.c_int, [_vp, C.c_int, _vp, C.POINTER(C.c_int), _vp]),
     ("pi_engine_status", C.c_int, [_vp, _vp]),
     ("pi_engine_set_wait_cycles", C.c_int, [_vp, C.c_longlong]),
@@ -76,7 +77,7 @@ for _name, _res, _args in [
     _fn.restype, _fn.argtypes = _res, _args
 
 ENGINE_EXPORTS = ["pi_engine_workspace_bytes", "pi_engine_kv_bytes", "pi_engine_create", "pi_engine_destroy",
-                  "pi_engine_set_exchange", "pi_engine_io", "pi_engine_decode", "pi_engine_advance", "pi_engine_decode_host",
+                  "pi_engine_set_exchange", "pi_engine_io", "pi_engine_decode", "pi_engine_advance", "pi_engine_decode_host", "pi_engine_prefill_host",
                   "pi_engine_profile_step", "pi_engine_time_stage", "pi_engine_status", "pi_engine_set_wait_cycles", "pi_engine_debug", "pi_engine_launches", "pi_engine_set_trace", "pi_engine_active_total",
                   "pi_device_malloc", "pi_device_free", "pi_ipc_export", "pi_ipc_import", "pi_ipc_close"]
 
@@ -185,6 +186,16 @@ class DecodeEngine:
         check(lib.pi_engine_decode_host(self.handle, self.h_tokens.data_ptr(), self.h_pos.data_ptr(), T,
                                         self.h_logits.data_ptr() if want_logits else None, self.h_argmax.data_ptr(), self.st))
         return (self.h_logits[:T].numpy() if want_logits else None), self.h_argmax[:T].numpy()
+
+    def prefill(self, tokens, seq: int = 0, pos0: int = 0, want_logits: bool = True):
+        """Prompt processing: `tokens` are consecutive tokens of sequence `seq` starting at position pos0; they go through
+        in chunks of up to max_batch tokens per step.  Returns (logits of the last token | None, its greedy id | None)."""
+        toks = np.ascontiguousarray(np.asarray(tokens, np.int32))
+        logits = np.empty(self.spec.n_vocab, np.float32) if want_logits else None
+        amax = np.zeros(1, np.int32)
+        check(lib.pi_engine_prefill_host(self.handle, toks.ctypes.data, len(toks), seq, pos0,
+                                         logits.ctypes.data if want_logits else None, amax.ctypes.data if want_logits else None, self.st))
+        return logits, (int(amax[0]) if want_logits else None)
 
     def decode_host_raw(self, T: int, want_logits: bool = True):
         """The same call with the staging buffers already filled (benchmark inner loop: no Python-side copies)."""
