@@ -439,17 +439,22 @@ static void add_bias(float * y, const float * b, int64_t n) {
     if (b) for (int64_t i = 0; i < n; i++) y[i] = y[i] + b[i];
 }
 
-/* llm_build_ffn_sparse (llama.cpp:4652-4757) with gpu_idx all zero (the --vram-budget 0 path) */
-static void ffn_sparse(pio_ctx * c, const pio_layer * L, const float * ffn_input, const float * pred_input, float * out) {
+/* llm_build_ffn_sparse (llama.cpp:4652-4757) with gpu_idx all zero (the --vram-budget 0 path).
+ * idx_imposed (tests only, not something the reference does): when not NULL, the sparse operators take THESE predictor
+ * logits instead of the ones computed here; c->pred still receives the logits computed here.  It lets a test compare two
+ * implementations under identical active sets, without the cascade one borderline neuron starts in the layers after it. */
+static void ffn_sparse(pio_ctx * c, const pio_layer * L, const float * ffn_input, const float * pred_input, float * out,
+                       const float * idx_imposed) {
     const pio_model * m = c->m;
     const int64_t F = m->n_ff, d = m->d;
     pio_mul_mat(PIO_F16, L->fc1, m->rank, d, pred_input, 1, c->pred_h);
     for (int i = 0; i < m->rank; i++) c->pred_h[i] = c->pred_h[i] > 0.0f ? c->pred_h[i] : 0.0f;
     pio_mul_mat(PIO_F16, L->fc2, F, m->rank, c->pred_h, 1, c->pred);
-    pio_mul_mat_idx(m->wtype, L->up, F, d, ffn_input, 1, c->pred, F, NULL, m->threshold, c->up);
+    const float * idx = idx_imposed ? idx_imposed : c->pred;
+    pio_mul_mat_idx(m->wtype, L->up, F, d, ffn_input, 1, idx, F, NULL, m->threshold, c->up);
     add_bias(c->up, L->up_b, F);
     if (L->gate) {
-        pio_mul_mat_idx(m->wtype, L->gate, F, d, ffn_input, 1, c->pred, F, NULL, m->threshold, c->gate);
+        pio_mul_mat_idx(m->wtype, L->gate, F, d, ffn_input, 1, idx, F, NULL, m->threshold, c->gate);
         for (int64_t i = 0; i < F; i++) {                                     /* llama.cpp:4725-4738: LLM_FFN_PAR | LLM_FFN_SYM */
             const float u = m->gate_sym ? (c->up[i] > 0.0f ? c->up[i] : 0.0f) : c->up[i];
             c->hbuf[i] = (c->gate[i] > 0.0f ? c->gate[i] : 0.0f) * u;
@@ -461,12 +466,17 @@ static void ffn_sparse(pio_ctx * c, const pio_layer * L, const float * ffn_input
     /* the CPU F16 axpy skips every row when src[3] is NULL (ggml.c:14424); the graph always passes the
      * all-zero gpu_idx, which selects "row lives on the CPU" for every neuron */
     int32_t * gi = calloc((size_t)F, sizeof *gi);
-    pio_axpy(m->wtype, L->down_t, F, d, c->hbuf, 1, c->pred, F, gi, m->threshold, out);
+    pio_axpy(m->wtype, L->down_t, F, d, c->hbuf, 1, idx, F, gi, m->threshold, out);
     free(gi);
     add_bias(out, L->down_b, d);
 }
 
 void pio_decode(pio_ctx * c, int32_t token, int32_t pos, float * logits, float * pred_out) {
+    pio_decode_imposed(c, token, pos, logits, pred_out, NULL);
+}
+
+/* pio_decode with the predictor logits of every layer imposed from outside (float [n_layer, n_ff]); see ffn_sparse */
+void pio_decode_imposed(pio_ctx * c, int32_t token, int32_t pos, float * logits, float * pred_out, const float * idx_imposed) {
     const pio_model * m = c->m;
     const int64_t d = m->d, dkv = d_kv(m), hd = d / m->n_head;
     pio_fp16_to_fp32_row(m->tok_embd + (size_t)token * d, c->x, d);          /* ggml_get_rows */
@@ -503,12 +513,12 @@ void pio_decode(pio_ctx * c, int32_t token, int32_t pos, float * logits, float *
         float * pred_dst = pred_out ? pred_out + (size_t)il * m->n_ff : NULL;
         if (m->arch == PIO_ARCH_FALCON) {
             /* parallel block: FFN reads attn_norm, predictor reads the layer input (llama.cpp:5422-5428) */
-            ffn_sparse(c, L, c->attn_norm, inpL, c->ffn_out);
+            ffn_sparse(c, L, c->attn_norm, inpL, c->ffn_out, idx_imposed ? idx_imposed + (size_t)il * m->n_ff : NULL);
             for (int64_t i = 0; i < d; i++) c->x[i] = (c->ffn_out[i] + c->attn_out[i]) + inpL[i];
         } else {
             for (int64_t i = 0; i < d; i++) c->ffn_inp[i] = c->attn_out[i] + inpL[i];
             build_norm(m, c->ffn_inp, L->ffn_norm_w, L->ffn_norm_b, c->cur);
-            ffn_sparse(c, L, c->cur, c->ffn_inp, c->ffn_out);
+            ffn_sparse(c, L, c->cur, c->ffn_inp, c->ffn_out, idx_imposed ? idx_imposed + (size_t)il * m->n_ff : NULL);
             for (int64_t i = 0; i < d; i++) c->x[i] = c->ffn_out[i] + c->ffn_inp[i];
         }
         if (pred_dst) memcpy(pred_dst, c->pred, (size_t)m->n_ff * 4);

@@ -104,6 +104,7 @@ void      pio_ctx_free(pio_ctx * c);
 /* One token at position pos; logits[n_vocab] out.  If mask_out != NULL it receives, per layer,
  * the predictor logits (n_layer * n_ff floats). */
 void pio_decode(pio_ctx * c, int32_t token, int32_t pos, float * logits, float * pred_out);
+void pio_decode_imposed(pio_ctx * c, int32_t token, int32_t pos, float * logits, float * pred_out, const float * idx_imposed);
 
 #ifdef __cplusplus
 }

@@ -242,6 +242,15 @@ class OracleModel:
         self.o.lib.pio_decode(self.ctx, C.c_int32(int(token)), C.c_int32(int(pos)), _ptr(logits), _ptr(pred))
         return (logits, pred) if want_pred else logits
 
+    def decode_imposed(self, token: int, pos: int, idx_imposed):
+        """decode() with every layer's sparse operators driven by the GIVEN predictor logits [n_layer, n_ff] (another
+        implementation's); returns (logits, the predictor logits computed here)."""
+        logits = np.empty(self.spec.n_vocab, np.float32)
+        pred = np.empty((self.spec.n_layer, self.spec.n_ff), np.float32)
+        imp = np.ascontiguousarray(idx_imposed, np.float32).reshape(self.spec.n_layer, self.spec.n_ff)
+        self.o.lib.pio_decode_imposed(self.ctx, C.c_int32(int(token)), C.c_int32(int(pos)), _ptr(logits), _ptr(pred), _ptr(imp))
+        return logits, pred
+
     def close(self):
         if self.ctx:
             self.o.lib.pio_ctx_free(self.ctx)

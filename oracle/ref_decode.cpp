@@ -75,15 +75,17 @@ int main(int argc, char ** argv) {
     mp.n_gpu_layers = 0;
     mp.vram_budget_gb = getenv("REF_VRAM_GB") ? (float)atof(getenv("REF_VRAM_GB")) : 0.0f;
     mp.use_mmap = true;
-    llama_model * model = llama_load_model_from_file(model_path, mp);
-    if (!model) { fprintf(stderr, "load failed\n"); return 1; }
-
     llama_context_params cp = llama_context_default_params();
     cp.seed = 0;
     cp.n_ctx = n_prompt + n_steps + 8;
     cp.n_batch = 512;
     cp.n_threads = n_threads;
     cp.n_threads_batch = n_threads;
+    // the loader is told the context it will serve, as the reference's own programs do (common/common.cpp:966): with a VRAM
+    // budget it then reserves room for the KV cache and offloads the attention nodes as well (llama.cpp:3392-3421)
+    llama_model * model = llama_load_model_from_file_with_context(model_path, mp, &cp);
+    if (!model) { fprintf(stderr, "load failed\n"); return 1; }
+
     llama_context * ctx = llama_new_context_with_model(model, cp);
     if (!ctx) { fprintf(stderr, "context failed\n"); return 1; }
     const int n_vocab = llama_n_vocab(model);

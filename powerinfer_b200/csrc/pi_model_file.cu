@@ -25,9 +25,14 @@ static const size_t SCALAR_SIZE[13] = {1, 1, 2, 2, 4, 4, 4, 1, 0, 0, 8, 8, 8};
 struct Value { uint32_t type; size_t pos; size_t len; };              // pos: offset of the value (string: of its bytes)
 struct Tensor { std::string name; int type; int64_t ne[4]; size_t offset; size_t nbytes; };
 
-// bytes of a tensor of a type this reader knows (enum ggml_type, ggml.h:307-333); 0 otherwise
+// bytes of a tensor of a type this reader knows (enum ggml_type, ggml.h:307-333); 0 for other types; SIZE_MAX when the
+// element count or the byte count does not fit 64 bits (four extents of up to 2^40 each can wrap the product, and a wrapped
+// size would pass the end-of-file check while the extents still advertise a huge tensor)
 size_t tensor_bytes(int type, const int64_t ne[4]) {
-    const uint64_t n = (uint64_t)ne[0] * (uint64_t)ne[1] * (uint64_t)ne[2] * (uint64_t)ne[3];
+    uint64_t n = 1;
+    for (int k = 0; k < 4; k++)
+        if (__builtin_mul_overflow(n, (uint64_t)ne[k], &n)) return SIZE_MAX;
+    if (n > (UINT64_MAX >> 3)) return SIZE_MAX;                       // n * 4 below must not wrap either
     switch (type) {
         case 0:  return n * 4;                                        // F32
         case 1:  return n * 2;                                        // F16
@@ -130,6 +135,7 @@ int parse(pi_model_file * f) {
         t.type = (int)c.take<uint32_t>();
         t.offset = (size_t)c.take<uint64_t>();
         t.nbytes = tensor_bytes(t.type, t.ne);
+        if (t.nbytes == SIZE_MAX) c.ok = false;
         if (!c.ok) break;
         f->by_name.emplace(t.name, f->tensors.size());
         f->tensors.push_back(std::move(t));

@@ -32,23 +32,32 @@ static constexpr int AXPY_MAX_CTA_ROWS = 4096;          // rows one axpy CTA may
 // ---------------------------------------------------------------------------------------------- masks -> ranks
 // s_mask[n_chunks], s_pref[n_chunks + 1] (exclusive prefix of popc), s_warp[ROWS_WARPS]: all in shared memory.
 // Returns the number of active rows.  Ends with a block barrier.
-__device__ __forceinline__ int scan_masks(const uint32_t * __restrict__ masks, int n_chunks, int nrows,
-                                          uint32_t * s_mask, int * s_pref, int * s_warp) {
-    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+static constexpr int SCAN_WORDS = ROWS_MAX_CHUNKS / ROWS_THREADS;   // mask words per thread
+
+// first half: this thread's mask words into registers (an L2 round trip the caller can overlap with other loads)
+__device__ __forceinline__ void scan_masks_load(const uint32_t * __restrict__ masks, int n_chunks, int nrows, uint32_t (&m)[SCAN_WORDS]) {
     const int per = (n_chunks + ROWS_THREADS - 1) / ROWS_THREADS;
-    const int c0 = min(tid * per, n_chunks), c1 = min(c0 + per, n_chunks);
-    uint32_t m[ROWS_MAX_CHUNKS / ROWS_THREADS];
-    int mine = 0;
+    const int c0 = min((int)threadIdx.x * per, n_chunks), c1 = min(c0 + per, n_chunks);
 #pragma unroll
-    for (int k = 0; k < ROWS_MAX_CHUNKS / ROWS_THREADS; k++) {
+    for (int k = 0; k < SCAN_WORDS; k++) {
         m[k] = 0u;
         if (c0 + k < c1) {
             m[k] = __ldcg(masks + c0 + k);
             const int left = nrows - (c0 + k) * 32;                 // bits beyond the last row never count
             if (left < 32) m[k] &= left <= 0 ? 0u : ((1u << left) - 1u);
-            mine += __popc(m[k]);
         }
     }
+}
+
+// second half: block-wide exclusive scan of the popcounts
+__device__ __forceinline__ int scan_masks_finish(const uint32_t (&m)[SCAN_WORDS], int n_chunks,
+                                                 uint32_t * s_mask, int * s_pref, int * s_warp) {
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int per = (n_chunks + ROWS_THREADS - 1) / ROWS_THREADS;
+    const int c0 = min(tid * per, n_chunks), c1 = min(c0 + per, n_chunks);
+    int mine = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_WORDS; k++) mine += __popc(m[k]);
     int incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -61,12 +70,19 @@ __device__ __forceinline__ int scan_masks(const uint32_t * __restrict__ masks, i
     for (int w = 0; w < wid; w++) base += s_warp[w];
     int off = base + incl - mine;
 #pragma unroll
-    for (int k = 0; k < ROWS_MAX_CHUNKS / ROWS_THREADS; k++) {
+    for (int k = 0; k < SCAN_WORDS; k++) {
         if (c0 + k < c1) { s_mask[c0 + k] = m[k]; s_pref[c0 + k] = off; off += __popc(m[k]); }
     }
     if (tid == ROWS_THREADS - 1) s_pref[n_chunks] = base + incl;
     __syncthreads();
     return s_pref[n_chunks];
+}
+
+__device__ __forceinline__ int scan_masks(const uint32_t * __restrict__ masks, int n_chunks, int nrows,
+                                          uint32_t * s_mask, int * s_pref, int * s_warp) {
+    uint32_t m[SCAN_WORDS];
+    scan_masks_load(masks, n_chunks, nrows, m);
+    return scan_masks_finish(m, n_chunks, s_mask, s_pref, s_warp);
 }
 
 // local row number of the active row with rank `rank` (0 <= rank < total)
@@ -118,6 +134,8 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_gather_rows(const GatherP p
 
     pdl_launch();
     pdl_wait();
+    uint32_t mw[SCAN_WORDS];                                        // the mask words travel while the activation is staged
+    scan_masks_load(p.masks, p.n_chunks, p.nrows, mw);
     // ---- stage the activation (FP16 vector, or Q8_0 planes lo | hi | {scale, sum})
     if (WT == PI_TYPE_F16) {
         const uint4 * src = reinterpret_cast<const uint4 *>(p.x.h16);
@@ -132,7 +150,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_gather_rows(const GatherP p
             ds[i] = make_uint2(__float_as_uint(p.x.d[i]), (unsigned)p.x.s[i]);
         }
     }
-    const int n = scan_masks(p.masks, p.n_chunks, p.nrows, s_mask, s_pref, s_warp);
+    const int n = scan_masks_finish(mw, p.n_chunks, s_mask, s_pref, s_warp);
 
     const int TW = gridDim.x * ROWS_WARPS, gw = blockIdx.x * ROWS_WARPS + wid;
     const int units = WT == PI_TYPE_F16 ? p.ncols / 8 : p.nb;       // 16-byte units per row

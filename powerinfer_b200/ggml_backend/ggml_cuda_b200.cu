@@ -133,7 +133,7 @@ void * workspace(size_t need) {
 // device address of an operand: resident tensors as they are; CPU-resident ones are staged for this node
 const void * operand(const ggml_tensor * t) {
     if (on_gpu(t)) {
-        if (!t->extra) die("operand without device memory", t->name);
+        if (!t->extra || !dev_of(t)->data) die("operand without device memory", t->name);
         return dev_of(t)->data;
     }
     if (!t_contiguous(t)) die("CPU-resident operand is not contiguous", t->name);
@@ -145,7 +145,7 @@ const void * operand(const ggml_tensor * t) {
 struct Result { void * dev; ggml_tensor * t; bool staged; };
 Result result_of(ggml_tensor * t) {
     Result r; r.t = t;
-    if (on_gpu(t)) { if (!t->extra) die("result without device memory", t->name); r.dev = dev_of(t)->data; r.staged = false; }
+    if (on_gpu(t)) { if (!t->extra || !dev_of(t)->data) die("result without device memory", t->name); r.dev = dev_of(t)->data; r.staged = false; }
     else {
         if (!t_contiguous(t)) die("CPU-resident result is not contiguous", t->name);
         r.dev = tmp_take(t_nbytes(t)); r.staged = true;
@@ -572,10 +572,9 @@ B2_EXPORT void ggml_cuda_assign_scratch_offset(ggml_tensor * t, size_t offset) {
     ensure_scratch();
     TensorDev * e = node_extra();
     if (shares_parent_memory(t) && on_gpu(t->src[0]) && t->src[0]->extra) e->data = (char *)dev_of(t->src[0])->data + view_offset(t);
-    else {
-        if (offset + t_nbytes(t) > g_scratch_size) die("node beyond the scratch buffer", t->name);
-        e->data = g_scratch + offset;
-    }
+    else if (t->op == GGML_OP_CPY && on_gpu(t->src[1]) && t->src[1]->extra) e->data = dev_of(t->src[1])->data;   // a copy's result IS its target
+    else if (offset <= g_scratch_size && t_nbytes(t) <= g_scratch_size - offset) e->data = g_scratch + offset;
+    else e->data = nullptr;      // not a node of the host's graph buffer (e.g. a view of the KV cache): never dereferenced as such
     t->extra = e;
 }
 

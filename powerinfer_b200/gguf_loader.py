@@ -183,3 +183,51 @@ def write_gpu_split(path: str, gpu_idx: list, gpu_bucket: list, vram_capacity: i
         f.write(head)
         for b in blobs:
             f.write(b)
+
+
+def write_model_file(spec, tensors, path):
+    """Write a synthetic model as a PowerInfer GGUF file the reference's loader accepts (magic PWRI, ggml.c:19481-19495; keys and
+    tensor names as llm_load_hparams / llm_load_sparse_model_tensors read them, llama.cpp:2330-2400, 3159-3390).  Needs the
+    `gguf` package."""
+    from . import synth
+    import gguf
+    V = spec.n_vocab
+    toks = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + [f"tok{i}" for i in range(V - 259)]
+    types = [2, 3, 3] + [6] * 256 + [1] * (V - 259)
+    arch = spec.arch_name
+    w = gguf.GGUFWriter(path, arch)
+    w.add_name("synthetic-" + arch)
+    w.add_context_length(2050 if spec.arch == synth.ARCH_OPT else spec.n_ctx)
+    w.add_embedding_length(spec.d)
+    w.add_block_count(spec.n_layer)
+    w.add_feed_forward_length(spec.n_ff)
+    w.add_head_count(spec.n_head)
+    w.add_head_count_kv(spec.n_head_kv)
+    if spec.arch == synth.ARCH_LLAMA:
+        w.add_rope_dimension_count(spec.head_dim)
+        w.add_layer_norm_rms_eps(spec.norm_eps)
+        w.add_rope_freq_base(spec.rope_base)
+    elif spec.arch == synth.ARCH_FALCON:
+        w.add_layer_norm_eps(spec.norm_eps)
+        w.add_rope_freq_base(spec.rope_base)
+    w.add_float32("powerinfer.sparse_threshold", spec.threshold)
+    w.add_tokenizer_model("llama")
+    w.add_token_list(toks)
+    w.add_token_scores([0.0] * V)
+    w.add_token_types(types)
+    w.add_bos_token_id(1)
+    w.add_eos_token_id(2)
+    w.add_unk_token_id(0)
+    for name, a in tensors.items():
+        if name.startswith("_"):
+            continue
+        if a.dtype == np.uint8:     # Q4_0 block bytes [rows, cols/32*18]
+            w.add_tensor(name, a, raw_dtype=gguf.GGMLQuantizationType.Q4_0)
+        else:
+            w.add_tensor(name, a)
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+    with open(path, "r+b") as f:
+        f.write(b"PWRI")

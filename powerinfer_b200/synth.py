@@ -107,9 +107,11 @@ def quantize_q4_0(x: np.ndarray) -> np.ndarray:
     return out.reshape(rows, cols // 32 * 18)
 
 
-def build_model(spec: ModelSpec) -> dict:
+def build_model(spec: ModelSpec, fast_q4: bool = False) -> dict:
     """Draw every tensor of the model.  2-D weights are float16 arrays, or uint8 Q4_0 block
-    arrays when spec.wtype == Q4_0 (predictor, embeddings and 1-D tensors stay F16 / F32)."""
+    arrays when spec.wtype == Q4_0 (predictor, embeddings and 1-D tensors stay F16 / F32).
+    fast_q4 (timing runs on large shapes only, never parity): Q4_0 blocks are drawn directly (uniform nibbles under one
+    scale chosen so that the weights' standard deviation is sigma) instead of quantising normal draws."""
     rng = np.random.default_rng(spec.seed)
     d, F, R, dkv = spec.d, spec.n_ff, spec.rank, spec.d_kv
 
@@ -117,6 +119,11 @@ def build_model(spec: ModelSpec) -> dict:
         return (rng.standard_normal(shape, dtype=np.float32) * np.float32(spec.sigma)).astype(np.float16)
 
     def w2(*shape):
+        if spec.wtype == Q4_0 and fast_q4:
+            rows, cols = shape
+            out = rng.integers(0, 256, (rows, cols // 32, 18), dtype=np.uint8)
+            out[..., 0:2] = np.array([spec.sigma / 4.61], np.float16).view(np.uint8)      # std of a uniform nibble - 8 is 4.61
+            return out.reshape(rows, cols // 32 * 18)
         w = f16(*shape)
         return quantize_q4_0(w.astype(np.float32)) if spec.wtype == Q4_0 else w
 

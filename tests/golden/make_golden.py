@@ -102,47 +102,8 @@ def op_inputs(c):
 
 def write_gguf(spec, tensors, path):
     """Write a PowerInfer GGUF the reference loader accepts (magic PWRI, ggml.c:19481-19495)."""
-    import gguf
-    V = spec.n_vocab
-    toks = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + [f"tok{i}" for i in range(V - 259)]
-    types = [2, 3, 3] + [6] * 256 + [1] * (V - 259)
-    arch = spec.arch_name
-    w = gguf.GGUFWriter(path, arch)
-    w.add_name("synthetic-" + arch)
-    w.add_context_length(2050 if spec.arch == synth.ARCH_OPT else spec.n_ctx)
-    w.add_embedding_length(spec.d)
-    w.add_block_count(spec.n_layer)
-    w.add_feed_forward_length(spec.n_ff)
-    w.add_head_count(spec.n_head)
-    w.add_head_count_kv(spec.n_head_kv)
-    if spec.arch == synth.ARCH_LLAMA:
-        w.add_rope_dimension_count(spec.head_dim)
-        w.add_layer_norm_rms_eps(spec.norm_eps)
-        w.add_rope_freq_base(spec.rope_base)
-    elif spec.arch == synth.ARCH_FALCON:
-        w.add_layer_norm_eps(spec.norm_eps)
-        w.add_rope_freq_base(spec.rope_base)
-    w.add_float32("powerinfer.sparse_threshold", spec.threshold)
-    w.add_tokenizer_model("llama")
-    w.add_token_list(toks)
-    w.add_token_scores([0.0] * V)
-    w.add_token_types(types)
-    w.add_bos_token_id(1)
-    w.add_eos_token_id(2)
-    w.add_unk_token_id(0)
-    for name, a in tensors.items():
-        if name.startswith("_"):
-            continue
-        if a.dtype == np.uint8:     # Q4_0 block bytes [rows, cols/32*18]
-            w.add_tensor(name, a, raw_dtype=gguf.GGMLQuantizationType.Q4_0)
-        else:
-            w.add_tensor(name, a)
-    w.write_header_to_file()
-    w.write_kv_data_to_file()
-    w.write_tensors_to_file()
-    w.close()
-    with open(path, "r+b") as f:
-        f.write(b"PWRI")
+    from powerinfer_b200 import gguf_loader
+    gguf_loader.write_model_file(spec, tensors, path)
 
 
 def run_ref_decode(gguf_path, tokens, n_prompt, n_steps, n_vocab, mode="batch", forced=False, threads=1):

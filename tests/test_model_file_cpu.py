@@ -104,6 +104,21 @@ def _s(b: bytes) -> bytes:
     return len(b).to_bytes(8, "little") + b
 
 
+def test_extents_whose_product_wraps_64_bits_are_refused(tmp_path):
+    """Four extents of 2^16 x 2^16 x 2^16 x 2^16 (each far below the per-extent limit) make an element count of 2^64,
+    which wraps to 0: such an entry must be refused, not read as an empty tensor that advertises huge extents."""
+    import struct
+    for ne in ([1 << 16] * 4, [1 << 40, 1 << 24, 1, 1], [1 << 31, 1 << 31, 2, 1]):
+        head = b"GGUF" + struct.pack("<I", 3) + struct.pack("<Q", 1) + struct.pack("<Q", 0)
+        info = _s(b"big") + struct.pack("<I", 4) + b"".join(struct.pack("<Q", e) for e in ne) + struct.pack("<I", 0) + struct.pack("<Q", 0)
+        blob = head + info
+        blob += b"\0" * ((-len(blob)) % 32) + b"\0" * 64
+        p = tmp_path / "wrap.gguf"
+        p.write_bytes(blob)
+        with pytest.raises(_lib.PiError):
+            model_file.ModelFile(str(p))
+
+
 def _random_container(rng):
     """A random GGUF v3 container: every key type (arrays of scalars and of strings included), tensors of the four types
     the readers know with 1..4 dimensions, a random alignment.  -> (bytes, expected keys, expected tensors)."""
