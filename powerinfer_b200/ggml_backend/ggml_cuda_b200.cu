@@ -37,6 +37,9 @@
 
 namespace {
 
+// Every copy, fill and kernel of this file goes through ONE stream (g_stream, non-blocking).  A synchronous cudaMemcpy
+// from pageable host memory may return before its DMA has landed, and a non-blocking stream is not ordered behind the
+// default stream: a kernel on g_stream could then read the destination too early.  So: async calls on g_stream only.
 // ------------------------------------------------------------------------------------------------ state
 struct TensorDev {                 // what tensor->extra points to
     void * data;                   // device address (first member: ggml_cuda_get_data_pp hands out its address)
@@ -112,7 +115,7 @@ void * tmp_take(size_t bytes) {
         const size_t want = (g_tmp_used + bytes) * 2 + (size_t(1) << 20);
         char * n = nullptr;
         CU(cudaMalloc(&n, want));
-        if (g_tmp) { CU(cudaMemcpy(n, g_tmp, g_tmp_used, cudaMemcpyDeviceToDevice)); CU(cudaFree(g_tmp)); }
+        if (g_tmp) { CU(cudaMemcpyAsync(n, g_tmp, g_tmp_used, cudaMemcpyDeviceToDevice, g_stream)); CU(cudaStreamSynchronize(g_stream)); CU(cudaFree(g_tmp)); }
         g_tmp = n; g_tmp_bytes = want;
     }
     void * p = g_tmp + g_tmp_used;
@@ -328,7 +331,8 @@ void op_rope(ggml_tensor * dst) {
         std::vector<float> host((size_t)ROPE_TABLE_POS * n_dims);
         pi_rope_table_host(host.data(), ROPE_TABLE_POS, n_dims, freq_base);
         CU(cudaMalloc(&table, host.size() * 4));
-        CU(cudaMemcpy(table, host.data(), host.size() * 4, cudaMemcpyHostToDevice));
+        CU(cudaMemcpyAsync(table, host.data(), host.size() * 4, cudaMemcpyHostToDevice, g_stream));
+        CU(cudaStreamSynchronize(g_stream));                  // `host` dies at the end of this block
     }
     const void * pa = operand(a);
     const void * pp = operand(pos);
@@ -473,7 +477,7 @@ void assign(ggml_tensor * t, bool scratch, bool force_inplace, bool defer) {
         e = new TensorDev();
         e->bytes = t_nbytes(t); e->owned = 1;
         CU(cudaMalloc(&e->data, e->bytes));
-        CU(cudaMemset(e->data, 0, e->bytes));
+        CU(cudaMemsetAsync(e->data, 0, e->bytes, g_stream));
     }
     t->extra = e;
 }
@@ -489,12 +493,13 @@ void upload(const void * host, ggml_tensor * t, bool alloc_only) {
         if (planar) {                                      // ggml blocks -> planar rows, through a staging copy
             void * staging = nullptr;
             CU(cudaMalloc(&staging, bytes));
-            CU(cudaMemcpy(staging, host, bytes, cudaMemcpyHostToDevice));
+            CU(cudaMemcpyAsync(staging, host, bytes, cudaMemcpyHostToDevice, g_stream));
             PI(pi_q4_0_repack(staging, e->data, t->ne[1], t->ne[0], g_stream));
             CU(cudaStreamSynchronize(g_stream));
             CU(cudaFree(staging));
         } else {
-            CU(cudaMemcpy(e->data, host, bytes, cudaMemcpyHostToDevice));
+            CU(cudaMemcpyAsync(e->data, host, bytes, cudaMemcpyHostToDevice, g_stream));
+            CU(cudaStreamSynchronize(g_stream));
         }
     }
     t->extra = e;
@@ -556,7 +561,8 @@ B2_EXPORT void ggml_cuda_cpy_1d(ggml_tensor * dst, const ggml_tensor * src) {
         PI(pi_q4_0_repack(staging, dev_of(dst)->data, 1, src->ne[0], g_stream));
         CU(cudaStreamSynchronize(g_stream));
     } else {
-        CU(cudaMemcpy(dev_of(dst)->data, src->data, bytes, cudaMemcpyHostToDevice));
+        CU(cudaMemcpyAsync(dev_of(dst)->data, src->data, bytes, cudaMemcpyHostToDevice, g_stream));
+        CU(cudaStreamSynchronize(g_stream));
     }
 }
 
