@@ -426,15 +426,30 @@ def main():
         torch.cuda.synchronize()
 
     g, layers = synth_device.build_local_model(spec, world, rank, seed=0)
-    eng = engine.DecodeEngine(spec, g, max_batch=T, n_ranks=world, rank=rank, local_layers=layers)
+    PB = 32                                           # prompt chunk: tokens of one sequence per step
+    eng = engine.DecodeEngine(spec, g, max_batch=max(T, PB), n_ranks=world, rank=rank, local_layers=layers)
     del layers
     if world > 1:
         eng.setup_exchange()
 
+    # ---- prompt: through the engine's chunked prompt path (pi_engine_prefill_host), timed on its own
     prompt = np.random.default_rng(0).integers(0, spec.n_vocab, (T, P))
-    for p in range(P):                                # prompt, one position per step (prefill is not on the measured path)
-        eng.decode([int(v) for v in prompt[:, p]], [p] * T, want_logits=False)
-    start_tokens = [int(v) for v in eng.h_argmax[:T]]
+    eng.prefill([int(v) for v in prompt[0, :PB]], seq=0, pos0=0, want_logits=True)       # warm-up: plain run + capture
+    eng.prefill([int(v) for v in prompt[0, :PB]], seq=0, pos0=0, want_logits=False)
+    eng.prefill([int(v) for v in prompt[0, :PB]], seq=0, pos0=0, want_logits=True)
+    eng.prefill([int(v) for v in prompt[0, :PB]], seq=0, pos0=0, want_logits=False)
+    barrier()
+    t0 = time.perf_counter()
+    start_tokens = []
+    for b in range(T):
+        _, first = eng.prefill([int(v) for v in prompt[b]], seq=b, pos0=0, want_logits=True)
+        start_tokens.append(int(first))
+    barrier()
+    prompt_s = time.perf_counter() - t0
+    if world > 1:
+        tp = torch.tensor([prompt_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tp, op=dist.ReduceOp.MAX)
+        prompt_s = float(tp[0])
 
     def reset(pos0):
         eng.set_inputs_device(start_tokens, [pos0] * T)
@@ -557,6 +572,7 @@ def main():
                               "per_step": spec.n_layer * (1 if spec.arch == 1 else 2), "bytes_per_exchange_per_peer": T * spec.d * 4,
                               "nccl_all_reduce_same_bytes_us": round(nccl_us, 2)} if world > 1 else None),
                 "greedy_ids": greedy_ids,
+                "prompt_tok_per_s": round(T * P / prompt_s, 1), "prompt_chunk": PB,
                 "stage_ms_profiled": {k: round(v, 4) for k, v in stage_ms.items()},
                 "mean_active_neurons_per_layer": round(active, 1), "env_overrides": pi_env()}
         if world == 1 and not args.no_cpu_baseline:

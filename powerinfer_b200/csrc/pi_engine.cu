@@ -118,6 +118,7 @@ struct pi_engine {
     pi_exchange xch;
     cudaGraphExec_t graphs[3][PI_MAX_BATCH + 1];   // [0] decode, [1] prompt chunk, [2] prompt chunk without the lm head
     bool warmed[3][PI_MAX_BATCH + 1];
+    int graph_nodes[3][PI_MAX_BATCH + 1];          // kernel nodes of each captured graph
     int launches;                            // kernels enqueued by the last enqueue_step
     float * pred_trace;                      // optional [n_layer, max_batch, F]: keeps every layer's predictor logits
     bool pdl;                                // programmatic dependent launch between the kernels of a step
@@ -236,6 +237,7 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
     e->k_cache = (__half *)k_cache; e->v_cache = (__half *)v_cache;
     memset(e->graphs, 0, sizeof e->graphs);
     memset(e->warmed, 0, sizeof e->warmed);
+    memset(e->graph_nodes, 0, sizeof e->graph_nodes);
     memset(&e->xch, 0, sizeof e->xch);
     e->pred_trace = nullptr; e->launches = 0;
     { const char * v = getenv("PI_PDL"); e->pdl = !(v && v[0] == '0'); }
@@ -576,7 +578,7 @@ int count_kernel_nodes(cudaGraph_t graph) {
 // first call for a batch size: one plain run (fills every per-kernel attribute cache), then capture
 int run_step(pi_engine * e, int T, cudaStream_t st, int mode = 0) {
     StageTimer tm;
-    if (e->graphs[mode][T]) { PI_CUDA(cudaGraphLaunch(e->graphs[mode][T], st)); return PI_OK; }
+    if (e->graphs[mode][T]) { PI_CUDA(cudaGraphLaunch(e->graphs[mode][T], st)); e->launches = e->graph_nodes[mode][T]; return PI_OK; }
     if (!e->warmed[mode][T]) {
         e->warmed[mode][T] = true;
         return enqueue_step(e, T, st, tm, mode);
@@ -592,7 +594,7 @@ int run_step(pi_engine * e, int T, cudaStream_t st, int mode = 0) {
     const cudaError_t ci = cudaGraphInstantiate(&exec, graph, 0);
     cudaGraphDestroy(graph);
     if (ci != cudaSuccess) return cuda_fail(ci, "cudaGraphInstantiate");
-    e->graphs[mode][T] = exec;
+    e->graphs[mode][T] = exec; e->graph_nodes[mode][T] = e->launches;
     PI_CUDA(cudaGraphLaunch(exec, st));
     return PI_OK;
 }

@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_gather_rows(const GatherP p
         }
     }
     const int n = scan_masks_finish(mw, p.n_chunks, s_mask, s_pref, s_warp);
+    PI_TL_MARK(0);
 
     const int TW = gridDim.x * ROWS_WARPS, gw = blockIdx.x * ROWS_WARPS + wid;
     const int units = WT == PI_TYPE_F16 ? p.ncols / 8 : p.nb;       // 16-byte units per row
@@ -159,6 +160,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_gather_rows(const GatherP p
         const long long rank = gw + (long long)(base + lane) * TW;
         const int my_row = rank < n ? row_of_rank((int)rank, p.n_chunks, s_mask, s_pref) : -1;
         const int cnt = __popc(__ballot_sync(0xffffffffu, my_row >= 0));
+        if (base == 0) PI_TL_MARK(1);
         for (int u0 = 0; u0 < cnt; u0++) {
             const int r = __shfl_sync(0xffffffffu, my_row, u0);
             const uint8_t * row = p.W + (size_t)r * p.row_bytes;
@@ -304,6 +306,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_axpy_rows(const AxpyRowsP p
     pdl_launch();
     pdl_wait();
     const int n = scan_masks(p.masks, p.n_chunks, p.nrows, s_mask, s_pref, s_warp);
+    PI_TL_MARK(0);
 
     // ---- the rows of this row group (ranks rg, rg + n_rg, ...) whose coefficient is not zero, in rank order.
     // Coefficient = what the CPU path multiplies the row by: FP16(h) for FP16 rows; for Q4_0 the int8 quant of h within its
@@ -345,6 +348,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_axpy_rows(const AxpyRowsP p
         __syncthreads();
     }
     const int m = s_cnt;
+    PI_TL_MARK(1);
 
     // ---- main loop: warp w takes entries w, w + 16, ...; a lane owns 32 columns of the slice:
     //      Q4_0: block `slice * 32 + lane` (sum index = column inside the block);
@@ -422,6 +426,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_axpy_rows(const AxpyRowsP p
     // ---- warps are added in warp order through shared memory (sum index a of lane l at a * 33 + l: no bank conflicts),
     //      then the slice of this row group's partial vector is written
     __syncthreads();                                                 // everyone is done with s_row / s_coef
+    PI_TL_MARK(2);
     float * s_red = reinterpret_cast<float *>(smem);
     float * mine = s_red + (size_t)wid * (32 * 33);
 #pragma unroll
@@ -432,6 +437,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_axpy_rows(const AxpyRowsP p
         mine[(2 * j + 1) * 33 + lane] = a1;
     }
     __syncthreads();
+    PI_TL_MARK(3);
     float * out = p.partial + (size_t)rg * p.ncols + (size_t)slice * SLICE;
     for (int cidx = tid; cidx < SLICE; cidx += ROWS_THREADS) {
         if ((size_t)slice * SLICE + cidx >= (size_t)p.ncols) break;

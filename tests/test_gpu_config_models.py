@@ -17,8 +17,8 @@ for the masks (`decode_imposed`), still computes its own predictor logits, and t
     on the small Q4_0 models, where such a rounding flip is rare, to 1e-7; at d 8192 the logits reach 7 and differ by 0.06
     to 0.10.)
   * active sets: a neuron can only come out differently where the two predictor logits straddle the threshold, so the
-    bound is on the predictor logits themselves: within 5e-3 (FP16 models) / 1 % of the largest logit (Q4_0) in every
-    layer, and fewer than 0.3 % of the neurons differ.
+    bound is on the predictor logits themselves: within 5e-3 or 0.1 % of the largest logit (FP16 models; the logits
+    reach 50 at d 12288) / 1 % of the largest logit (Q4_0) in every layer, and fewer than 0.3 % of the neurons differ.
   * greedy choice identical to the checker's wherever the checker's top-2 gap exceeds twice the logit bar.
 The free-running greedy stream against the reference's own stream is reported (length of the common prefix) and must be
 identical for the falcon-shape model, where it is; elsewhere a borderline neuron or a near-tie (top-2 gaps of 0.02 occur)
@@ -82,7 +82,7 @@ def test_configuration_shaped_model_32_steps(engine_mod, name):
         worst_pred, worst_pred_rel, most_flips = max(worst_pred, pdiff), max(worst_pred_rel, pdiff / pscale), max(most_flips, flips)
         bar = 2.5e-2 * scale if q4 else 2e-2
         assert err <= bar, (pos, err, bar)
-        assert (pdiff <= 1e-2 * pscale) if q4 else (pdiff <= 5e-3), (pos, pdiff, pscale)
+        assert pdiff <= (1e-2 * pscale if q4 else max(5e-3, 1e-3 * pscale)), (pos, pdiff, pscale)
         assert flips <= 3e-3 * spec.n_layer * spec.n_ff, (pos, flips)
         srt = np.sort(lo)[::-1]
         if srt[0] - srt[1] > 2 * bar:
