@@ -568,7 +568,7 @@ def main():
                              "frac_of_measured_peak": round(step_bytes / (ms / K * 1e-3) / 1e9 / peak, 3)},
                 "ops": ops, "latency_stages": {st: {"ms_per_step": round(b2b[st][0] * b2b[st][1] * 1e-3, 4), "launches_per_step": b2b[st][1],
                                                     "us_per_launch": round(b2b[st][0], 2)} for st in ("norm", "attention", "compact") if st in b2b},
-                "exchange": ({"kernel": "inside the norm that consumes the sum (k_norm_cluster): peer stores, per-slice flags, bounded wait",
+                "exchange": ({"kernel": "inside the norm that consumes the sum (k_norm_cluster): each value stored into the peers beside the number of the exchange, bounded poll, no flag and no fence",
                               "per_step": spec.n_layer * (1 if spec.arch == 1 else 2), "bytes_per_exchange_per_peer": T * spec.d * 4,
                               "nccl_all_reduce_same_bytes_us": round(nccl_us, 2)} if world > 1 else None),
                 "greedy_ids": greedy_ids,

@@ -210,20 +210,22 @@ typedef struct {
     const void  * output;            /* [n_vocab, d] in wtype; NULL: tied to tok_embd (opt, llama.cpp:5199) */
 } pi_model_weights;
 
-/* Peer mailboxes for the per-layer exchange of partial d_model vectors (n_ranks > 1).  Every rank owns a mailbox
- * [2, n_ranks, slot_floats] F32 and flags [2, n_ranks, flag_words] u32 in ITS OWN memory; peers write into it with plain
- * stores (the mapped addresses of every rank's mailbox and flags, own included, are listed here), nobody reads remote
- * memory.  slot_floats >= max_batch * d, flag_words >= 8 * max_batch.  `epoch` is a zero-initialised u32 word in this
- * rank's memory: the engine counts its steps there (all ranks run the same steps, so all agree on the number of every
- * exchange); `ticket` is not used.  The exchange itself is part of the norm kernel that consumes the sum: it pushes this
- * rank's share, raises one flag per slice of the vector, waits (bounded) for the other ranks' flags of its own slice. */
+/* Peer mailboxes for the per-layer exchange of partial d_model vectors (n_ranks > 1).  Every rank owns a mailbox of
+ * [2, n_ranks, slot_floats] 8-byte pairs {F32 value, u32 number of the exchange} in ITS OWN memory, zero-initialised;
+ * peers write into it with plain stores (the mapped addresses of every rank's mailbox, own included, are listed here),
+ * nobody reads remote memory.  slot_floats >= max_batch * d, so a mailbox takes 2 * n_ranks * slot_floats * 8 bytes.
+ * `epoch` is a zero-initialised u32 word in this rank's memory: the engine counts its steps there (all ranks run the
+ * same steps, so all agree on the number of every exchange).  The exchange itself is part of the norm kernel that
+ * consumes the sum: it writes this rank's share into every other rank's mailbox, each value beside the number of the
+ * exchange, and waits (bounded) until the pairs of its own values in its own mailbox carry that number: one trip over
+ * the link, no flag, no fence.  The two halves of a mailbox alternate, so a rank that runs ahead cannot overwrite what
+ * a slower one has not yet read. */
 typedef struct {
     int n_ranks, rank_id;
     int64_t slot_floats;
-    float * mailbox_local; unsigned int * flags_local;
-    float * mailbox_peer[PI_MAX_RANKS]; unsigned int * flags_peer[PI_MAX_RANKS];
-    unsigned int * epoch, * ticket;
-    int flag_words;
+    unsigned int * mailbox_local;
+    unsigned int * mailbox_peer[PI_MAX_RANKS];
+    unsigned int * epoch;
 } pi_exchange;
 
 typedef struct pi_engine pi_engine;

@@ -110,11 +110,16 @@ struct GemvArgs {
     const void * W2 = nullptr;
     // one token: activity bit masks (one word per 32 LOCAL rows) instead of a list; selects the register-streaming kernel
     const uint32_t * masks = nullptr;
+    unsigned long long * rows_total = nullptr;   // with masks (optional): incremented by the number of active rows (statistics)
+    // dense, one token: also write the activity bit masks of the result, bit (row % 32) of word (row / 32) = !(result <
+    // masks_threshold): the predictor's mask, made where the logit is.  Room for (nrows + 63) / 64 * 2 words.
+    uint32_t * masks_out = nullptr; float masks_threshold = 0.f;
     unsigned int * status = nullptr;   // device status word; when given, T == 1 shapes use the bulk-copy ring kernel
     bool pdl = false;                  // launch with programmatic dependent launch (the kernel waits for its producer itself)
 };
 int launch_gemv(const GemvArgs & a, cudaStream_t st);
-int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaStream_t st);   // PI_ERR_UNSUPPORTED: not eligible
+// PI_ERR_UNSUPPORTED: not eligible; *wrote_masks: the kernel that ran honoured masks_out itself
+int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaStream_t st, bool * wrote_masks = nullptr);
 int launch_gemv_mma(const GemvArgs & a, cudaStream_t st);                                     // FP16 rows, T <= 32; PI_ERR_UNSUPPORTED: not eligible
 int launch_gemv_mma_q4(const GemvArgs & a, cudaStream_t st);                                  // Q4_0 rows, T >= 2; PI_ERR_UNSUPPORTED: not eligible
 
@@ -142,6 +147,9 @@ struct AxpyArgs {
     const float * h = nullptr; int64_t h_stride = 0; int T = 1;       // by global id
     const int32_t * list = nullptr; const int32_t * count = nullptr; const int32_t * bucket = nullptr;
     const uint32_t * masks = nullptr;                                 // one token: activity bit masks instead of the list
+    // with masks: entries of h at inactive rows are taken as 0 whatever h holds there (nobody has cleared them); needs
+    // bucket == nullptr.  Only the Q4_0 coefficients look at such entries (the scale of a block of 32 neurons).
+    bool h_uncleared = false;
     const float * idx = nullptr; int64_t idx_stride = 0; float threshold = 0.f;
     // Q4_0: coefficient planes made by launch_neuron_q8 (int8 by global id, float scale per 32-neuron block)
     const int8_t * cq = nullptr; const float * cd = nullptr; int64_t c_stride = 0;
@@ -175,9 +183,10 @@ struct NormArgs {
     const float * in_bias = nullptr;
     int64_t partial_stride = 0;        // floats between consecutive partials (0: T * n)
     // Sharded runs (xch != nullptr): the vector built so far (sum of the partials | x, + xch_extra) is this rank's share.
-    // The norm pushes it into slot rank_id of every rank's mailbox (plain stores, then a release flag per slice of the
-    // vector), waits (bounded by wait_cycles; on expiry bit 0 of *status is raised and the kernel carries on) for every
-    // rank's flag of the same slice in ITS OWN mailbox, and adds the slots in rank order, so all ranks hold identical sums.
+    // The norm writes it into slot rank_id of every other rank's mailbox, every value beside the number of the exchange
+    // (plain 16-byte stores of two such pairs), polls the pairs of the same values in ITS OWN mailbox until they carry that
+    // number (bounded by wait_cycles; on expiry bit 0 of *status is raised and the kernel carries on), and adds the shares
+    // in rank order, so all ranks hold identical sums.
     // xch_index is the number of this exchange within the step (0 .. xch_per_step - 1).
     const pi_exchange * xch = nullptr; int xch_index = 0, xch_per_step = 1; const float * xch_extra = nullptr;
     long long wait_cycles = 0; unsigned int * status = nullptr;
@@ -207,9 +216,6 @@ struct AttnArgs {
     bool pdl = false;
 };
 int launch_attention(const AttnArgs & a, cudaStream_t st);
-
-// flag words per (parity, rank) in a mailbox: one per (token, slice of the vector)
-static constexpr int XCH_SLICES = 8;
 
 // ------------------------------------------------------------------------------------ device primitives
 #ifdef __CUDACC__
@@ -282,9 +288,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t * bar, unsigned parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// Weights are read once per step and a step streams far more of them than L2 holds: they are marked evict-first, so what
+// IS re-used between kernels (kernel code, activations, partial vectors, masks) is not pushed out of L2 by them.
+#ifndef PI_L2_EVICT_FIRST
+#define PI_L2_EVICT_FIRST 1
+#endif
+__device__ __forceinline__ uint64_t l2_stream_policy() {
+    uint64_t pol;
+    asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));   // not volatile: one per kernel after hoisting
+    return pol;
+}
 __device__ __forceinline__ void bulk_g2s(void * dst, const void * src, unsigned bytes, uint64_t * bar) {
+#if PI_L2_EVICT_FIRST
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 :: "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(l2_stream_policy()) : "memory");
+#else
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  :: "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+#endif
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t * bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
@@ -301,10 +322,15 @@ inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
-__device__ __forceinline__ uint4 ldg_stream(const void * p) {     // read-once weights: bypass L1 allocation
+__device__ __forceinline__ uint4 ldg_stream(const void * p) {     // read-once weights: bypass L1 allocation, evict-first in L2
     uint4 v;
+#if PI_L2_EVICT_FIRST
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(l2_stream_policy()));
+#else
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+#endif
     return v;
 }
 __device__ __forceinline__ uint2 ldg_stream8(const void * p) {

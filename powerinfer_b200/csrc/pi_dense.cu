@@ -21,9 +21,9 @@ struct NormP {
     const float * x; int64_t n; int rms; float eps; const float * w; const float * b;
     const float * partial; int n_groups; int T; const float * residual; const float * residual2; const float * in_bias; float * x_out;
     int64_t partial_stride; unsigned int * status;
-    // exchange (see NormArgs): mailboxes and flags of every rank, this rank's own, the step counter
-    int x_ranks, x_rank, x_index, x_per_step, x_flag_words; int64_t x_slot; long long x_wait;
-    float * x_mbox[PI_MAX_RANKS]; unsigned int * x_flags[PI_MAX_RANKS]; const float * x_mbox_local; const unsigned int * x_flags_local;
+    // exchange (see NormArgs): mailboxes of every rank, this rank's own, the step counter
+    int x_ranks, x_rank, x_index, x_per_step; int64_t x_slot; long long x_wait;
+    unsigned int * x_mbox[PI_MAX_RANKS]; const unsigned int * x_mbox_local;
     const unsigned int * x_step; const float * x_extra;
     float * y; int act_type; ActBuf act; int act2_type; ActBuf act2; int act2_src;
 };
@@ -292,49 +292,66 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
         add8(*reinterpret_cast<const float4 *>(p.x + o), *reinterpret_cast<const float4 *>(p.x + o + 4));
     }
     if (p.x_ranks > 1) {
-        // ---- exchange: v is this rank's share.  Push it to every rank's mailbox, flag this (token, slice), wait for every
-        //      rank's flag of the same (token, slice) in this rank's own mailbox, add the slots in rank order.
+        // ---- exchange: v is this rank's share.  Every value travels as an 8-byte pair {value, number of this exchange}
+        //      (two pairs per 16-byte store), written into every other rank's mailbox with plain stores.  A pair arrives
+        //      whole, so the receiver needs no flag, no fence and no barrier: each thread polls the pairs of its own 8 values
+        //      in its own mailbox until they carry this exchange's number (bounded), then adds the shares in rank order.
         if (p.x_extra) add8(*reinterpret_cast<const float4 *>(p.x_extra + o), *reinterpret_cast<const float4 *>(p.x_extra + o + 4));
         const unsigned int epoch = __ldcg(p.x_step) * (unsigned)p.x_per_step + (unsigned)p.x_index + 1u;
         const unsigned int par = epoch & 1u;
-        const size_t slot = ((size_t)par * p.x_ranks + p.x_rank) * (size_t)p.x_slot + o;
-        const float4 v0 = make_float4(v[0], v[1], v[2], v[3]), v1 = make_float4(v[4], v[5], v[6], v[7]);
+        const size_t own_w = (((size_t)par * p.x_ranks + p.x_rank) * (size_t)p.x_slot + o) * 2;
         for (int q = 0; q < p.x_ranks; q++) {
-            *reinterpret_cast<float4 *>(p.x_mbox[q] + slot) = v0;
-            *reinterpret_cast<float4 *>(p.x_mbox[q] + slot + 4) = v1;
-        }
-        __threadfence_system();
-        __syncthreads();
-        const size_t fl = ((size_t)par * p.x_ranks) * p.x_flag_words + blockIdx.x;          // + rank * flag_words
-        if (threadIdx.x < (unsigned)p.x_ranks) {
-            unsigned int * f = p.x_flags[threadIdx.x] + fl + (size_t)p.x_rank * p.x_flag_words;
-            asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(f), "r"(epoch) : "memory");
-            const unsigned int * mine = p.x_flags_local + fl + (size_t)threadIdx.x * p.x_flag_words;
-            const long long t0 = clock64();
-            bool ok_flag = false;
-            for (;;) {
-                unsigned int seen;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine));
-                if ((int)(seen - epoch) >= 0) { ok_flag = true; break; }
-                if (clock64() - t0 > p.x_wait) break;                  // never forever: the step finishes, the host reads the status
-                __nanosleep(64);
-            }
-            if (!ok_flag) atomicOr(p.status, 1u);
-        }
-        __syncthreads();
+            if (q == p.x_rank) continue;
+            unsigned int * dst = p.x_mbox[q] + own_w;
 #pragma unroll
-        for (int j = 0; j < 8; j++) v[j] = 0.f;
-        float4 a[PI_MAX_RANKS], b[PI_MAX_RANKS];
+            for (int j = 0; j < 4; j++)
+                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};"
+                             :: "l"(dst + 4 * j), "r"(__float_as_uint(v[2 * j])), "r"(epoch), "r"(__float_as_uint(v[2 * j + 1])) : "memory");
+        }
+        uint4 w[PI_MAX_RANKS][4];
+        auto fetch = [&](int q) {
+            const unsigned int * src = p.x_mbox_local + (((size_t)par * p.x_ranks + q) * (size_t)p.x_slot + o) * 2;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(w[q][j].x), "=r"(w[q][j].y), "=r"(w[q][j].z), "=r"(w[q][j].w) : "l"(src + 4 * j) : "memory");
+        };
+        auto arrived = [&](int q) {
+            bool ok_all = true;
+#pragma unroll
+            for (int j = 0; j < 4; j++) ok_all = ok_all && (int)(w[q][j].y - epoch) >= 0 && (int)(w[q][j].w - epoch) >= 0;
+            return ok_all;
+        };
+        unsigned int pending = 0;
+#pragma unroll
+        for (int q = 0; q < PI_MAX_RANKS; q++) if (q < p.x_ranks && q != p.x_rank) fetch(q);
+#pragma unroll
+        for (int q = 0; q < PI_MAX_RANKS; q++) if (q < p.x_ranks && q != p.x_rank && !arrived(q)) pending |= 1u << q;
+        if (pending) {
+            const long long t0 = clock64();
+            while (pending) {
+#pragma unroll
+                for (int q = 0; q < PI_MAX_RANKS; q++) if (pending >> q & 1u) fetch(q);
+#pragma unroll
+                for (int q = 0; q < PI_MAX_RANKS; q++) if ((pending >> q & 1u) && arrived(q)) pending &= ~(1u << q);
+                if (pending && clock64() - t0 > p.x_wait) break;       // never forever: the step finishes, the host reads the status
+            }
+            if (pending) atomicOr(p.status, 1u);
+        }
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int q = 0; q < PI_MAX_RANKS; q++) {
-            a[q] = z4; b[q] = z4;
-            if (q < p.x_ranks) {
-                const float * sp = p.x_mbox_local + ((size_t)par * p.x_ranks + q) * (size_t)p.x_slot + o;
-                a[q] = __ldcg(reinterpret_cast<const float4 *>(sp)); b[q] = __ldcg(reinterpret_cast<const float4 *>(sp + 4));
+            if (q >= p.x_ranks) continue;
+            if (q == p.x_rank) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) s[j] += v[j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) { s[2 * j] += __uint_as_float(w[q][j].x); s[2 * j + 1] += __uint_as_float(w[q][j].z); }
             }
         }
 #pragma unroll
-        for (int q = 0; q < PI_MAX_RANKS; q++) add8(a[q], b[q]);
+        for (int j = 0; j < 8; j++) v[j] = s[j];
     }
     if (p.in_bias) add8(*reinterpret_cast<const float4 *>(p.in_bias + c), *reinterpret_cast<const float4 *>(p.in_bias + c + 4));
     if (p.residual) add8(r0, r1);
@@ -420,19 +437,18 @@ int launch_norm(const NormArgs & a, cudaStream_t st) {
     p.x = a.x; p.n = a.n; p.rms = a.rms; p.eps = a.eps; p.w = a.w; p.b = a.b;
     p.partial = a.partial; p.n_groups = a.n_groups; p.T = a.T; p.residual = a.residual; p.residual2 = a.residual2; p.in_bias = a.in_bias; p.x_out = a.x_out;
     p.partial_stride = a.partial_stride; p.status = a.status;
-    p.x_ranks = 1; p.x_rank = 0; p.x_index = 0; p.x_per_step = 1; p.x_flag_words = 0; p.x_slot = 0; p.x_wait = 0;
-    p.x_mbox_local = nullptr; p.x_flags_local = nullptr; p.x_step = nullptr; p.x_extra = nullptr;
-    for (int q = 0; q < PI_MAX_RANKS; q++) { p.x_mbox[q] = nullptr; p.x_flags[q] = nullptr; }
+    p.x_ranks = 1; p.x_rank = 0; p.x_index = 0; p.x_per_step = 1; p.x_slot = 0; p.x_wait = 0;
+    p.x_mbox_local = nullptr; p.x_step = nullptr; p.x_extra = nullptr;
+    for (int q = 0; q < PI_MAX_RANKS; q++) p.x_mbox[q] = nullptr;
     const bool xch = a.xch && a.xch->n_ranks > 1;
     if (xch) {
         const pi_exchange & x = *a.xch;
-        PI_REQUIRE(x.n_ranks <= PI_MAX_RANKS && x.mailbox_local && x.flags_local && x.epoch && a.status, "norm: exchange not configured");
+        PI_REQUIRE(x.n_ranks <= PI_MAX_RANKS && x.mailbox_local && x.epoch && a.status, "norm: exchange not configured");
         PI_REQUIRE((int64_t)a.T * a.n <= x.slot_floats, "norm: vector of %lld floats does not fit a mailbox slot", (long long)a.T * a.n);
-        PI_REQUIRE(a.T * XCH_SLICES <= x.flag_words, "norm: %d tokens need %d flag words per rank, the mailbox has %d", a.T, a.T * XCH_SLICES, x.flag_words);
-        p.x_ranks = x.n_ranks; p.x_rank = x.rank_id; p.x_index = a.xch_index; p.x_per_step = a.xch_per_step; p.x_flag_words = x.flag_words;
+        p.x_ranks = x.n_ranks; p.x_rank = x.rank_id; p.x_index = a.xch_index; p.x_per_step = a.xch_per_step;
         p.x_slot = x.slot_floats; p.x_wait = a.wait_cycles > 0 ? a.wait_cycles : 2000000000LL;       // about a second
-        for (int q = 0; q < x.n_ranks; q++) { p.x_mbox[q] = x.mailbox_peer[q]; p.x_flags[q] = x.flags_peer[q]; }
-        p.x_mbox_local = x.mailbox_local; p.x_flags_local = x.flags_local; p.x_step = x.epoch; p.x_extra = a.xch_extra;
+        for (int q = 0; q < x.n_ranks; q++) p.x_mbox[q] = x.mailbox_peer[q];
+        p.x_mbox_local = x.mailbox_local; p.x_step = x.epoch; p.x_extra = a.xch_extra;
     }
     p.y = a.y; p.act_type = a.act_type; p.act = a.act; p.act2_type = a.act2_type; p.act2 = a.act2; p.act2_src = a.act2_src;
     static int use_cluster = -1;
@@ -441,7 +457,6 @@ int launch_norm(const NormArgs & a, cudaStream_t st) {
         int cs = 0;
         for (int k = 8; k >= (xch ? 1 : 2); k /= 2) if (a.n % (k * 256) == 0 && a.n / k / 8 <= 256) { cs = k; break; }
         if (cs) {
-            PI_REQUIRE(cs <= XCH_SLICES, "norm: cluster larger than the flag layout");
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(a.T * cs); cfg.blockDim = dim3((unsigned)(a.n / cs / 8)); cfg.dynamicSmemBytes = 0; cfg.stream = st;
             cudaLaunchAttribute attr[2];
@@ -592,7 +607,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
     const float scale = 1.0f / sqrtf((float)hd);
     float mx = -INFINITY;
     if ((chunks & (chunks - 1)) == 0 && chunks <= 32) {
-        constexpr int U = 4;
+        constexpr int U = 12;                                        // rows in flight per group: 384 positions per round trip at head_dim 128
         const int LP = chunks, NG = ATTN_THREADS / LP, gi = tid / LP, c = tid % LP;
         float qr[8];
 #pragma unroll
@@ -676,10 +691,11 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
         acc[6] = fmaf(pj, v3.x, acc[6]); acc[7] = fmaf(pj, v3.y, acc[7]);
     };
     if (sl < slices) {
-        for (int j0 = sl; j0 <= pos; j0 += slices * 4) {
-            uint4 vv[4]; float pj[4];
+        constexpr int UV = 12;
+        for (int j0 = sl; j0 <= pos; j0 += slices * UV) {
+            uint4 vv[UV]; float pj[UV];
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < UV; u++) {
                 const int j = j0 + u * slices;
                 pj[u] = 0.f; vv[u] = make_uint4(0u, 0u, 0u, 0u);
                 if (j <= pos) {
@@ -689,7 +705,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attention(const AttnP p) {
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; u++) fma8(pj[u], vv[u]);
+            for (int u = 0; u < UV; u++) fma8(pj[u], vv[u]);
         }
     }
     PI_TL_MARK(3);

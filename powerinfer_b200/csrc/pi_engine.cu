@@ -123,6 +123,7 @@ struct pi_engine {
     float * pred_trace;                      // optional [n_layer, max_batch, F]: keeps every layer's predictor logits
     bool pdl;                                // programmatic dependent launch between the kernels of a step
     bool gate_sym;                           // bamboo: relu on the gated product as well
+    bool fc2_masks;                          // ... with the activity masks written by the predictor's second mat-vec itself (no mask kernel)
     bool rows1;                              // one token: masks-only compaction + register-streaming sparse kernels (shape eligible)
     long long wait_cycles;                   // bound of the exchange waits (0: about a second)
     unsigned skip_mask;                      // set only inside pi_engine_time_stage: the stages left out of the captured sequence
@@ -163,7 +164,7 @@ static void carve(pi_engine * e, void * ws, size_t ws_bytes, bool dry, size_t * 
     e->logits = cv.take<float>((size_t)T * c.n_vocab);
     e->cs = cv.take<float>((size_t)c.n_ctx * e->hd);
     e->list = cv.take<int32_t>(F); e->count = cv.take<int32_t>(1); e->ticket = cv.take<unsigned int>(1);
-    e->masks = cv.take<uint32_t>((F + 31) / 32);
+    e->masks = cv.take<uint32_t>((F + 63) / 64 * 2);
     e->cq = cv.take<int8_t>(T * F); e->cd = cv.take<float>(T * (F / 32 + 1));
     e->hidden16 = cv.take<__half>((size_t)T * c.rank);
     e->act_a = cv.act(c.wtype, c.d, T);
@@ -243,6 +244,7 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
     { const char * v = getenv("PI_PDL"); e->pdl = !(v && v[0] == '0'); }
     e->skip_mask = 0u; e->wait_cycles = 0;
     e->rows1 = rows_eligible(cfg->wtype, e->F, cfg->d) && axpy_rows_groups(e->F, cfg->d) <= e->G;
+    { const char * v = getenv("PI_FC2_MASKS"); e->fc2_masks = !(v && v[0] == '0'); }     // 0: the separate mask kernel (diagnostic)
     cudaStream_t st = (cudaStream_t)stream;
     // one-time device state: sequence ids 0..T-1, zeroed ticket / status, RoPE angle table
     std::vector<int32_t> ids(e->T_max);
@@ -279,8 +281,8 @@ int pi_engine_io(pi_engine * e, int32_t ** tokens, int32_t ** pos, float ** logi
 int pi_engine_set_exchange(pi_engine * e, const pi_exchange * x) {
     PI_REQUIRE(e && x, "engine_set_exchange: null argument");
     PI_REQUIRE(x->n_ranks == e->c.n_ranks && x->rank_id == e->c.rank_id, "engine_set_exchange: rank layout differs from the engine's");
-    PI_REQUIRE(x->flag_words >= e->T_max * XCH_SLICES && x->slot_floats >= (int64_t)e->T_max * e->c.d,
-               "engine_set_exchange: need flag_words >= %d and slot_floats >= %lld", e->T_max * XCH_SLICES, (long long)e->T_max * e->c.d);
+    PI_REQUIRE(x->slot_floats >= (int64_t)e->T_max * e->c.d && x->mailbox_local && x->epoch,
+               "engine_set_exchange: need a mailbox, a step counter and slot_floats >= %lld", (long long)e->T_max * e->c.d);
     e->xch = *x;
     for (auto & gm : e->graphs) for (auto & g : gm) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
     return PI_OK;
@@ -490,6 +492,11 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm, int mod
 
         // ---- predictor: idx = fc2 . relu(fc1 . p)   (llama.cpp:4688-4695)
         float * pred = e->pred_trace ? e->pred_trace + (size_t)il * c.max_batch * F : e->pred;
+        // One token: the sparse kernels rank the active rows themselves from bit masks, which the predictor's second mat-vec
+        // writes in its epilogue (then no mask kernel runs at all).  Q4_0 rows with an up bias keep the mask kernel: it also
+        // writes relu(bias) into the hidden vector where a row is inactive, which the axpy's per-block quantisation must see.
+        const bool rows1 = T == 1 && e->rows1;
+        const bool masks1 = rows1 && e->fc2_masks && !(wt == PI_TYPE_Q4_0 && L->up_b);
         {
             GemvArgs g1;
             g1.status = e->status; g1.pdl = pdl;
@@ -500,13 +507,13 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm, int mod
             GemvArgs g2;
             g2.status = e->status; g2.pdl = pdl;
             g2.W = L->fc2; g2.nrows = F; g2.ncols = c.rank; g2.x = hx; g2.T = T; g2.dst = pred; g2.dst_stride = F;
+            if (masks1) { g2.masks_out = e->masks; g2.masks_threshold = c.threshold; }
             STAGE(PI_STAGE_PRED, (T + 7) / 8, launch_gemv(g2, st));
         }
         // ---- mask -> activity bit masks, and for batches the sorted list of rows active for at least one token.
         //      Where a row is inactive for a token the dense hidden vector holds 0 (or relu(bias)): the Q4_0 axpy quantises
         //      that vector per 32 neurons, and a union list leaves per-token holes.
-        const bool rows1 = T == 1 && e->rows1;
-        {
+        if (!masks1) {
             CompactArgs ca;
             ca.pdl = pdl;
             ca.idx = pred; ca.idx_stride = F; ca.T = T; ca.threshold = c.threshold; ca.n_local = F;
@@ -521,7 +528,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm, int mod
             GemvArgs g;
             g.status = e->status; g.pdl = pdl;
             g.wtype = wt; g.W = L->up; g.W2 = L->gate; g.nrows = F; g.ncols = d; g.x = e->act_a.view(); g.T = T;
-            if (rows1) g.masks = e->masks; else { g.list = e->list; g.count = e->count; }
+            if (rows1) { g.masks = e->masks; if (masks1) g.rows_total = e->active_total; } else { g.list = e->list; g.count = e->count; }
             g.idx = pred; g.idx_stride = F; g.threshold = c.threshold;
             g.bias = L->up_b; g.relu = L->gate ? (e->gate_sym ? 1 : 0) : 1;
             g.dst = e->h; g.dst_stride = F;
@@ -533,7 +540,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm, int mod
             AxpyArgs a;
             a.pdl = pdl;
             a.wtype = wt; a.Wt = L->down_t; a.nrows = F; a.ncols = d; a.h = e->h; a.h_stride = F; a.T = T;
-            if (rows1) a.masks = e->masks; else { a.list = e->list; a.count = e->count; }
+            if (rows1) { a.masks = e->masks; a.h_uncleared = masks1; } else { a.list = e->list; a.count = e->count; }
             a.idx = pred; a.idx_stride = F; a.threshold = c.threshold;
             a.cq = e->cq; a.cd = e->cd; a.c_stride = F; a.partial = e->partial; a.n_groups = e->G; a.status = e->status;
             STAGE(PI_STAGE_DOWN, T == 1 ? 1 : (wt == PI_TYPE_Q4_0 ? (T + 1) / 2 : (T + 3) / 4), launch_axpy(a, st, &used));

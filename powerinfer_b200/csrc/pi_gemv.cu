@@ -298,7 +298,22 @@ static int launch_wt(const GemvP & p, int tt, bool sparse, bool gated, size_t sm
     }
 }
 
+// launch_gemv proper (below) + the activity masks a dense one-token mat-vec was asked for: made by the mat-vec's own
+// epilogue where the kernel that runs has one, else by the mask kernel over the result
+static int launch_gemv_main(const GemvArgs & a, cudaStream_t st, bool * wrote_masks);
+
 int launch_gemv(const GemvArgs & a, cudaStream_t st) {
+    bool wrote = false;
+    const int rc = launch_gemv_main(a, st, &wrote);
+    if (rc != PI_OK || !a.masks_out || wrote || a.T <= 0 || a.nrows <= 0) return rc;
+    if (a.T != 1 || a.list || a.masks || !a.dst) { set_error("gemv: masks_out needs a dense one-token mat-vec with an F32 result"); return PI_ERR_UNSUPPORTED; }
+    CompactArgs ca;
+    ca.pdl = a.pdl; ca.idx = a.dst; ca.idx_stride = a.dst_stride; ca.T = 1; ca.threshold = a.masks_threshold; ca.n_local = a.nrows;
+    ca.masks = a.masks_out;
+    return launch_compact(ca, st);
+}
+
+static int launch_gemv_main(const GemvArgs & a, cudaStream_t st, bool * wrote_masks) {
     if (a.T <= 0 || a.nrows <= 0) return PI_OK;
     if (a.T == 1 && a.masks) {                                     // one token, rows named by bit masks
         const int rc = launch_gather_rows(a, st);
@@ -314,7 +329,7 @@ int launch_gemv(const GemvArgs & a, cudaStream_t st) {
         if (rc != PI_ERR_UNSUPPORTED) return rc;
     }
     if (a.T == 1 && a.status) {
-        const int rc = launch_gemv_ring(a, a.status, a.pdl, st);
+        const int rc = launch_gemv_ring(a, a.status, a.pdl, st, wrote_masks);
         if (rc != PI_ERR_UNSUPPORTED) return rc;
     }
     const bool q4 = a.wtype == PI_TYPE_Q4_0;

@@ -30,6 +30,7 @@ struct RingP {
     const float * idx; float threshold;
     const float * bias; int relu;
     float * dst; __half * dst16;
+    uint32_t * masks_out; float masks_threshold;
     unsigned int * status;
     int R, split, stages, max_items; size_t stage_bytes;
 };
@@ -327,12 +328,17 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
     const int units = WT == PI_TYPE_F16 ? p.ncols / 8 : p.nb;
     const int rpw = R / RING_WARPS;                                 // rows of a stage per warp (1, 2, 4 or 8), consecutive
     bool dead = false;                                              // warp-uniform
-    auto store = [&](int r, float o) {
+    auto store = [&](int r, float o) -> unsigned {
         if (p.bias) o += p.bias[r];
         if (p.relu) o = fmaxf(o, 0.f);
         if (p.dst)   p.dst[r] = o;
         if (p.dst16) p.dst16[r] = __float2half_rn(o);
+        return (o < p.masks_threshold) ? 0u : 1u;                  // a NaN counts as active, as where the reference skips on `<`
     };
+    // activity masks of the result (masks_out): lane 0 of every warp leaves the bits of its rows of a stage in a byte of
+    // shared memory before it hands the stage back; warp 0, which waits for all eight hand-backs anyway, joins them and
+    // writes the stage's R bits: no atomics, nothing to clear beforehand
+    unsigned char * s_bits = smem + 192;                            // [S][RING_WARPS]
     for (int st = 0; st < n_stages; st++) {
         const int s = st % S;
         const unsigned parity = (unsigned)(st / S) & 1u;
@@ -346,6 +352,7 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
         const unsigned char * base = ring + (size_t)s * p.stage_bytes;
         const int first = stage_first(st);
         const int n = min(R, n_items - first);
+        unsigned bits = 0u;
         if (!dead) {
             int k = warp * rpw;
             const int k_end = min(k + rpw, n);
@@ -353,23 +360,35 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
                 float acc[2];
                 ring_dot_rows<WT, 2>(base + (size_t)k * p.row_bytes, (size_t)p.row_bytes, 0, units, p.nb, xs, lane, acc);
                 const float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
-                if (lane == 0) { store(first + k, v0); store(first + k + 1, v1); }
+                if (lane == 0) { bits |= store(first + k, v0) << (k - warp * rpw); bits |= store(first + k + 1, v1) << (k + 1 - warp * rpw); }
             }
             if (k < k_end) {
                 float acc[1];
                 ring_dot_rows<WT, 1>(base + (size_t)k * p.row_bytes, (size_t)p.row_bytes, 0, units, p.nb, xs, lane, acc);
                 const float v0 = warp_sum(acc[0]);
-                if (lane == 0) store(first + k, v0);
+                if (lane == 0) bits |= store(first + k, v0) << (k - warp * rpw);
             }
         }
+        if (p.masks_out && lane == 0) s_bits[s * RING_WARPS + warp] = (unsigned char)bits;
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + s);                     // this warp is done with stage s (also when it gave up)
-        if (warp == 0 && st + S < n_stages) {                        // refill: wait (bounded) until every warp has arrived
+        if (warp == 0 && (st + S < n_stages || p.masks_out)) {       // refill / masks: wait (bounded) until every warp has arrived
             int spins = 0;
             bool gave_up = false;
             while (!mbar_try_wait(empty + s, parity)) { if (++spins > (1 << 20)) { gave_up = true; break; } }
             if (gave_up) { if (lane == 0) atomicOr(p.status, 4u); }
-            else if (lane == 0 && !dead) issue(st + S);
+            else if (lane == 0 && !dead) {
+                if (p.masks_out) {
+                    unsigned long long m = 0ull;
+                    for (int w = 0; w < RING_WARPS; w++) m |= (unsigned long long)s_bits[s * RING_WARPS + w] << (w * rpw);
+                    unsigned char * mo = reinterpret_cast<unsigned char *>(p.masks_out) + first / 8;      // first % R == 0
+                    if (R == 8)       *mo = (unsigned char)m;
+                    else if (R == 16) *reinterpret_cast<unsigned short *>(mo) = (unsigned short)m;
+                    else if (R == 32) *reinterpret_cast<unsigned int *>(mo) = (unsigned int)m;
+                    else              *reinterpret_cast<unsigned long long *>(mo) = m;
+                }
+                if (st + S < n_stages) issue(st + S);
+            }
         }
     }
     if (__syncthreads_or(dead) && tid == 0) {                       // do not exit with copies still landing in shared memory
@@ -604,7 +623,8 @@ static int launch_ring_inst(const RingP & p, const RingPlan & pl, bool pdl, cuda
 }
 
 // PI_ERR_UNSUPPORTED: shape not eligible, the caller uses the register-streaming kernel instead
-int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaStream_t st) {
+int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaStream_t st, bool * wrote_masks) {
+    if (wrote_masks) *wrote_masks = false;
     if (a.T != 1 || !status) return PI_ERR_UNSUPPORTED;
     const bool sparse = a.list != nullptr, gated = a.W2 != nullptr;
     const RingPlan pl = ring_plan(a.wtype, a.nrows, a.ncols, sparse, gated);
@@ -614,6 +634,7 @@ int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaSt
     p.nrows = (int)a.nrows; p.ncols = (int)a.ncols; p.nb = (int)(a.ncols / QK); p.x = a.x;
     p.list = a.list; p.count = a.count; p.bucket = a.bucket; p.idx = a.idx; p.threshold = a.threshold;
     p.bias = a.bias; p.relu = a.relu; p.dst = a.dst; p.dst16 = a.dst16; p.status = status;
+    p.masks_out = nullptr; p.masks_threshold = a.masks_threshold;
     p.R = pl.R; p.split = pl.split; p.stages = pl.stages; p.max_items = pl.max_items; p.stage_bytes = pl.stage_bytes;
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
     {
@@ -629,6 +650,10 @@ int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaSt
                 attr_w[q4][dev] = true;
             }
             const dim3 grid(sm_count() * pl.ctas_per_sm);
+            if (pl.R == 8 || pl.R == 16 || pl.R == 32 || pl.R == 64) {      // a stage's rows are whole bytes of the masks
+                p.masks_out = a.masks_out;
+                if (wrote_masks) *wrote_masks = a.masks_out != nullptr;
+            }
             if (q4) PI_CUDA(launch_k(k_gemv_ring_w<PI_TYPE_Q4_0>, grid, dim3(RING_THREADS), pl.smem, st, pdl, p));
             else    PI_CUDA(launch_k(k_gemv_ring_w<PI_TYPE_F16>, grid, dim3(RING_THREADS), pl.smem, st, pdl, p));
             return PI_OK;

@@ -117,16 +117,16 @@ struct GatherP {
     Act x;
     const uint32_t * masks; const int32_t * bucket;
     const float * bias; int relu;
-    float * dst;
+    float * dst; unsigned long long * rows_total;
 };
 
-template <int WT, bool GATED>
+// U: 128-bit loads per matrix a lane issues before it consumes any (a row of U * 32 units or fewer is one round trip)
+template <int WT, bool GATED, int U>
 __global__ void __launch_bounds__(ROWS_THREADS, 1) k_gather_rows(const GatherP p) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_warp[ROWS_WARPS];
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     constexpr int NM = GATED ? 2 : 1;
-    constexpr int U = WT == PI_TYPE_F16 ? 8 / NM * 1 : 8;            // 128-bit loads per matrix a lane issues before it consumes
     const size_t x_bytes = WT == PI_TYPE_F16 ? (size_t)p.ncols * 2 : (size_t)p.nb * 40;
     unsigned char * xs = smem;
     uint32_t * s_mask = reinterpret_cast<uint32_t *>(smem + ((x_bytes + 127) & ~(size_t)127));
@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_gather_rows(const GatherP p
         }
     }
     const int n = scan_masks_finish(mw, p.n_chunks, s_mask, s_pref, s_warp);
+    if (p.rows_total && blockIdx.x == 0 && tid == 0 && n) atomicAdd(p.rows_total, (unsigned long long)n);    // statistics
     PI_TL_MARK(0);
 
     const int TW = gridDim.x * ROWS_WARPS, gw = blockIdx.x * ROWS_WARPS + wid;
@@ -159,6 +160,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_gather_rows(const GatherP p
         // lane l looks up the row of this warp's (base + l)-th rank; ranks grow with l, so the valid lanes are a prefix
         const long long rank = gw + (long long)(base + lane) * TW;
         const int my_row = rank < n ? row_of_rank((int)rank, p.n_chunks, s_mask, s_pref) : -1;
+        if (base == 0) PI_TL_MARK(4);
         const int cnt = __popc(__ballot_sync(0xffffffffu, my_row >= 0));
         if (base == 0) PI_TL_MARK(1);
         for (int u0 = 0; u0 < cnt; u0++) {
@@ -212,6 +214,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_gather_rows(const GatherP p
             }
             acc = warp_sum(acc);
             if (GATED) acc2 = warp_sum(acc2);
+            if (base == 0 && u0 == 0) PI_TL_MARK(2);
             if (lane == 0) {
                 const int64_t g = p.bucket ? p.bucket[r] : r;
                 float o = acc;                                       // one token: a row named by the mask is an active row
@@ -229,18 +232,27 @@ static size_t gather_smem(int wtype, int64_t ncols, int n_chunks) {
     return ((x_bytes + 127) & ~size_t(127)) + (size_t)(2 * n_chunks + 1) * 4 + 128;
 }
 
-template <int WT, bool GATED>
-static int launch_gather_inst(const GatherP & p, size_t smem, bool pdl, cudaStream_t st) {
+template <int WT, bool GATED, int U>
+static int launch_gather_u(const GatherP & p, size_t smem, bool pdl, cudaStream_t st) {
     static bool attr_done[16] = {false};
     int dev = 0;
     PI_CUDA(cudaGetDevice(&dev));
-    auto kern = k_gather_rows<WT, GATED>;
+    auto kern = k_gather_rows<WT, GATED, U>;
     if (dev >= 0 && dev < 16 && !attr_done[dev]) {
         PI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         attr_done[dev] = true;
     }
     PI_CUDA(launch_k(kern, dim3(sm_count()), dim3(ROWS_THREADS), smem, st, pdl, p));
     return PI_OK;
+}
+
+template <int WT, bool GATED>
+static int launch_gather_inst(const GatherP & p, size_t smem, bool pdl, cudaStream_t st) {
+    if (WT == PI_TYPE_F16) return launch_gather_u<WT, GATED, 8>(p, smem, pdl, st);
+    // Q4_0: 9 loads per lane where that saves a round trip per row (rows of 257..288 blocks: d_model 8192 + its scales)
+    const int units = p.nb;
+    if ((units + 287) / 288 < (units + 255) / 256) return launch_gather_u<WT, GATED, 9>(p, smem, pdl, st);
+    return launch_gather_u<WT, GATED, 8>(p, smem, pdl, st);
 }
 
 static void axpy_rows_shape(int64_t nrows, int64_t ncols, int * n_slices, int * n_rg, int * max_rows);
@@ -267,6 +279,7 @@ int launch_gather_rows(const GemvArgs & a, cudaStream_t st) {
     p.W = (const uint8_t *)a.W; p.W2 = (const uint8_t *)a.W2; p.row_bytes = (int64_t)pi_row_bytes(a.wtype, a.ncols);
     p.nrows = (int)a.nrows; p.ncols = (int)a.ncols; p.nb = (int)(a.ncols / QK); p.n_chunks = (int)((a.nrows + 31) / 32);
     p.x = a.x; p.masks = a.masks; p.bucket = a.bucket; p.bias = a.bias; p.relu = a.relu; p.dst = a.dst;
+    p.rows_total = a.rows_total;
     const size_t smem = gather_smem(a.wtype, a.ncols, p.n_chunks);
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
     if (a.W2) return q4 ? launch_gather_inst<PI_TYPE_Q4_0, true>(p, smem, a.pdl, st) : launch_gather_inst<PI_TYPE_F16, true>(p, smem, a.pdl, st);
@@ -276,7 +289,7 @@ int launch_gather_rows(const GemvArgs & a, cudaStream_t st) {
 // ---------------------------------------------------------------------------------------------- axpy
 struct AxpyRowsP {
     const uint8_t * Wt; int64_t row_bytes; int nrows; int ncols; int nb; int n_chunks;
-    const float * h; const uint32_t * masks; const int32_t * bucket;
+    const float * h; const uint32_t * masks; const int32_t * bucket; int h_uncleared;
     float * partial; int n_slices; int n_rg; int max_rows;
 };
 
@@ -319,6 +332,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_axpy_rows(const AxpyRowsP p
         int r = -1; float c = 0.f;
         if (t < n_mine) {
             r = row_of_rank(rg + t * p.n_rg, p.n_chunks, s_mask, s_pref);
+            if (t0 == 0) PI_TL_MARK(4);
             const int64_t g = p.bucket ? p.bucket[r] : r;
             if (WT == PI_TYPE_F16) {
                 c = round_f16(__ldcg(p.h + g));
@@ -327,6 +341,16 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_axpy_rows(const AxpyRowsP p
                 float4 v[8];
 #pragma unroll
                 for (int k = 0; k < 8; k++) v[k] = __ldcg(hb + k);
+                if (p.h_uncleared) {                                // nobody cleared h where a row is inactive: those entries count as 0
+                    const uint32_t mk = s_mask[r >> 5];
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        if (!(mk >> (4 * k) & 1u))     v[k].x = 0.f;
+                        if (!(mk >> (4 * k + 1) & 1u)) v[k].y = 0.f;
+                        if (!(mk >> (4 * k + 2) & 1u)) v[k].z = 0.f;
+                        if (!(mk >> (4 * k + 3) & 1u)) v[k].w = 0.f;
+                    }
+                }
                 float amax = 0.f;
 #pragma unroll
                 for (int k = 0; k < 8; k++) amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[k].x), fabsf(v[k].y)), fmaxf(fabsf(v[k].z), fabsf(v[k].w))));
@@ -336,6 +360,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1) k_axpy_rows(const AxpyRowsP p
             }
         }
         // keep the order: ballot inside the warp, warp offsets through shared memory
+        if (t0 == 0) PI_TL_MARK(5);
         const bool keep = r >= 0 && c != 0.f;
         const unsigned bal = __ballot_sync(0xffffffffu, keep);
         if (lane == 0) s_warp[wid] = __popc(bal);
@@ -486,12 +511,13 @@ static int launch_axpy_rows_inst(const AxpyRowsP & p, size_t smem, bool pdl, cud
 
 int launch_axpy_rows(const AxpyArgs & a, cudaStream_t st, int * groups_used) {
     if (a.T != 1 || !a.masks || !rows_eligible(a.wtype, a.nrows, a.ncols)) return PI_ERR_UNSUPPORTED;
+    if (a.h_uncleared && a.bucket) return PI_ERR_UNSUPPORTED;          // the masks are by local row, h by global id
     AxpyRowsP p;
     axpy_rows_shape(a.nrows, a.ncols, &p.n_slices, &p.n_rg, &p.max_rows);
     if (p.max_rows > AXPY_MAX_CTA_ROWS || p.n_rg > a.n_groups) return PI_ERR_UNSUPPORTED;
     p.Wt = (const uint8_t *)a.Wt; p.row_bytes = (int64_t)pi_row_bytes(a.wtype, a.ncols); p.nrows = (int)a.nrows;
     p.ncols = (int)a.ncols; p.nb = (int)(a.ncols / QK); p.n_chunks = (int)((a.nrows + 31) / 32);
-    p.h = a.h; p.masks = a.masks; p.bucket = a.bucket; p.partial = a.partial;
+    p.h = a.h; p.masks = a.masks; p.bucket = a.bucket; p.h_uncleared = a.h_uncleared ? 1 : 0; p.partial = a.partial;
     const size_t smem = axpy_rows_smem(p.n_chunks, p.max_rows);
     if (smem > 160 * 1024) return PI_ERR_UNSUPPORTED;
     if (groups_used) *groups_used = p.n_rg;

@@ -42,9 +42,7 @@ class ModelWeights(C.Structure):
 
 class Exchange(C.Structure):
     _fields_ = [("n_ranks", C.c_int), ("rank_id", C.c_int), ("slot_floats", C.c_int64),
-                ("mailbox_local", _vp), ("flags_local", _vp),
-                ("mailbox_peer", _vp * PI_MAX_RANKS), ("flags_peer", _vp * PI_MAX_RANKS),
-                ("epoch", _vp), ("ticket", _vp), ("flag_words", C.c_int)]
+                ("mailbox_local", _vp), ("mailbox_peer", _vp * PI_MAX_RANKS), ("epoch", _vp)]
 
 
 for _name, _res, _args in [
@@ -270,14 +268,15 @@ class DecodeEngine:
                 _wrap_device(lst.value, F, torch.int32)[:n].cpu().numpy())
 
     # ---- sharded runs: mailboxes in every rank's memory, addresses exchanged through the process group
+    def _exchange_sizes(self):
+        slot = self.max_batch * self.spec.d
+        mbox_bytes = 2 * self.n_ranks * slot * 8          # pairs {value, number of the exchange}
+        return slot, mbox_bytes, mbox_bytes + 256         # + the step counter
+
     def setup_exchange(self, group=None):
         import torch.distributed as dist
         assert self.n_ranks > 1
-        slot = self.max_batch * self.spec.d
-        mbox_bytes = 2 * self.n_ranks * slot * 4
-        flag_words = 8 * self.max_batch
-        flag_bytes = (2 * self.n_ranks * flag_words * 4 + 255) // 256 * 256
-        total = mbox_bytes + 2 * flag_bytes
+        slot, mbox_bytes, total = self._exchange_sizes()
         base = _vp()
         check(lib.pi_device_malloc(C.byref(base), total))
         handle = (C.c_char * 64)()
@@ -286,7 +285,7 @@ class DecodeEngine:
         allh = [torch.empty_like(mine) for _ in range(self.n_ranks)]
         dist.all_gather(allh, mine, group=group)
         x = Exchange()
-        x.n_ranks, x.rank_id, x.slot_floats, x.flag_words = self.n_ranks, self.rank, slot, flag_words
+        x.n_ranks, x.rank_id, x.slot_floats = self.n_ranks, self.rank, slot
         self._peer_ptrs = []
         for r in range(self.n_ranks):
             if r == self.rank:
@@ -298,50 +297,41 @@ class DecodeEngine:
                 p = pp.value
                 self._peer_ptrs.append(p)
             x.mailbox_peer[r] = p
-            x.flags_peer[r] = p + mbox_bytes
         x.mailbox_local = base.value
-        x.flags_local = base.value + mbox_bytes
-        x.epoch = base.value + mbox_bytes + flag_bytes
-        x.ticket = base.value + mbox_bytes + flag_bytes + 64
+        x.epoch = base.value + mbox_bytes
         self._xch_mem = base
         self.xch = x
         check(lib.pi_engine_set_exchange(self.handle, C.byref(x)))
         dist.barrier(group=group)
 
     def setup_exchange_loopback(self):
-        """A sharded engine alone on one GPU (tests of the bounded waits): this rank's pushes to the other ranks land in a
-        spare buffer nobody reads, and the other ranks' flags in this rank's mailbox are raised by nobody, so every
-        exchange wait runs out, unless `raise_peer_flags` is called."""
+        """A sharded engine alone on one GPU (tests of the bounded waits): this rank's shares for the other ranks land in a
+        spare buffer nobody reads, and nobody writes the other ranks' shares into this rank's mailbox, so every exchange
+        wait runs out, unless `fill_peer_shares` is called."""
         assert self.n_ranks > 1
-        slot = self.max_batch * self.spec.d
-        mbox_bytes = 2 * self.n_ranks * slot * 4
-        flag_words = 8 * self.max_batch
-        flag_bytes = (2 * self.n_ranks * flag_words * 4 + 255) // 256 * 256
-        total = mbox_bytes + 2 * flag_bytes
+        slot, mbox_bytes, total = self._exchange_sizes()
         base, spare = _vp(), _vp()
         check(lib.pi_device_malloc(C.byref(base), total))
         check(lib.pi_device_malloc(C.byref(spare), total))
         x = Exchange()
-        x.n_ranks, x.rank_id, x.slot_floats, x.flag_words = self.n_ranks, self.rank, slot, flag_words
+        x.n_ranks, x.rank_id, x.slot_floats = self.n_ranks, self.rank, slot
         for r in range(self.n_ranks):
-            p = base.value if r == self.rank else spare.value
-            x.mailbox_peer[r] = p
-            x.flags_peer[r] = p + mbox_bytes
+            x.mailbox_peer[r] = base.value if r == self.rank else spare.value
         x.mailbox_local = base.value
-        x.flags_local = base.value + mbox_bytes
-        x.epoch = base.value + mbox_bytes + flag_bytes
-        x.ticket = base.value + mbox_bytes + flag_bytes + 64
+        x.epoch = base.value + mbox_bytes
         self._xch_mem, self._xch_spare, self._peer_ptrs = base, spare, []
-        self._flags_view = _wrap_device(base.value + mbox_bytes, 2 * self.n_ranks * flag_words, torch.int32)
+        self._mbox_view = _wrap_device(base.value, 2 * self.n_ranks * slot * 2, torch.int32)
         self.xch = x
         check(lib.pi_engine_set_exchange(self.handle, C.byref(x)))
 
-    def raise_peer_flags(self):
-        """Loopback only: mark every other rank's flags as delivered for all future exchanges (their slots hold zeros)."""
-        fl = self._flags_view.view(2, self.n_ranks, -1)
+    def fill_peer_shares(self):
+        """Loopback only: make every other rank's share read as delivered for all future exchanges (value 0.0 beside a
+        number larger than any exchange's)."""
+        mb = self._mbox_view.view(2, self.n_ranks, -1, 2)
         for r in range(self.n_ranks):
             if r != self.rank:
-                fl[:, r, :] = 0x3fffffff
+                mb[:, r, :, 0] = 0
+                mb[:, r, :, 1] = 0x3fffffff
         torch.cuda.synchronize()
 
     def set_wait_cycles(self, cycles: int):

@@ -1,5 +1,9 @@
 """Sharded decode on 2 and 4 GPUs (neuron + head sharding, mailbox exchange over NVLink) against the CPU checker.
 
+Every step of every case is checked: the checker is driven with the predictor logits the ranks computed (gathered over
+the ranks) for its masks, so both sides work on identical active sets, and still computes its own predictor logits, which
+must agree with the ranks' to rounding; the logits are then held to the stated bars (2e-2 for FP16 weights, 5e-2 for Q4_0).
+
 Needs two (four) devices; skipped otherwise.  Ranks are child processes with NCCL's NVLS switched off (the process group only
 hands IPC handles around and keeps the ranks in step); the exchange itself uses plain peer stores and bounded waits.
 """
@@ -43,26 +47,25 @@ def _worker(rank, world, port, name, out_dir):
     from oracle import pio
     from powerinfer_b200 import engine
     spec = SPECS[name]
+    bar = 5e-2 if spec.wtype == synth.Q4_0 else 2e-2
     t = synth.build_model(spec)
     eng = engine.DecodeEngine(spec, t, max_batch=2, n_ranks=world, rank=rank)
     eng.setup_exchange()
     eng.enable_trace()
     om = pio.OracleModel(spec, t)
-    worst, n_flip_steps, cur = 0.0, 0, 9
-    F = spec.n_ff // world
+    worst, worst_pred, cur = 0.0, 0.0, 9
     for pos in range(12):
         logits, amax = eng.decode([cur], [pos])
-        ref, pred = om.decode(cur, pos, want_pred=True)
-        got = eng.predictor_trace(1)[:, 0]                      # this rank's neurons
-        ref_local = pred[:, rank * F:(rank + 1) * F]
-        flips = (got >= 0) != (ref_local >= 0)
-        assert np.all(np.abs(ref_local[flips]) <= 1e-3)
-        nf = torch.tensor([int(flips.sum())], device="cuda")
-        dist.all_reduce(nf)
-        if int(nf.item()) == 0:
-            worst = max(worst, float(np.abs(logits[0] - ref).max()))
-        else:
-            n_flip_steps += 1
+        got = torch.from_numpy(np.ascontiguousarray(eng.predictor_trace(1)[:, 0])).cuda()      # this rank's neurons [n_layer, F / world]
+        parts = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(parts, got)
+        full = torch.cat(parts, dim=1).cpu().numpy()                                            # ranks own contiguous neuron ranges
+        ref, pred = om.decode_imposed(cur, pos, full)
+        worst_pred = max(worst_pred, float(np.abs(full - pred).max()))
+        worst = max(worst, float(np.abs(logits[0] - ref).max()))
+        srt = np.sort(ref)[::-1]
+        if srt[0] - srt[1] > 2 * bar:
+            assert int(amax[0]) == int(ref.argmax()), pos
         cur = int(ref.argmax())
     eng.status()
     # a batch of two sequences through the sharded engine equals two single runs of it
@@ -71,7 +74,7 @@ def _worker(rank, world, port, name, out_dir):
     eng.k_cache.zero_(); eng.v_cache.zero_(); torch.cuda.synchronize(); dist.barrier()
     eng.decode([11, 40], [0, 0])
     b = eng.decode([12, 41], [1, 1])[0][0].copy()
-    np.save(os.path.join(out_dir, f"{name}_r{rank}.npy"), np.array([worst, n_flip_steps, float(np.abs(a[1] - b).max())]))
+    np.save(os.path.join(out_dir, f"{name}_r{rank}.npy"), np.array([worst, worst_pred, float(np.abs(a[1] - b).max()), bar]))
     all_logits = [torch.empty(spec.n_vocab, device="cuda") for _ in range(world)]
     dist.all_gather(all_logits, torch.from_numpy(b).cuda())
     assert all(torch.equal(all_logits[0], x) for x in all_logits)   # every rank holds the same logits, bit for bit
@@ -87,10 +90,12 @@ def _run(tmp_path, name, world):
     import torch.multiprocessing as mp
     mp.spawn(_worker, args=(world, _free_port(), name, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
-        worst, n_flip_steps, batch_err = np.load(tmp_path / f"{name}_r{r}.npy")
-        assert worst <= 5e-3, worst
-        assert n_flip_steps <= 3          # steps where a borderline neuron (within 1e-3 of the threshold) came out differently
-        assert batch_err <= 1e-3
+        worst, worst_pred, batch_err, bar = np.load(tmp_path / f"{name}_r{r}.npy")
+        print(f"{name} x{world} rank {r}: max |logit error| {worst:.2e} (bar {bar}), max |predictor logit difference| {worst_pred:.2e}, "
+              f"batch of two against single sequences {batch_err:.2e}")
+        assert worst <= bar, worst
+        assert worst_pred <= 5e-3, worst_pred
+        assert batch_err <= (bar if bar > 2e-2 else 1e-3)     # Q4_0: the batched kernels add in another order, then Q8_0 roundings differ
 
 
 @pytest.mark.parametrize("name", sorted(SPECS))

@@ -1,7 +1,7 @@
 """A bounded device-side wait that runs out, on one GPU and without any fault: a sharded engine (rank 0 of 2) is given
-a loopback exchange in which the other rank's flags are never raised.  Every exchange wait then reaches its (shortened)
-bound, the kernels carry on, the step finishes, and the host reads PI_ERR_TIMEOUT from the status word.  After the flags
-are raised from the host the same engine runs clean steps again: the context was never lost."""
+a loopback exchange in which the other rank's share never arrives.  Every exchange wait then reaches its (shortened)
+bound, the kernels carry on, the step finishes, and the host reads PI_ERR_TIMEOUT from the status word.  After the shares
+are filled in from the host the same engine runs clean steps again: the context was never lost."""
 import numpy as np
 import pytest
 
@@ -27,7 +27,7 @@ def test_exchange_wait_runs_out_and_the_engine_stays_usable():
         assert rc == 5, (step, rc, lib.pi_last_error())        # PI_ERR_TIMEOUT
         assert b"exchange" in lib.pi_last_error()
     assert lib.pi_engine_status(eng.handle, eng.st) == 0       # reported once, then cleared
-    eng.raise_peer_flags()
+    eng.fill_peer_shares()
     logits, amax = eng.decode([7], [3])
     eng.status()                                               # clean
     assert np.isfinite(logits).all() and int(amax[0]) == int(logits[0].argmax())
