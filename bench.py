@@ -510,7 +510,7 @@ def main():
     active = eng.active_total() / (n_prof * spec.n_layer) * world     # mean active neurons per layer (all ranks)
     # ---- per-kernel durations: each stage's kernels for all layers, back to back (overlapped as inside the step)
     b2b = {}
-    for st in ("qkv", "out_proj", "predictor", "up_gate", "down", "lm_head", "norm", "attention", "compact"):
+    for st in ("qkv", "out_proj", "predictor", "up_gate", "down", "sparse_ffn", "lm_head", "norm", "attention", "compact"):
         ms_launch, n_launch = eng.time_stage(T, st)     # the norms of a sharded run carry the exchange (all ranks replay them together)
         if n_launch > 0:
             b2b[st] = (ms_launch * 1e3, n_launch)
@@ -536,7 +536,7 @@ def main():
         peak, peak_kind = measured_peaks()
         bytes_tok = C2.bytes_per_token(spec, active)
         ops = {}
-        for st in ("qkv", "out_proj", "predictor", "up_gate", "down", "lm_head"):
+        for st in ("qkv", "out_proj", "predictor", "up_gate", "down", "sparse_ffn", "lm_head"):
             if stage_ms.get(st, 0.0) <= 0 or st not in b2b:
                 continue
             us_launch, n_launch = b2b[st]
@@ -548,7 +548,8 @@ def main():
         dom = max(ops, key=lambda k: ops[k]["ms_per_step"])
         roofline = {"bound": "hbm", "kernel": {"qkv": "k_gemv_ring_w (dense, QKV rows)", "out_proj": "k_gemv_ring_w (dense, out-proj)",
                                                "predictor": "k_gemv_ring_g + k_gemv_ring_w (dense F16, fc1 + fc2)", "up_gate": "k_gather_rows (gather, up+gate)",
-                                               "down": "k_axpy_rows", "lm_head": "k_gemv_ring_w (dense, lm head)"}[dom],
+                                               "down": "k_axpy_rows",
+                                               "sparse_ffn": "k_ffn_rows (gather over up + gate rows, activation, axpy over down rows: one launch)", "lm_head": "k_gemv_ring_w (dense, lm head)"}[dom],
                     "achieved": ops[dom]["GBps"], "peak": peak, "unit": "GB/s", "frac": round(ops[dom]["GBps"] / peak, 3),
                     "peak_source": f"of {peak_kind}", "launches_per_step": ops[dom]["launches_per_step"],
                     "bytes_per_launch": bytes_tok[dom] / world / ops[dom]["launches_per_step"],

@@ -282,7 +282,8 @@ int  pi_engine_prefill_host(pi_engine * e, const int32_t * host_tokens, int n_to
 #define PI_STAGE_LM_HEAD   8
 #define PI_STAGE_EXCHANGE  9
 #define PI_STAGE_OTHER    10
-#define PI_N_STAGES       11
+#define PI_STAGE_FFN      11     /* up/gate, activation and down in one launch (one token, where the shape allows it) */
+#define PI_N_STAGES       12
 int  pi_engine_profile_step(pi_engine * e, int T, float * host_ms, int * host_launches, void * stream);
 /* Measurement helper: the kernels of ONE stage for every layer, back to back in a CUDA graph exactly as they are launched
  * inside a step (programmatic dependent launch included), `reps` replays between two events.  host_ms_per_rep = time of

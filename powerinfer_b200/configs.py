@@ -37,4 +37,5 @@ def bytes_per_token(spec: synth.ModelSpec, active_per_layer: float) -> dict:
         "lm_head": spec.n_vocab * (rb(d) if spec.arch != synth.ARCH_OPT else 2 * d),
     }
     out["total"] = sum(out.values())
+    out["sparse_ffn"] = out["up_gate"] + out["down"]        # the same bytes when one kernel does both (not added to the total twice)
     return out

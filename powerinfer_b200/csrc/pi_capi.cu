@@ -263,6 +263,23 @@ int pi_sparse_ffn(int wtype, const void * up, const void * gate, const void * do
     if (bucket || T > 1 || wtype == PI_TYPE_Q4_0) PI_CUDA(cudaMemsetAsync(h, 0, (size_t)T * F * 4, st));
     if ((rc = launch_convert_act(wtype, x, ncols, ncols, T, act, st))) return rc;
     // the kernels below are chained with programmatic dependent launch: each may start while its predecessor drains
+    {
+        // one token, every row on this device, no bias that inactive rows would keep: masks, then the whole FFN in one launch
+        FfnRowsArgs f;
+        f.pdl = true;
+        f.wtype = wtype; f.up = up; f.gate = gate; f.down_t = down_t; f.nrows = n_w_rows; f.ncols = ncols;
+        f.x = act.view(); f.masks = ss.masks; f.bias = up_bias; f.relu = gate ? 0 : 1;
+        f.h = h; f.partial = partial; f.n_groups = G;
+        if (T == 1 && !bucket && !(wtype == PI_TYPE_Q4_0 && up_bias) && ffn_rows_eligible(f)) {
+            CompactArgs cm;
+            cm.pdl = true;
+            cm.idx = idx; cm.idx_stride = idx_stride; cm.T = 1; cm.threshold = threshold; cm.n_local = n_w_rows; cm.masks = ss.masks;
+            if ((rc = launch_compact(cm, st))) return rc;
+            int used1 = G;
+            if ((rc = launch_ffn_rows(f, st, &used1))) return rc;
+            return launch_reduce_partials(partial, used1, 1, ncols, nullptr, nullptr, dst, st, true);
+        }
+    }
     CompactArgs c;
     c.pdl = true;
     c.idx = idx; c.idx_stride = idx_stride; c.T = T; c.threshold = threshold; c.n_local = n_w_rows; c.bucket = bucket;

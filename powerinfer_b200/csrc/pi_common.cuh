@@ -114,6 +114,7 @@ struct GemvArgs {
     // dense, one token: also write the activity bit masks of the result, bit (row % 32) of word (row / 32) = !(result <
     // masks_threshold): the predictor's mask, made where the logit is.  Room for (nrows + 63) / 64 * 2 words.
     uint32_t * masks_out = nullptr; float masks_threshold = 0.f;
+    int pre_stages = -1;               // ring kernels: stages of weights requested before the dependency wait (-1: the whole ring)
     unsigned int * status = nullptr;   // device status word; when given, T == 1 shapes use the bulk-copy ring kernel
     bool pdl = false;                  // launch with programmatic dependent launch (the kernel waits for its producer itself)
 };
@@ -166,6 +167,21 @@ bool rows_eligible(int wtype, int64_t nrows, int64_t ncols);
 int launch_gather_rows(const GemvArgs & a, cudaStream_t st);
 int launch_axpy_rows(const AxpyArgs & a, cudaStream_t st, int * groups_used);
 int axpy_rows_groups(int64_t nrows, int64_t ncols);                                  // partial vectors launch_axpy_rows writes
+// one token, the whole sparse FFN in one launch (pi_ffn_rows.cu): h = act(up/gate rows . x) over the rows the masks name,
+// partial[c] = sum of the rows of down_t times their coefficients, one partial vector per cluster (groups_used of them, at
+// most n_groups).  h (optional) receives the activations by row.  PI_ERR_UNSUPPORTED: not eligible (use the two kernels).
+struct FfnRowsArgs {
+    int wtype = PI_TYPE_F16;
+    const void * up = nullptr; const void * gate = nullptr; const void * down_t = nullptr;   // [nrows, ncols] each
+    int64_t nrows = 0, ncols = 0;
+    Act x; const uint32_t * masks = nullptr;
+    const float * bias = nullptr; int relu = 0;
+    float * h = nullptr; float * partial = nullptr; int n_groups = 0;
+    unsigned long long * rows_total = nullptr;
+    bool pdl = false;
+};
+int launch_ffn_rows(const FfnRowsArgs & a, cudaStream_t st, int * groups_used);
+bool ffn_rows_eligible(const FfnRowsArgs & a);      // up / gate / down_t (null or not), shape and n_groups as they will be passed
 // h F32 [T, stride] -> Q8_0 over 32-neuron blocks: cq int8 [T, stride], cd float [T, stride/32]
 int launch_neuron_q8(const float * h, int64_t stride, int64_t n, int T, int8_t * cq, float * cd, cudaStream_t st);
 

@@ -291,6 +291,7 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
     } else {
         add8(*reinterpret_cast<const float4 *>(p.x + o), *reinterpret_cast<const float4 *>(p.x + o + 4));
     }
+    PI_TL_MARK(0);
     if (p.x_ranks > 1) {
         // ---- exchange: v is this rank's share.  Every value travels as an 8-byte pair {value, number of this exchange}
         //      (two pairs per 16-byte store), written into every other rank's mailbox with plain stores.  A pair arrives
@@ -372,6 +373,7 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
         *reinterpret_cast<float4 *>(p.x_out + o + 4) = make_float4(v[4], v[5], v[6], v[7]);
     }
     if (p.act2_type && p.act2_src == 0) emit_act8(p.act2_type, p.act2, t, n, (int)(c / 8), v, true);
+    PI_TL_MARK(1);
 
     auto cluster_total = [&](double mine, int slot) {               // every CTA gets the sum over the cluster, ranks in order
         mine = block_sum_d(mine, s_red);
@@ -399,6 +401,7 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
         const float var = (float)(cluster_total(s2, 1) / (double)n);
         scale = 1.0f / sqrtf(var + p.eps);
     }
+    PI_TL_MARK(2);
     float y[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) {
@@ -414,7 +417,9 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
     }
     if (p.act_type) emit_act8(p.act_type, p.act, t, n, (int)(c / 8), y, true);
     if (p.act2_type && p.act2_src == 1) emit_act8(p.act2_type, p.act2, t, n, (int)(c / 8), y, true);
+    PI_TL_MARK(3);
     cluster_sync();                                                  // nobody leaves while a peer may still read its partial sums
+    PI_TL_MARK(4);
 }
 
 // One CTA per SM, every thread issues bulk L2 prefetches for its pieces: no shared memory and few registers, so the

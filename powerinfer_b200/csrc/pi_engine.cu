@@ -123,6 +123,7 @@ struct pi_engine {
     float * pred_trace;                      // optional [n_layer, max_batch, F]: keeps every layer's predictor logits
     bool pdl;                                // programmatic dependent launch between the kernels of a step
     bool gate_sym;                           // bamboo: relu on the gated product as well
+    int qkv_pre;                             // ring stages the QKV mat-vec requests before its dependency wait after a norm that collects vectors (-1: all)
     bool fc2_masks;                          // ... with the activity masks written by the predictor's second mat-vec itself (no mask kernel)
     bool rows1;                              // one token: masks-only compaction + register-streaming sparse kernels (shape eligible)
     long long wait_cycles;                   // bound of the exchange waits (0: about a second)
@@ -244,6 +245,7 @@ int pi_engine_create(const pi_engine_config * cfg, const pi_model_weights * gw, 
     { const char * v = getenv("PI_PDL"); e->pdl = !(v && v[0] == '0'); }
     e->skip_mask = 0u; e->wait_cycles = 0;
     e->rows1 = rows_eligible(cfg->wtype, e->F, cfg->d) && axpy_rows_groups(e->F, cfg->d) <= e->G;
+    { const char * v = getenv("PI_QKV_PRE"); e->qkv_pre = v ? atoi(v) : 0; }
     { const char * v = getenv("PI_FC2_MASKS"); e->fc2_masks = !(v && v[0] == '0'); }     // 0: the separate mask kernel (diagnostic)
     cudaStream_t st = (cudaStream_t)stream;
     // one-time device state: sequence ids 0..T-1, zeroed ticket / status, RoPE angle table
@@ -401,6 +403,7 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm, int mod
         n1.T = T; n1.n = d; n1.rms = rms; n1.eps = c.norm_eps;
         n1.w = last ? e->g.out_norm_w : L->attn_norm_w;
         n1.b = last ? e->g.out_norm_b : L->attn_norm_b;
+        const bool n1_collects = pend.partial != nullptr || pend.exchange;     // partial vectors (or the ranks' shares) to read first
         if (pend.any()) norm_inputs(e, pend, n1, &xch_index, xch_per_step); else n1.x = e->x;
         if (last && mode == 2) break;
         if (last) {
@@ -447,6 +450,10 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm, int mod
             g.status = e->status; g.pdl = pdl;
             g.wtype = wt; g.W = L->wqkv; g.nrows = qkv_rows; g.ncols = d; g.x = qkv_in.view(); g.T = T;
             g.bias = L->bqkv; g.dst = e->qkv; g.dst_stride = qkv_rows;
+            // A ring kernel requests its first stages of weights (tens of MB over all SMs) the moment it becomes resident, i.e.
+            // while the norm before it is still reading the partial vectors; those reads then queue behind the burst
+            // (measured: 5 us for 0.5 MB).  After such a norm the QKV mat-vec starts its ring only when its wait is over.
+            g.pre_stages = n1_collects ? e->qkv_pre : -1;
             STAGE(PI_STAGE_QKV, (T + 7) / 8, launch_gemv(g, st));
         }
         {
@@ -523,27 +530,37 @@ int enqueue_step(pi_engine * e, int T, cudaStream_t st, StageTimer & tm, int mod
             STAGE(PI_STAGE_COMPACT, 1, launch_compact(ca, st));
         }
         int used = e->G;
-        // ---- up (and gate) over the active rows: h = relu(gate.x) * (up.x) | relu(up.x + b)
-        {
-            GemvArgs g;
-            g.status = e->status; g.pdl = pdl;
-            g.wtype = wt; g.W = L->up; g.W2 = L->gate; g.nrows = F; g.ncols = d; g.x = e->act_a.view(); g.T = T;
-            if (rows1) { g.masks = e->masks; if (masks1) g.rows_total = e->active_total; } else { g.list = e->list; g.count = e->count; }
-            g.idx = pred; g.idx_stride = F; g.threshold = c.threshold;
-            g.bias = L->up_b; g.relu = L->gate ? (e->gate_sym ? 1 : 0) : 1;
-            g.dst = e->h; g.dst_stride = F;
-            STAGE(PI_STAGE_UPGATE, (T + 7) / 8, launch_gemv(g, st));
-        }
-        // ---- down: axpy over the same rows; the sum over row groups (and, sharded, over ranks) is left to the next norm
-        if (wt == PI_TYPE_Q4_0 && T > 1) STAGE(PI_STAGE_DOWN, 1, launch_neuron_q8(e->h, F, F, T, e->cq, e->cd, st));
-        {
-            AxpyArgs a;
-            a.pdl = pdl;
-            a.wtype = wt; a.Wt = L->down_t; a.nrows = F; a.ncols = d; a.h = e->h; a.h_stride = F; a.T = T;
-            if (rows1) { a.masks = e->masks; a.h_uncleared = masks1; } else { a.list = e->list; a.count = e->count; }
-            a.idx = pred; a.idx_stride = F; a.threshold = c.threshold;
-            a.cq = e->cq; a.cd = e->cd; a.c_stride = F; a.partial = e->partial; a.n_groups = e->G; a.status = e->status;
-            STAGE(PI_STAGE_DOWN, T == 1 ? 1 : (wt == PI_TYPE_Q4_0 ? (T + 1) / 2 : (T + 3) / 4), launch_axpy(a, st, &used));
+        // ---- one token with masks from the predictor: the whole sparse FFN in one launch where the shape allows it
+        FfnRowsArgs f;
+        f.pdl = pdl;
+        f.wtype = wt; f.up = L->up; f.gate = L->gate; f.down_t = L->down_t; f.nrows = F; f.ncols = d;
+        f.x = e->act_a.view(); f.masks = e->masks; f.bias = L->up_b; f.relu = L->gate ? (e->gate_sym ? 1 : 0) : 1;
+        f.h = e->h; f.partial = e->partial; f.n_groups = e->G < NORM_MAX_GROUPS ? e->G : NORM_MAX_GROUPS; f.rows_total = e->active_total;
+        if (masks1 && ffn_rows_eligible(f)) {                          // (the plan is cached: a table look-up after the first call)
+            STAGE(PI_STAGE_FFN, 1, launch_ffn_rows(f, st, &used));
+        } else {
+            // ---- up (and gate) over the active rows: h = relu(gate.x) * (up.x) | relu(up.x + b)
+            {
+                GemvArgs g;
+                g.status = e->status; g.pdl = pdl;
+                g.wtype = wt; g.W = L->up; g.W2 = L->gate; g.nrows = F; g.ncols = d; g.x = e->act_a.view(); g.T = T;
+                if (rows1) { g.masks = e->masks; if (masks1) g.rows_total = e->active_total; } else { g.list = e->list; g.count = e->count; }
+                g.idx = pred; g.idx_stride = F; g.threshold = c.threshold;
+                g.bias = L->up_b; g.relu = L->gate ? (e->gate_sym ? 1 : 0) : 1;
+                g.dst = e->h; g.dst_stride = F;
+                STAGE(PI_STAGE_UPGATE, (T + 7) / 8, launch_gemv(g, st));
+            }
+            // ---- down: axpy over the same rows; the sum over row groups (and, sharded, over ranks) is left to the next norm
+            if (wt == PI_TYPE_Q4_0 && T > 1) STAGE(PI_STAGE_DOWN, 1, launch_neuron_q8(e->h, F, F, T, e->cq, e->cd, st));
+            {
+                AxpyArgs a;
+                a.pdl = pdl;
+                a.wtype = wt; a.Wt = L->down_t; a.nrows = F; a.ncols = d; a.h = e->h; a.h_stride = F; a.T = T;
+                if (rows1) { a.masks = e->masks; a.h_uncleared = masks1; } else { a.list = e->list; a.count = e->count; }
+                a.idx = pred; a.idx_stride = F; a.threshold = c.threshold;
+                a.cq = e->cq; a.cd = e->cd; a.c_stride = F; a.partial = e->partial; a.n_groups = e->G; a.status = e->status;
+                STAGE(PI_STAGE_DOWN, T == 1 ? 1 : (wt == PI_TYPE_Q4_0 ? (T + 1) / 2 : (T + 3) / 4), launch_axpy(a, st, &used));
+            }
         }
         pend = Pending();
         pend.bias = L->down_b;

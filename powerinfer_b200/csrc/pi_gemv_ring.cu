@@ -31,6 +31,7 @@ struct RingP {
     const float * bias; int relu;
     float * dst; __half * dst16;
     uint32_t * masks_out; float masks_threshold;
+    int pre;
     unsigned int * status;
     int R, split, stages, max_items; size_t stage_bytes;
 };
@@ -308,8 +309,10 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_w(const RingP p) {
         mbar_expect_tx(full + s, (unsigned)(n * p.row_bytes));
         bulk_g2s(ring + (size_t)s * p.stage_bytes, p.W + (size_t)first * p.row_bytes, (unsigned)(n * p.row_bytes), full + s);
     };
-    if (tid == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);   // weights need no producer: before the wait
+    const int pre = p.pre < 0 ? S : min(p.pre, S);
+    if (tid == 0) for (int st = 0; st < pre && st < n_stages; st++) issue(st);   // weights need no producer: before the wait
     pdl_wait();
+    if (tid == 0) for (int st = pre; st < S && st < n_stages; st++) issue(st);
     if (WT == PI_TYPE_F16) {
         const uint4 * src = reinterpret_cast<const uint4 *>(p.x.h16);
         uint4 * dstx = reinterpret_cast<uint4 *>(xs);
@@ -445,9 +448,11 @@ __global__ void __launch_bounds__(RING_THREADS) k_gemv_ring_g(const RingP p) {
         n_items = p.nrows;
         const int total_stages = (n_items + R - 1) / R;
         n_stages = cta < total_stages ? (total_stages - cta + G - 1) / G : 0;
-        if (warp == 0) for (int st = 0; st < S && st < n_stages; st++) issue(st);
+        const int pre = p.pre < 0 ? S : min(p.pre, S);
+        if (warp == 0) for (int st = 0; st < pre && st < n_stages; st++) issue(st);
     }
     pdl_wait();
+    if (!SPARSE && p.pre >= 0 && warp == 0) for (int st = min(p.pre, S); st < S && st < n_stages; st++) issue(st);
     if (SPARSE) {
         // the list entry this thread would own is read together with the count, not after it (the list buffer has nrows
         // entries whatever the count; entries beyond the count are stale and dropped below): one round trip, not two
@@ -635,6 +640,7 @@ int launch_gemv_ring(const GemvArgs & a, unsigned int * status, bool pdl, cudaSt
     p.list = a.list; p.count = a.count; p.bucket = a.bucket; p.idx = a.idx; p.threshold = a.threshold;
     p.bias = a.bias; p.relu = a.relu; p.dst = a.dst; p.dst16 = a.dst16; p.status = status;
     p.masks_out = nullptr; p.masks_threshold = a.masks_threshold;
+    p.pre = a.pre_stages;
     p.R = pl.R; p.split = pl.split; p.stages = pl.stages; p.max_items = pl.max_items; p.stage_bytes = pl.stage_bytes;
     const bool q4 = a.wtype == PI_TYPE_Q4_0;
     {

@@ -18,8 +18,8 @@ from ._lib import PI_TYPE_F16, PI_TYPE_Q4_0, check, lib
 
 PI_MAX_RANKS = 8
 PI_ARCH_BAMBOO = 3                     # the llama graph with the symmetric gate relu(gate) * relu(up)
-N_STAGES = 11
-STAGE_NAMES = ["norm", "qkv", "attention", "out_proj", "predictor", "compact", "up_gate", "down", "lm_head", "exchange", "other"]
+N_STAGES = 12
+STAGE_NAMES = ["norm", "qkv", "attention", "out_proj", "predictor", "compact", "up_gate", "down", "lm_head", "exchange", "other", "sparse_ffn"]
 
 _vp = C.c_void_p
 
