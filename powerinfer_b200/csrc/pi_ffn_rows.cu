@@ -16,6 +16,7 @@
 // time out: same bits every run.
 #include "pi_rows.cuh"
 
+#include <cstdio>
 #include <cstdlib>
 
 namespace pi {
@@ -415,6 +416,7 @@ bool ffn_plan_cs(const FfnRowsArgs & a, int cs, FfnPlan & pl) {
     if (cudaGetDevice(&dev) != cudaSuccess) return false;
     if (dev >= 0 && dev < 16 && !attr_done[dev]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) { cudaGetLastError(); return false; }
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) cudaGetLastError();   // clusters of 16
         attr_done[dev] = true;
     }
     const int n_chunks = (int)((a.nrows + 31) / 32);
@@ -461,7 +463,7 @@ int ffn_go(const FfnRowsP & p0, const FfnPlan & pl, bool pdl, cudaStream_t st) {
 template <int WT, bool GATED>
 int ffn_launch(const FfnRowsP & p, const FfnRowsArgs & a, int * groups_used, cudaStream_t st, bool plan_only) {
     constexpr int U = 8;                                            // 128-bit loads per matrix in flight per lane
-    // one plan per device and shape: the cluster size (8 or 4; PI_FFN_CS forces one) that keeps the most SMs busy
+    // one plan per device and shape (PI_FFN_CS forces a cluster size)
     struct Key { int dev; int64_t nrows, ncols; int groups; FfnPlan pl; };
     static Key cache[8];
     static int n_cache = 0;
@@ -475,14 +477,19 @@ int ffn_launch(const FfnRowsP & p, const FfnRowsArgs & a, int * groups_used, cud
         static int forced = -1;
         if (forced < 0) { const char * v = getenv("PI_FFN_CS"); forced = v ? atoi(v) : 0; }
         const int n_slices = (int)((a.ncols + SLICE - 1) / SLICE);
-        for (int cs = 8; cs >= 2; cs /= 2) {
-            if (forced && cs != forced) continue;
+        for (int cs = 16; cs >= 2; cs /= 2) {
+            if (forced ? cs != forced : cs > 8) continue;             // 16 only on request
             FfnPlan c;
             const bool two = (n_slices + cs - 1) / cs >= 2;
             const bool ok = two ? ffn_plan_cs<WT, GATED, U, 2>(a, cs, c) : ffn_plan_cs<WT, GATED, U, 1>(a, cs, c);
-            // more CTAs win, but a smaller cluster must beat a larger one by more than 5 %: it leaves twice the partial vectors
-            if (ok && (!pl.ok || c.n_clusters * c.cs * 100 > pl.n_clusters * pl.cs * 105)) pl = c;
+            // The largest cluster that can be launched wins although it keeps fewer SMs busy (15 x 8 = 120 of 148 on a B200
+            // against 33 x 4 = 132): it leaves half the partial vectors, which the norm after this kernel reads in one pass
+            // instead of two (measured per step: 6.11 ms against 6.25 ms).
+            if (ok && !pl.ok) pl = c;
         }
+        if (getenv("PI_FFN_VERBOSE"))
+            fprintf(stderr, "sparse FFN kernel plan: rows %lld cols %lld -> %s, cluster size %d, %d clusters, %d slices at a time, %zu bytes of shared memory\n",
+                    (long long)a.nrows, (long long)a.ncols, pl.ok ? "one launch" : "not eligible", pl.cs, pl.n_clusters, pl.ns, pl.smem);
         if (n_cache < 8) { cache[n_cache].dev = dev; cache[n_cache].nrows = a.nrows; cache[n_cache].ncols = a.ncols; cache[n_cache].groups = a.n_groups; cache[n_cache].pl = pl; n_cache++; }
     }
     if (!pl.ok) return PI_ERR_UNSUPPORTED;
