@@ -425,6 +425,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # refuse before allocating anything when this rank's share of the weights cannot fit the device (the weights are drawn
+    # once, then packed into the engine's layout: about twice their size at the peak)
+    rb = (lambda cols: cols // 32 * 18) if spec.wtype == 2 else (lambda cols: cols * 2)
+    per_layer = (spec.d + 2 * spec.d_kv + spec.d) * rb(spec.d) + 3 * spec.n_ff * rb(spec.d) + 2 * spec.rank * (spec.d + spec.n_ff)
+    need = spec.n_layer * per_layer / world * 1.25 + 2 * spec.n_vocab * spec.d * 2
+    have = torch.cuda.get_device_properties(local_rank).total_memory
+    if need > 0.92 * have:
+        raise SystemExit(f"bench.py: {cfg_name} needs about {need / 2**30:.0f} GiB per GPU on {world} GPU(s), the device has "
+                         f"{have / 2**30:.0f} GiB: run it with more GPUs (--gpus N under torch.distributed.run)")
     g, layers = synth_device.build_local_model(spec, world, rank, seed=0)
     PB = 32                                           # prompt chunk: tokens of one sequence per step
     eng = engine.DecodeEngine(spec, g, max_batch=max(T, PB), n_ranks=world, rank=rank, local_layers=layers)

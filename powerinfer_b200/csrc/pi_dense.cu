@@ -234,30 +234,29 @@ __global__ void __launch_bounds__(MAXT) k_norm(const NormP p) {
 // The same norm spread over a thread-block cluster: one SM moves the ~170 KB a norm of 8192 values touches (input,
 // residual, weights, new residual stream, activation planes) in ~3 us, eight SMs in a fraction of that.  CTA `rank` of the
 // cluster owns a contiguous slice of n / cluster_size values (a multiple of 256: whole Q8_0 blocks, whole warps); the
-// partial sums are exchanged through distributed shared memory and added in rank order, so the result does not depend on
-// timing.  Same order of additions and roundings per element as k_norm.
+// partial sums are pushed into every CTA's shared memory (distributed shared memory) and added in rank order, so the
+// result does not depend on timing.  Same order of additions and roundings per element as k_norm.
 __device__ __forceinline__ unsigned cluster_rank()  { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ unsigned cluster_size()  { unsigned r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ double cluster_read_f64(const double * local, unsigned rank) {
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait()   { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// store into the same shared-memory variable of CTA `rank` of this cluster
+__device__ __forceinline__ void cluster_store_f64(double * local, unsigned rank, double v) {
     unsigned la = (unsigned)__cvta_generic_to_shared(local), ra;
-    double v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(rank));
-    asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(ra) : "memory");
-    return v;
+    asm volatile("st.shared::cluster.f64 [%0], %1;" :: "r"(ra), "d"(v) : "memory");
 }
 
 __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
     __shared__ double s_red[32];
-    __shared__ double s_part[2];
+    __shared__ double s_all[2][8];                                  // [statistic][CTA of the cluster]: every CTA's partial sums, pushed by their owners
     const unsigned rank = cluster_rank(), CS = cluster_size();
     const int t = blockIdx.x / CS;
     const int64_t n = p.n;
     const int64_t c = (int64_t)rank * (n / CS) + (int64_t)threadIdx.x * 8;      // every thread owns 8 values: blockDim = n / CS / 8
     const size_t o = (size_t)t * n + c;
     pdl_launch();
+    cluster_arrive();                                                // (waited for before the first store into a peer's shared memory)
     if ((threadIdx.x & 3) == 0) {
         if (p.w) asm volatile("prefetch.global.L2 [%0];" :: "l"(p.w + c));
         if (p.b) asm volatile("prefetch.global.L2 [%0];" :: "l"(p.b + c));
@@ -285,6 +284,15 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
                     b[u] = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)(g0 + u) * tn + o + 4));
                 }
             }
+#ifdef PI_TIMELINE
+            if (g0 == 0) {                                           // when did the residual, the first and the last partial vector arrive?
+                unsigned t0, t1, t2;
+                asm volatile("mov.b32 %0, %1;" : "=r"(t0) : "f"(r0.x)); PI_TL_MARK(5);
+                asm volatile("mov.b32 %0, %1;" : "=r"(t1) : "f"(a[0].x)); PI_TL_MARK(6);
+                asm volatile("mov.b32 %0, %1;" : "=r"(t2) : "f"(b[14].w)); PI_TL_MARK(7);          // (15 partial vectors in the case under the lens)
+                if ((t0 ^ t1 ^ t2) == 0x7fc12345u) v[0] = 1.f;
+            }
+#endif
 #pragma unroll
             for (int u = 0; u < GP; u++) add8(a[u], b[u]);
         }
@@ -375,12 +383,18 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
     if (p.act2_type && p.act2_src == 0) emit_act8(p.act2_type, p.act2, t, n, (int)(c / 8), v, true);
     PI_TL_MARK(1);
 
-    auto cluster_total = [&](double mine, int slot) {               // every CTA gets the sum over the cluster, ranks in order
+    // Every CTA gets the sum over the cluster, ranks in order.  The partial sums are PUSHED: CTA r writes its sum into slot r of
+    // every CTA's table, one cluster barrier, then everybody adds its own table.  Nobody reads remote shared memory, so no
+    // CTA has to wait at the end of the kernel for peers that might still be reading from it.
+    bool peers_running = false;
+    auto cluster_total = [&](double mine, int slot) {
         mine = block_sum_d(mine, s_red);
-        if (threadIdx.x == 0) s_part[slot] = mine;
-        cluster_sync();
+        if (!peers_running) { cluster_wait(); peers_running = true; }      // the arrival of the kernel's first line: every CTA has started
+        if (threadIdx.x < CS) cluster_store_f64(&s_all[slot][rank], threadIdx.x, mine);
+        cluster_arrive();
+        cluster_wait();
         double tot = 0.0;
-        for (unsigned r = 0; r < CS; r++) tot += cluster_read_f64(&s_part[slot], r);
+        for (unsigned r = 0; r < CS; r++) tot += s_all[slot][r];
         return tot;
     };
     float scale;
@@ -418,7 +432,6 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
     if (p.act_type) emit_act8(p.act_type, p.act, t, n, (int)(c / 8), y, true);
     if (p.act2_type && p.act2_src == 1) emit_act8(p.act2_type, p.act2, t, n, (int)(c / 8), y, true);
     PI_TL_MARK(3);
-    cluster_sync();                                                  // nobody leaves while a peer may still read its partial sums
     PI_TL_MARK(4);
 }
 
