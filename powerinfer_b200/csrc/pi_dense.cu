@@ -284,15 +284,6 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
                     b[u] = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)(g0 + u) * tn + o + 4));
                 }
             }
-#ifdef PI_TIMELINE
-            if (g0 == 0) {                                           // when did the residual, the first and the last partial vector arrive?
-                unsigned t0, t1, t2;
-                asm volatile("mov.b32 %0, %1;" : "=r"(t0) : "f"(r0.x)); PI_TL_MARK(5);
-                asm volatile("mov.b32 %0, %1;" : "=r"(t1) : "f"(a[0].x)); PI_TL_MARK(6);
-                asm volatile("mov.b32 %0, %1;" : "=r"(t2) : "f"(b[14].w)); PI_TL_MARK(7);          // (15 partial vectors in the case under the lens)
-                if ((t0 ^ t1 ^ t2) == 0x7fc12345u) v[0] = 1.f;
-            }
-#endif
 #pragma unroll
             for (int u = 0; u < GP; u++) add8(a[u], b[u]);
         }
