@@ -119,6 +119,12 @@ int pi_sparse_ffn(int wtype, const void * up, const void * gate, const void * do
  * one array: the words that must start at zero are cleared on the stream at the start of every call, and two calls that
  * overlap on the GPU (different streams, or different host threads) race on it, so serialise them. */
 size_t pi_axpy_static_max_bytes(void);
+
+/* Did the last pi_mul_mat_idx / pi_axpy / pi_sparse_ffn that used `workspace` finish all its bounded device-side waits (the
+ * batch kernels stream rows through rings of bulk copies guarded by waits that give up after a limit rather than hang)?
+ * PI_OK, or PI_ERR_TIMEOUT with the status bits in pi_last_error(): the call's result is then incomplete.  workspace NULL:
+ * the built-in array of pi_axpy_static on the current device.  Synchronises `stream`.  (The engine has pi_engine_status.) */
+int pi_op_status(const void * workspace, void * stream);
 int pi_axpy_static(int wtype, const void * Wt, int64_t n_w_rows, int64_t ncols,
                    const float * h, int64_t h_stride, const float * idx, int64_t idx_stride,
                    const int32_t * bucket, float threshold, float * dst, void * stream);

@@ -37,6 +37,7 @@ def _load():
         "pi_sparse_ffn": (i32, [i32, vp, vp, vp, i64, i64, vp, i32, vp, i64, vp, f32, vp, vp, vp, sz, vp]),
         "pi_axpy_static_max_bytes": (sz, []),
         "pi_axpy_static": (i32, [i32, vp, i64, i64, vp, i64, vp, i64, vp, f32, vp, vp]),
+        "pi_op_status": (i32, [vp, vp]),
         "pi_mul_mat": (i32, [i32, vp, i64, i64, vp, i32, vp, vp, vp, sz, vp]),
         "pi_predictor": (i32, [vp, vp, i64, i64, i64, vp, i32, vp, vp, sz, vp]),
         "pi_active_list": (i32, [vp, i64, i32, i64, f32, vp, vp, vp, sz, vp]),
@@ -53,7 +54,7 @@ def _load():
 
 lib = _load()
 EXPORTS = ["pi_last_error", "pi_version", "pi_row_bytes", "pi_workspace_bytes", "pi_quantize_q4_0", "pi_q4_0_repack",
-           "pi_dequantize_q4_0", "pi_quantize_q8_0", "pi_mul_mat_idx", "pi_axpy", "pi_sparse_ffn", "pi_axpy_static_max_bytes", "pi_axpy_static",
+           "pi_dequantize_q4_0", "pi_quantize_q8_0", "pi_mul_mat_idx", "pi_axpy", "pi_sparse_ffn", "pi_axpy_static_max_bytes", "pi_axpy_static", "pi_op_status",
            "pi_mul_mat", "pi_predictor",
            "pi_active_list", "pi_norm", "pi_rope", "pi_rope_table_host", "pi_attention_decode"]
 

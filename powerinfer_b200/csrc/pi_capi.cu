@@ -45,9 +45,11 @@ static int check_w(int wtype, int64_t ncols, const void * W) {
 
 struct SparseScratch { int32_t * list; int32_t * count; unsigned int * ticket; unsigned int * status; uint32_t * masks; };
 
+// The control words come FIRST in every sparse operator's workspace (count, ticket, status at bytes 0, 4, 8), so that
+// pi_op_status can find the status word of whichever operator used the workspace last.
 static bool carve_sparse(Scratch & s, int64_t n_rows, SparseScratch & o) {
-    o.list = (int32_t *)s.take((size_t)n_rows * 4);
     int32_t * ct = (int32_t *)s.take(256);
+    o.list = (int32_t *)s.take((size_t)n_rows * 4);
     o.masks = (uint32_t *)s.take((size_t)((n_rows + 31) / 32) * 4);
     if (!o.list || !ct || !o.masks) return false;
     o.count = ct; o.ticket = (unsigned int *)(ct + 1); o.status = (unsigned int *)(ct + 2);
@@ -173,8 +175,9 @@ int pi_mul_mat_idx(int wtype, const void * W, int64_t n_w_rows, int64_t ncols,
     cudaStream_t st = (cudaStream_t)stream;
     Scratch s(workspace, workspace_bytes);
     SparseScratch ss;
+    const bool carved = carve_sparse(s, n_w_rows, ss);
     char * actp = (char *)s.take(act_bytes(wtype, ncols, T));
-    if (!aligned(workspace, 256) || !actp || !carve_sparse(s, n_w_rows, ss)) { set_error("mul_mat_idx: workspace too small or misaligned"); return PI_ERR_WORKSPACE; }
+    if (!aligned(workspace, 256) || !actp || !carved) { set_error("mul_mat_idx: workspace too small or misaligned"); return PI_ERR_WORKSPACE; }
     ActBuf act = act_carve(wtype, ncols, T, &actp);
     if (bucket) PI_CUDA(cudaMemsetAsync(dst, 0, (size_t)T * n_dst_rows * 4, st));      // rows held elsewhere read 0
     PI_CUDA(cudaMemsetAsync(ss.count, 0, 12, st));                                      // count, ticket, status
@@ -247,8 +250,9 @@ int pi_sparse_ffn(int wtype, const void * up, const void * gate, const void * do
     Scratch s(workspace, workspace_bytes);
     SparseScratch ss;
     const int G = axpy_groups(wtype, ncols, T);
+    const bool carved = carve_sparse(s, n_w_rows, ss);
     char * actp = (char *)s.take(act_bytes(wtype, ncols, T));
-    bool ok = aligned(workspace, 256) && actp && carve_sparse(s, n_w_rows, ss);
+    bool ok = aligned(workspace, 256) && actp && carved;
     float * h = ok ? (float *)s.take((size_t)T * F * 4) : nullptr;
     int8_t * cq = nullptr; float * cd = nullptr;
     if (ok && wtype == PI_TYPE_Q4_0) {
@@ -304,6 +308,23 @@ int pi_sparse_ffn(int wtype, const void * up, const void * gate, const void * do
     int used = G;
     if ((rc = launch_axpy(a, st, &used))) return rc;
     return launch_reduce_partials(partial, used, T, ncols, nullptr, nullptr, dst, st, T == 1);
+}
+
+int pi_op_status(const void * workspace, void * stream) {
+    const void * ws = workspace;
+    if (!ws) {                                                       // the built-in array of pi_axpy_static on the current device
+        void * p = nullptr;
+        const int rc = static_scratch_address(&p);
+        if (rc) return rc;
+        ws = p;
+    }
+    PI_REQUIRE(aligned(ws, 256), "op_status: the workspace of the call to be checked (256-byte aligned), or NULL for pi_axpy_static");
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned int word = 0;
+    PI_CUDA(cudaMemcpyAsync(&word, (const char *)ws + 8, 4, cudaMemcpyDeviceToHost, st));
+    PI_CUDA(cudaStreamSynchronize(st));
+    if (word) { set_error("a bounded wait inside a kernel of the last sparse operator ran out (status bits 0x%x): its result is incomplete", word); return PI_ERR_TIMEOUT; }
+    return PI_OK;
 }
 
 int pi_norm(const float * x, int T, int64_t n, int rms, float eps, const float * w, const float * b, float * y, void * stream) {

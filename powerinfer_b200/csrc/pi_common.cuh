@@ -84,8 +84,6 @@ int launch_quantize_q8_0_ggml(const float * x, void * q8, int64_t nrows, int64_t
 // x F32 [T, n] (row stride x_stride) -> activation planes for `wtype` weights
 int launch_convert_act(int wtype, const float * x, int64_t x_stride, int64_t n, int T, ActBuf out, cudaStream_t st);
 
-// Byte ranges for l2_prefetch() below.
-struct Prefetch { const void * ptr[2] = {nullptr, nullptr}; size_t bytes[2] = {0, 0}; };
 
 struct GemvArgs {
     int wtype = PI_TYPE_F16;
@@ -140,7 +138,6 @@ struct CompactArgs {
 int launch_compact(const CompactArgs & a, cudaStream_t st);
 
 // pulls the byte ranges into L2 (a hint; nothing may depend on it)
-int launch_prefetch(const Prefetch & pf, cudaStream_t st);
 
 struct AxpyArgs {
     int wtype = PI_TYPE_F16;
@@ -186,6 +183,7 @@ bool ffn_rows_eligible(const FfnRowsArgs & a);      // up / gate / down_t (null 
 int launch_neuron_q8(const float * h, int64_t stride, int64_t n, int T, int8_t * cq, float * cd, cudaStream_t st);
 
 // sum partial [n_groups, T, n] in group order (+ residual + bias) -> dst [T, n]
+int static_scratch_address(void ** out);      // device address of pi_axpy_static's built-in scratch array on the current device
 int launch_reduce_partials(const float * partial, int n_groups, int T, int64_t n, const float * residual,
                            const float * bias, float * dst, cudaStream_t st, bool pdl = false,
                            const float * residual2 = nullptr, double * stats_out = nullptr);
@@ -270,24 +268,6 @@ __device__ __forceinline__ void pdl_wait() {
 }
 #define PI_TL_MARK(i) do { if (tl_me()) g_tl[s_tl_slot * 16 + 8 + (i)] = tl_time(); } while (0)
 #endif
-
-// Up to two byte ranges (weights of kernels that run later in the step) to pull into L2.  Every participating thread
-// issues bulk L2 prefetches for 8 KB pieces, pieces interleaved over all participating threads so the range arrives
-// front to back, the order the consumer streams it in.  A hint only: nothing waits for it and nothing depends on it.
-__device__ __forceinline__ void l2_prefetch(const Prefetch & pf, int part, int n_parts, int tid, int nthreads) {
-    constexpr size_t PIECE = 8192;
-#pragma unroll
-    for (int k = 0; k < 2; k++) {
-        if (!pf.ptr[k]) continue;
-        const size_t bytes = pf.bytes[k] & ~size_t(15);
-        const size_t n_piece = (bytes + PIECE - 1) / PIECE;
-        for (size_t c = (size_t)part * nthreads + tid; c < n_piece; c += (size_t)n_parts * nthreads) {
-            const size_t off = c * PIECE;
-            const unsigned sz = (unsigned)(bytes - off < PIECE ? bytes - off : PIECE);
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(reinterpret_cast<const char *>(pf.ptr[k]) + off), "r"(sz) : "memory");
-        }
-    }
-}
 
 // ---- shared-memory transaction barriers and bulk copies (plain cp.async.bulk: non-tensor, one destination CTA) used by
 // every ring kernel.  A wait is always a bounded loop around mbar_try_wait in the caller.

@@ -426,18 +426,6 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
     PI_TL_MARK(4);
 }
 
-// One CTA per SM, every thread issues bulk L2 prefetches for its pieces: no shared memory and few registers, so the
-// CTAs fit beside whatever the main chain has resident.
-__global__ void __launch_bounds__(128) k_prefetch(const Prefetch pf) {
-    l2_prefetch(pf, (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, (int)blockDim.x);
-}
-
-int launch_prefetch(const Prefetch & pf, cudaStream_t st) {
-    k_prefetch<<<sm_count(), 128, 0, st>>>(pf);
-    PI_LAUNCH_CHECK("k_prefetch");
-    return PI_OK;
-}
-
 int launch_norm(const NormArgs & a, cudaStream_t st) {
     if (a.T <= 0) return PI_OK;
     PI_REQUIRE(a.n % 8 == 0 && a.n <= (int64_t)NORM_CHUNKS * 1024 * 8, "norm: n=%lld must be a multiple of 8 and <= %d",

@@ -19,7 +19,7 @@ static constexpr int MAX_DEVICES = 64;
 static void * g_scratch_ptr[MAX_DEVICES] = {nullptr};
 
 // Device address of the scratch array on the CURRENT device; looked up once per device.
-static int scratch_address(void ** out) {
+int static_scratch_address(void ** out) {
     int dev = 0;
     PI_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MAX_DEVICES) { set_error("axpy_static: device ordinal %d not supported", dev); return PI_ERR_UNSUPPORTED; }
@@ -53,7 +53,7 @@ int pi_axpy_static(int wtype, const void * Wt, int64_t n_w_rows, int64_t ncols,
     PI_REQUIRE(need <= STATIC_AXPY_BYTES, "axpy_static: this shape needs %zu bytes of scratch, the built-in array holds %zu; use pi_axpy",
                need, STATIC_AXPY_BYTES);
     void * scratch = nullptr;
-    const int rc = scratch_address(&scratch);
+    const int rc = static_scratch_address(&scratch);
     if (rc) return rc;
     // pi_axpy clears the words that must start at zero (count, ticket, status) itself and overwrites the rest before
     // reading it, so whatever the previous call left in the array is harmless.

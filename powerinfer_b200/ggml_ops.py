@@ -59,6 +59,14 @@ class Workspace:
 _ws = Workspace()
 
 
+def last_op_status() -> int:
+    """Status of the last sparse operator issued through this module (pi_op_status): 0, or 5 (a bounded device-side wait ran out)."""
+    if _ws.buf is None:
+        return 0
+    off = (-_ws.buf.data_ptr()) % 256
+    return int(lib.pi_op_status(_ws.buf.data_ptr() + off, _stream()))
+
+
 def upload_weight(host: np.ndarray, wtype: int, nrows: int, ncols: int) -> Weight:
     """host: float16 [nrows, ncols], or uint8 ggml Q4_0 blocks [nrows, ncols/32*18]."""
     if wtype == PI_TYPE_F16:

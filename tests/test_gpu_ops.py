@@ -148,6 +148,7 @@ def test_sparse_ffn_one_call_vs_oracle_nodes(ops, oracle, wtype, T, gated):
                            up_bias=dev(bias) if bias is not None else None)
     ref_b = ref_ffn(gpu_idx)
     assert np.abs(got_b.cpu().numpy() - ref_b).max() <= 5 * ATOL, np.abs(got_b.cpu().numpy() - ref_b).max()
+    assert ops.last_op_status() == 0                                  # no bounded wait of the batch kernels ran out
 
 
 @pytest.mark.parametrize("wtype", [synth.F16, synth.Q4_0])

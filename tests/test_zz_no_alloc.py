@@ -50,6 +50,8 @@ def test_axpy_static_matches_axpy_on_two_calls_in_a_row(wtype, oracle):
         assert torch.equal(got, want), f"call {call}: same kernels, same order"
         ref = oracle.axpy(wtype, Wt, F, d, h, idx, np.zeros(F, np.int32))
         assert np.abs(got.cpu().numpy() - ref).max() <= ATOL, f"call {call}: against the CPU checker"
+        assert lib.pi_op_status(None, stream) == 0, lib.pi_last_error().decode()     # the built-in array's status word: no wait ran out
+        assert ggml_ops.last_op_status() == 0
 
 
 def test_axpy_static_rejects_shapes_beyond_its_scratch():
