@@ -79,7 +79,8 @@ def pi_env() -> dict:
 # ------------------------------------------------------------------------------------------------ clocks
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons sampled every 50 ms; `stop(t0, t1)` keeps the samples that arrived while the
+    timed region ran (host clock around it: from the first launch to the end of the synchronisation that follows it)."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -87,7 +88,7 @@ class ClockSampler:
         self.rows, self.proc = [], None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(index)], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -95,19 +96,20 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
-    def stop(self) -> dict:
+    def stop(self, t0: float | None = None, t1: float | None = None) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
+        time.sleep(0.1)                                    # let the last line of the region arrive
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             pass
         sm, mx, reasons = [], [], set()
-        for r in self.rows:
+        inside = [r for (t, r) in self.rows if t0 is not None and t1 is not None and t0 <= t <= t1 + 0.05]
+        for r in (inside if inside else [r for (_, r) in self.rows]):
             try:
                 sm.append(float(r[0])); mx.append(float(r[1]))
             except Exception:
@@ -471,6 +473,7 @@ def main():
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_host0 = time.monotonic()
     with torch.cuda.stream(eng.stream):
         torch.cuda.nvtx.range_push("timed_steps")     # lets a profiler pick exactly the timed launches (--nvtx-include "timed_steps/")
         ev0.record()
@@ -479,9 +482,10 @@ def main():
         ev1.record()
         torch.cuda.nvtx.range_pop()
     eng.stream.synchronize()
+    t_host1 = time.monotonic()
     barrier()
     ms = ev0.elapsed_time(ev1)
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(t_host0, t_host1) if sampler else None
     eng.status()
     launches_per_step = eng.launches() + 1
 
