@@ -99,3 +99,24 @@ def test_shard_shapes_and_block_alignment():
             assert sl["gate"] is None and sl["fc2"].shape == (spec.n_ff // world, spec.rank)
             rows += sl["down_t"].shape[0]
         assert rows == spec.n_ff
+
+
+def test_eight_rank_shards_partition_heads_and_neurons():
+    """The 8-GPU split of a model with the headline's proportions (8 heads and one KV head per rank, neurons in whole
+    32-blocks): shapes per rank, and the ranks' rows put together give back the unsharded tensors."""
+    spec = synth.ModelSpec(arch=synth.ARCH_LLAMA, wtype=synth.F16, n_layer=1, d=1024, n_ff=4096, n_head=64, n_head_kv=8, rank=64)
+    t = synth.build_model(spec)
+    world = 8
+    full = sharding.shard_layer(spec, t, 0, 1, 0)
+    ups, downs, fc2s = [], [], []
+    for r in range(world):
+        sl = sharding.shard_layer(spec, t, 0, world, r)
+        dq, dkv = spec.d // world, spec.d_kv // world
+        assert sl["wqkv"].shape[0] == dq + 2 * dkv and dkv == spec.d_kv // spec.n_head_kv      # exactly one KV head
+        assert sl["wo"].shape[0] == spec.d
+        assert sl["up"].shape[0] == spec.n_ff // world and sl["up"].shape[0] % 32 == 0
+        assert np.array_equal(sl["fc1"], full["fc1"])                                           # replicated
+        ups.append(sl["up"]); downs.append(sl["down_t"]); fc2s.append(sl["fc2"])
+    assert np.array_equal(np.concatenate(ups), full["up"])
+    assert np.array_equal(np.concatenate(downs), full["down_t"])
+    assert np.array_equal(np.concatenate(fc2s), full["fc2"])
