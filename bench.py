@@ -497,7 +497,7 @@ def main():
         eng.decode_host_raw(T)
         eng.h_tokens[:T] = eng.h_argmax[:T]; eng.h_pos[:T] += 1
     barrier()
-    greedy_ids = []                                   # sequence 0's greedy continuation: the same at every GPU count
+    greedy_ids = []                                   # sequence 0's greedy continuation (a record of the run: on random weights the stream changes with the GPU count, because the partial vectors are added in another order and neurons at the threshold flip)
     t0 = time.perf_counter()
     for _ in range(K):
         eng.decode_host_raw(T)                        # H2D ids+positions, graph, D2H logits + greedy id, synchronize
