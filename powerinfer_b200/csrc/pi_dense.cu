@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(256) k_norm_cluster(const NormP p) {
     if (p.partial) {
         const size_t tn = p.partial_stride ? (size_t)p.partial_stride : (size_t)p.T * n;
         const float * partial = p.partial;
-        constexpr int GP = 20;                                         // slots in flight per pass (the one-token axpy writes 12-37)
+        constexpr int GP = 24;                                         // slots in flight per pass (the one-token sparse kernels write 12-37)
         float4 a[GP], b[GP];
         for (int g0 = 0; g0 < p.n_groups; g0 += GP) {
 #pragma unroll

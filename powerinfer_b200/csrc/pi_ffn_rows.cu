@@ -477,8 +477,8 @@ int ffn_launch(const FfnRowsP & p, const FfnRowsArgs & a, int * groups_used, cud
         static int forced = -1;
         if (forced < 0) { const char * v = getenv("PI_FFN_CS"); forced = v ? atoi(v) : 0; }
         const int n_slices = (int)((a.ncols + SLICE - 1) / SLICE);
-        for (int cs = 16; cs >= 2; cs /= 2) {
-            if (forced ? cs != forced : cs > 8) continue;             // 16 only on request
+        for (int cs = 16; cs >= 2; cs--) {
+            if (forced ? cs != forced : (cs != 8 && cs != 4 && cs != 2)) continue;     // other sizes only on request
             FfnPlan c;
             const bool two = (n_slices + cs - 1) / cs >= 2;
             const bool ok = two ? ffn_plan_cs<WT, GATED, U, 2>(a, cs, c) : ffn_plan_cs<WT, GATED, U, 1>(a, cs, c);
