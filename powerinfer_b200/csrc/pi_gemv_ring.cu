@@ -582,6 +582,10 @@ static RingPlan ring_plan(int wtype, int64_t nrows, int64_t ncols, bool sparse, 
         const int G = sm_count() * cps;
         int R = 1;
         while (R < 64 && (size_t)(2 * R) * nm * row_bytes <= (budget <= 64 * 1024 ? 19 : 36) * 1024) R *= 2;
+        // a small dense matrix (a rank's share in a sharded run): rather more, smaller stages than CTAs without any
+        static int small_on = -1;                                    // PI_RING_SMALL=0: keep the large stages (diagnostic)
+        if (small_on < 0) { const char * v = getenv("PI_RING_SMALL"); small_on = !(v && v[0] == '0'); }
+        while (small_on && !sparse && R > RING_WARPS && (nrows + R - 1) / R < G) R /= 2;
         // RW vectors per warp (register blocking), `split` warps per group of RW; a warp's column share stays >= 32 units
         const int nv = R * nm;
         if (nv > RING_MAX_VEC) continue;
